@@ -1,0 +1,225 @@
+"""Matrix orthogonalisation (zeroth power / polar factor): quintic Newton–Schulz, Polar Express,
+QR and SVD modes, plus the Scion linear-minimisation oracles built on top of them.
+
+Behavioural parity targets: ``heavyball/utils.py:550-657`` (iterations and coefficient tables),
+``heavyball/utils.py:784-821`` (mode dispatch and scaling), ``heavyball/utils.py:660-733`` (Scion).
+
+Each polynomial step maps ``X -> (a I + b S + c S^2) X`` with ``S = X X^T``.  On sm_100a the chain runs
+as three tcgen05 GEMMs per step (``heavyball_b200.ops.newton_schulz``): the Gram matrix and the
+polynomial are symmetric, so only upper-triangular tiles are computed and mirrored; the diagonal
+shifts are folded into the GEMM epilogues.  The PyTorch code below is the numerics reference for
+that kernel and the path taken on CPU, for fp64 inputs and for batches the kernel does not cover.
+"""
+
+from __future__ import annotations
+
+import enum
+import itertools
+import math
+import sys
+from typing import List, Union
+
+import torch
+from torch import Tensor
+
+from .core import copy_stochastic_, list_guard, promote, stochastic_divide_, stochastic_divide_with_eps_, stochastic_round_
+
+
+def _settings():
+    return sys.modules[__package__]
+
+
+class ZerothPowerMode(enum.Enum):
+    newtonschulz = "newtonschulz"
+    legacy_newtonschulz = "legacy_newtonschulz"
+    qr = "qr"
+    svd = "svd"
+    legacy_svd = "legacy_svd"
+    thinky_polar_express = "thinky_polar_express"
+
+
+class OrthoScaleMode(enum.Enum):
+    none = "none"
+    scale = "scale"
+    graft = "graft"
+
+
+# Per-step (a, b, c) of the quintic used by Muon's five-step iteration.
+NS5_COEFFS = (
+    (4.0848, -6.8946, 2.9270),
+    (3.9505, -6.3029, 2.6377),
+    (3.7418, -5.5913, 2.3037),
+    (2.8769, -3.1427, 1.2046),
+    (2.8366, -3.0525, 1.2012),
+)
+
+# Polar Express (arXiv:2505.16932v3) minimax polynomials.
+ABC_LIST = [
+    (8.28721201814563, -23.595886519098837, 17.300387312530933),
+    (4.107059111542203, -2.9478499167379106, 0.5448431082926601),
+    (3.9486908534822946, -2.908902115962949, 0.5518191394370137),
+    (3.3184196573706015, -2.488488024314874, 0.51004894012372),
+    (2.300652019954817, -1.6689039845747493, 0.4188073119525673),
+    (1.891301407787398, -1.2679958271945868, 0.37680408948524835),
+    (1.8750014808534479, -1.2500016453999487, 0.3750001645474248),
+    (1.875, -1.25, 0.375),
+]
+_SAFETY = 1.01
+ABC_LIST_STABLE = [(a / _SAFETY, b / _SAFETY**3, c / _SAFETY**5) for a, b, c in ABC_LIST[:-1]] + [ABC_LIST[-1]]
+
+LEGACY_COEFFS = (3.4445, -4.7750, 2.0315)
+
+
+def _poly_step(x: Tensor, a: float, b: float, c: float) -> Tensor:
+    s = x @ x.mT
+    y = c * s
+    y.diagonal(dim1=-2, dim2=-1).add_(b)
+    y = y @ s
+    y.diagonal(dim1=-2, dim2=-1).add_(a)
+    return y @ x
+
+
+def _iterate(G: Tensor, coeffs, eps: float) -> Tensor:
+    tall = G.size(-2) > G.size(-1)
+    Gn = G / G.norm(dim=(-2, -1), keepdim=True).clamp(min=eps)
+    x = Gn if G.dtype == torch.float64 else stochastic_round_(Gn)
+    if tall:
+        x = x.mT
+    for a, b, c in coeffs:
+        x = _poly_step(x, a, b, c)
+    if tall:
+        x = x.mT
+    return x.to(G.dtype)
+
+
+def _device_kernel(G: Tensor, coeffs):
+    """Returns the fused sm_100a implementation's result, or ``None`` when it does not apply."""
+    if not G.is_cuda or G.dtype == torch.float64:
+        return None
+    from .. import ops
+
+    if not ops.available():
+        return None
+    return ops.newton_schulz(G, coeffs)
+
+
+def zeropower_via_newtonschulz5(G: Tensor, steps: int = 5, eps: float = 1e-7) -> Tensor:
+    assert G.ndim >= 2
+    assert steps == 5
+    out = _device_kernel(G, NS5_COEFFS)
+    return out if out is not None else _iterate(G, NS5_COEFFS, eps)
+
+
+def msign(G: Tensor, steps: int = 10, eps: float = 1e-7) -> Tensor:
+    """Polar Express iteration for the matrix sign / polar factor."""
+    assert G.ndim >= 2
+    coeffs = [ABC_LIST_STABLE[min(i, len(ABC_LIST_STABLE) - 1)] for i in range(steps)]
+    out = _device_kernel(G, coeffs)
+    return out if out is not None else _iterate(G, coeffs, eps)
+
+
+def legacy_zeropower_via_newtonschulz5(G: Tensor, steps: int = 5, eps: float = 1e-7) -> Tensor:
+    assert G.ndim == 2
+    x = G.clone()
+    x = x if G.dtype == torch.float64 else stochastic_round_(x)
+    stochastic_divide_with_eps_(x, G.norm(dim=(-2, -1)), eps)
+    tall = G.size(0) > G.size(1)
+    if tall:
+        x = x.T
+    for _ in range(steps):
+        x = _poly_step(x, *LEGACY_COEFFS)
+    if tall:
+        x = x.T
+    return x.to(G.dtype)
+
+
+def _compilable_grafting(magnitude: Tensor, direction: Tensor) -> Tensor:
+    return direction * (magnitude.norm() / direction.norm().clamp(min=1e-6))
+
+
+def _compilable_orthogonal_(x: Tensor, mode, out, scale_mode):
+    mode = mode if isinstance(mode, ZerothPowerMode) else ZerothPowerMode(mode)
+    scale_mode = scale_mode if isinstance(scale_mode, OrthoScaleMode) else OrthoScaleMode(scale_mode)
+    if mode is ZerothPowerMode.newtonschulz or x.shape[-2] != x.shape[-1]:
+        y = zeropower_via_newtonschulz5(x, 5)
+    elif mode is ZerothPowerMode.thinky_polar_express:
+        y = msign(x, 10)
+    elif mode is ZerothPowerMode.legacy_newtonschulz:
+        y = legacy_zeropower_via_newtonschulz5(x, 5)
+    elif mode is ZerothPowerMode.qr:
+        y = torch.linalg.qr(promote(x)).Q
+    elif mode is ZerothPowerMode.svd:
+        u, _, vt = torch.linalg.svd(promote(x))
+        y = u @ vt
+    elif mode is ZerothPowerMode.legacy_svd:
+        u, _, vt = torch.linalg.svd(promote(x))
+        y = u @ vt.T
+    else:
+        raise NotImplementedError(f"Unknown zeroth_power_mode: {mode}")
+    if scale_mode is OrthoScaleMode.scale:
+        y = y * max(1, x.size(-2) / x.size(-1)) ** 0.5
+    elif scale_mode is OrthoScaleMode.graft:
+        y = _compilable_grafting(x, y)
+    if out is None:
+        return y
+    out.copy_(y)
+
+
+def inplace_orthogonal_(x: Tensor, mode=None, out=None, scale_mode: str = "none"):
+    return _compilable_orthogonal_(x, mode or _settings().zeroth_power_mode, out, scale_mode)
+
+
+# ---------------------------------------------------------------------------------------- Scion
+
+
+def _scion_bias_rms_direction(x: Tensor, eps: float = 1e-8) -> Tensor:
+    if x.ndim == 0:
+        return x / x.abs().clamp(min=eps)
+    rms = x.square().mean(dim=0, keepdim=True).sqrt()
+    stochastic_divide_(x, rms, eps=eps)
+    return x
+
+
+def _scion_matrix_direction(x: Tensor, conv: bool) -> Tensor:
+    flat = inplace_orthogonal_(x.reshape(x.shape[0], -1))
+    if conv:
+        spatial = math.prod(x.shape[2:]) if x.ndim > 2 else 1
+        scale = math.sqrt(x.shape[0] / max(x.shape[1], 1)) / max(spatial, 1)
+    else:
+        scale = math.sqrt(x.shape[0] / max(flat.shape[1], 1))
+    return flat.reshape_as(x) * scale
+
+
+def scion_auto_lmo_(update: Union[List[Tensor], Tensor], scale):
+    """Norm-constrained LMO chosen by rank: spectral (matrices), unfolded spectral (conv kernels),
+    RMS (vectors, scalars)."""
+    update = list_guard(update)
+    for t in update:
+        t32 = promote(t)
+        if t32.ndim in (3, 4):
+            d = _scion_matrix_direction(t32, True)
+        elif t32.ndim == 2:
+            d = _scion_matrix_direction(t32, False)
+        else:
+            d = _scion_bias_rms_direction(t32.clone() if t32 is t else t32)
+        copy_stochastic_(t, d * float(scale))
+    return update
+
+
+def scion_auto_init_param_(param: Tensor, scale, seed: int = 0):
+    """Deterministic (CPU, fp64, seeded) orthogonal re-initialisation of matrices; zeros for the
+    rest.  Matches the norm ball the Scion LMO moves on."""
+    p32 = promote(param)
+    gen = torch.Generator(device="cpu")
+    gen.manual_seed(seed)
+    if param.ndim >= 2:
+        w = p32.clone().cpu().double()
+        for idx in itertools.product(*(range(s) for s in w.shape[2:])):
+            torch.nn.init.orthogonal_(w[(slice(None), slice(None), *idx)], generator=gen)
+        spatial = math.prod(w.shape[2:])
+        w.mul_(math.sqrt(w.shape[0] / max(w.shape[1], 1)) / max(spatial, 1))
+        init = w.to(dtype=p32.dtype, device=p32.device)
+    else:
+        init = torch.zeros_like(p32)
+    init.mul_(float(scale))
+    copy_stochastic_(param, init.to(dtype=param.dtype, device=param.device))

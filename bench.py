@@ -1,0 +1,295 @@
+"""Headline benchmark: training throughput (tokens/s) and optimizer step time of a GPT-2-small-shaped
+decoder trained with SplitOpt(Muon lr 0.02 on the 2-D block weights, AdamW lr 3e-4 on the rest),
+bf16 autocast over fp32 master weights, 16 sequences x 1024 tokens per GPU, synthetic token ids.
+
+    python bench.py --gpus N --steps K --warmup W [--impl ours|reference]
+
+For N > 1 launch with ``python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N``.
+Rank 0 prints one JSON line.  ``value`` is device-timed (CUDA events, max over ranks, inputs
+pre-staged on the GPU); ``e2e.value`` times the same steps through the public API including the
+pinned host->device copy of every step's tokens and the device->host read of its loss.
+
+``--impl reference`` runs the unmodified reference package installed under ``baseline/_ref`` (its own
+optimizers and stock compile path, ``torch.nn`` DDP, a plain ``torch.nn`` model) for the same metric.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PUBLISHED_BASELINE = None  # the reference publishes no tokens/s figure for this config
+
+CONFIGS = {
+    "gpt2-small": dict(n_layer=12, n_head=12, d_model=768, vocab_size=50257, seq_len=1024, seqs_per_gpu=16),
+    "gpt2-tiny": dict(n_layer=2, n_head=4, d_model=256, vocab_size=4096, seq_len=256, seqs_per_gpu=4),
+}
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="gpt2-small", choices=sorted(CONFIGS))
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end phase")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = (
+        "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+        "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+        "clocks_event_reasons.sw_power_cap"
+    )
+
+    def __init__(self, device_index):
+        self.proc, self.index = None, device_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )  # fmt: skip
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        clocks, maxes, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                maxes.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        return {
+            "sm_mhz": clocks[len(clocks) // 2] if clocks else None,
+            "sm_max_mhz": max(maxes) if maxes else None,
+            "samples": len(clocks),
+            "reasons": sorted(reasons),
+        }
+
+
+def build_ours(cfg, device):
+    import heavyball_b200 as hb
+    from heavyball_b200.models import GPT, GPTConfig, split_param_groups
+
+    model = GPT(GPTConfig(cfg["n_layer"], cfg["n_head"], cfg["d_model"], 0, cfg["vocab_size"], cfg["seq_len"])).to(device)
+    mats, rest = split_param_groups(model)
+    opt = hb.SplitOpt([
+        {"params": mats, "optimizer": hb.Muon, "lr": 0.02},
+        {"params": rest, "optimizer": hb.AdamW, "lr": 3e-4},
+    ])
+    return model, opt
+
+
+def build_reference(cfg, device):
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import heavyball
+    from ref_model import RefGPT, split
+
+    mode = os.environ.get("HB_REF_COMPILE_MODE")  # unset = the reference's stock setting
+    if mode is not None:
+        heavyball.utils.compile_mode = None if mode in ("", "none") else mode
+    model = RefGPT(cfg["n_layer"], cfg["n_head"], cfg["d_model"], cfg["vocab_size"], cfg["seq_len"]).to(device)
+    mats, rest = split(model)
+    opt = heavyball.SplitOpt([
+        {"params": mats, "optimizer": heavyball.Muon, "lr": 0.02},
+        {"params": rest, "optimizer": heavyball.AdamW, "lr": 3e-4},
+    ])
+    return model, opt
+
+
+def main():
+    args = parse()
+    if args.impl == "reference" and not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "heavyball")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is missing (reference not installed)"}))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+
+    cfg = CONFIGS[args.config]
+    torch.manual_seed(0)
+    model, opt = (build_ours if args.impl == "ours" else build_reference)(cfg, device)
+    launches = None
+    if args.impl == "ours":
+        from heavyball_b200 import ops
+
+        launches = ops.launch_counter
+    if world > 1:
+        if args.impl == "ours":
+            from heavyball_b200.parallel import ddp as hb_ddp
+
+            train_model = hb_ddp.wrap(model, opt)
+        else:
+            from torch.nn.parallel import DistributedDataParallel
+
+            train_model = DistributedDataParallel(model, device_ids=[local])
+    else:
+        train_model = model
+
+    B, T, V = cfg["seqs_per_gpu"], cfg["seq_len"], cfg["vocab_size"]
+    n_host = 8
+    gen = torch.Generator().manual_seed(1234 + rank)
+    host_tokens = [torch.randint(0, V, (B, T + 1), generator=gen).pin_memory() for _ in range(n_host)]
+    dev_tokens = [t.to(device) for t in host_tokens]
+
+    def train_step(tokens):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = train_model(tokens[:, :-1], tokens[:, 1:])
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for i in range(args.warmup):
+        train_step(dev_tokens[i % n_host])
+    barrier()
+
+    # ---- phase 1: device-timed, inputs already on the GPU
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    if launches is not None:
+        launches.reset()
+    opt_ms = []
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    last = None
+    for i in range(args.steps):
+        last = train_step(dev_tokens[i % n_host])
+    stop.record()
+    barrier()
+    n_launch = launches.count if launches is not None else None
+    clocks = sampler.stop() if rank == 0 else None
+    step_ms = max_over_ranks(start.elapsed_time(stop) / args.steps)
+
+    # ---- optimizer step alone (same state, gradients from one backward), device-timed
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(min(args.steps, 10)):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = train_model(dev_tokens[i % n_host][:, :-1], dev_tokens[i % n_host][:, 1:])
+        loss.backward()
+        torch.cuda.synchronize()
+        e0.record()
+        opt.step()
+        e1.record()
+        torch.cuda.synchronize()
+        opt.zero_grad(set_to_none=True)
+        opt_ms.append(e0.elapsed_time(e1))
+    opt_ms.sort()
+    opt_step_ms = max_over_ranks(opt_ms[len(opt_ms) // 2])
+
+    # ---- phase 2: end to end through the public API: pinned H2D copy of the tokens and a D2H read of
+    # the loss every step
+    e2e = None
+    if not args.no_e2e:
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            tokens = host_tokens[i % n_host].to(device, non_blocking=True)
+            loss = train_step(tokens)
+            _ = loss.item()
+        barrier()
+        e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3 / args.steps)
+        e2e = {
+            "value": B * T * world / (e2e_ms * 1e-3),
+            "unit": "tokens/s",
+            "ms_per_step": e2e_ms,
+            "h2d_bytes_per_step": host_tokens[0].numel() * host_tokens[0].element_size(),
+            "d2h_bytes_per_step": 4,
+        }
+
+    if args.impl == "ours":
+        from heavyball_b200 import ops
+
+        ops.check_status()
+    if rank == 0:
+        value = B * T * world / (step_ms * 1e-3)
+        out = {
+            "metric": "train tokens/s (GPT-2-small, SplitOpt Muon+AdamW); optimizer step ms in 'optimizer_step_ms'",
+            "impl": args.impl,
+            "value": value,
+            "unit": "tokens/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": step_ms,
+            "optimizer_step_ms": opt_step_ms,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": (value / PUBLISHED_BASELINE) if PUBLISHED_BASELINE else None,
+            "dtype": "bf16",
+            "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
+            "config": {
+                "model": args.config, "global_batch": B * world, "seq_len": T, "parallelism": f"dp{world}",
+                "optimizer": "SplitOpt(Muon lr=0.02 NS5 on 2-D block weights, AdamW lr=3e-4 on the rest)",
+                "precision": "bf16 autocast, fp32 master weights and optimizer state",
+                "l2": "per-step working set (activations, 124M fp32 params + state) exceeds the 126 MB L2",
+            },
+            "clocks": clocks,
+            "e2e": e2e,
+            "gpu_launches": n_launch,
+            "final_loss": float(last.detach()),
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -174,6 +174,36 @@ class ZeroSlots(Layer):
             else:
                 ecc.init_state(st, self.keys[n], param)
 
+    def _slab_init(self, states, group, param):
+        """When several parameters are initialised in one call, each slot's buffers are carved out
+        of one zeroed slab (16-byte aligned segments) instead of being allocated one by one, so a
+        group's state is contiguous in memory for the multi-tensor kernels."""
+        todo = [
+            (st, p) for st, p in zip(states, param)
+            if self.index not in st.get("is_initialized", ()) and p.is_contiguous()
+        ]  # fmt: skip
+        if len(todo) < 2 or len({(p.device, p.dtype) for _, p in todo}) != 1:
+            return
+        ecc = ECCConfig.from_group(group)
+        kinds = [("", _storage_dtype(group))] if ecc is None else [("", ecc.primary_dtype), ("::ecc", ecc.corr_dtype)]
+        sizes = [(p.numel() + 15) // 16 * 16 for _, p in todo]
+        dev = todo[0][1].device
+        for n in self.slots:
+            for suffix, dtype in kinds:
+                key = self.keys[n] + suffix
+                if any(key in st for st, _ in todo):
+                    continue
+                slab = torch.zeros(sum(sizes), dtype=dtype, device=dev)
+                off = 0
+                for (st, p), size in zip(todo, sizes):
+                    st[key] = slab[off : off + p.numel()].view(p.shape)
+                    off += size
+
+    def run(self, tr, depth, state, group, update, grad, param, *args, **kwargs):
+        if len(param) > 1 and group.get("slab_state", True):
+            self._slab_init(_states_of(state, param), group, param)
+        return super().run(tr, depth, state, group, update, grad, param, *args, **kwargs)
+
     def forward(self, tr, depth, state, group, update, grad, param, slot_lists, *args, **kwargs):
         ecc = ECCConfig.from_group(group)
         if ecc is None:

@@ -1,5 +1,296 @@
-"""Placeholder replaced below."""
+"""Chain lowering: run a whole transform chain as a handful of sm_100a kernel launches.
+
+``ChainOpt`` offers every step to :func:`try_run`.  The chain is matched against a small set of
+*programs*; when one fits and the tensors are eligible, the step executes through
+``heavyball_b200.ops`` and the PyTorch definitions in ``chainable`` / ``utils`` are bypassed.
+Otherwise ``try_run`` returns ``False`` and the caller runs those definitions (same results up to
+rounding-noise layout, which the tests bound).
+
+Programs
+--------
+``elementwise``   ``[mars] [palm] <rule>``: one launch per group (two with ``caution``: the mask's
+                  keep-ratio is a per-tensor reduction over the finished update, so the masked update is
+                  parked in a scratch buffer, counted, then applied).
+``orthogonal``    ``[mars] [palm] <momentum rule> orthogonalize_update``: momentum launch -> batched
+                  Newton–Schulz per shape bucket (tcgen05 GEMM chain) -> parameter-update launch.
+
+State is created by the PyTorch path on the first step of a parameter (``ZeroSlots`` hands out views
+of one slab per slot, so buffers of a group are contiguous); lowering engages once all state exists,
+and writes the same state keys, so checkpoints do not depend on which path ran.
+"""
+
+from __future__ import annotations
+
+import os
+from typing import List, Optional
+
+import torch
+
+from . import chainable as C
+from . import ops, utils
+
+enabled = os.environ.get("HB200_DISABLE_LOWERING") != "1"
+
+# transform name -> (algo, state slot names in kernel order, needs second beta)
+_RULES = {
+    "update_by_adam": (ops.ADAM, ("exp_avg", "exp_avg_sq")),
+    "update_by_adamc": (ops.ADAM, ("exp_avg", "exp_avg_sq")),
+    "scale_by_adam": (ops.ADAM, ("exp_avg", "exp_avg_sq")),
+    "update_by_laprop": (ops.LAPROP, ("exp_avg", "exp_avg_sq")),
+    "scale_by_laprop": (ops.LAPROP, ("exp_avg", "exp_avg_sq")),
+    "update_by_adopt": (ops.ADOPT, ("exp_avg", "exp_avg_sq")),
+    "scale_by_adopt": (ops.ADOPT, ("exp_avg", "exp_avg_sq")),
+    "update_by_ademamix": (ops.ADEMAMIX, ("exp_avg_fast", "exp_avg_sq", "exp_avg_slow")),
+    "scale_by_ademamix": (ops.ADEMAMIX, ("exp_avg_fast", "exp_avg_sq", "exp_avg_slow")),
+    "scale_by_exp_avg_sq": (ops.RMSPROP, (None, "exp_avg_sq")),
+    "scale_by_unscaled_adam": (ops.UNSCALED_ADAM, ("exp_avg", "exp_avg_sq")),
+    "exp_avg": (ops.EXP_AVG, ("exp_avg",)),
+    "nesterov_ema": (ops.NESTEROV_EMA, ("momentum",)),
+    "heavyball_momentum": (ops.HEAVYBALL, ("momentum",)),
+    "nesterov_momentum": (ops.NESTEROV_MOM, ("momentum",)),
+}
 
 
-def try_run(opt, state, group, grads, params):
-    return False
+class _Program:
+    __slots__ = ("kind", "mars", "palm", "rule", "ortho", "workspace")
+
+    def __init__(self, kind, mars, palm, rule, ortho):
+        self.kind, self.mars, self.palm, self.rule, self.ortho = kind, mars, palm, rule, ortho
+        self.workspace = {}
+
+
+def _match(fns) -> Optional[_Program]:
+    fns = list(fns)
+    mars = palm = None
+    if fns and isinstance(fns[0], C.FunctionTransform) and fns[0].fn_name == "mars":
+        mars = fns.pop(0)
+    if fns and getattr(fns[0], "__name__", "") == "palm_beta2" and not isinstance(fns[0], C.FunctionTransform):
+        palm = fns.pop(0)
+    if not fns or not all(isinstance(f, C.FunctionTransform) for f in fns):
+        return None
+    rule = fns[0]
+    if rule.fn_name not in _RULES:
+        return None
+    if len(fns) == 1:
+        return _Program("elementwise", mars, palm, rule, None)
+    if len(fns) == 2 and fns[1].fn_name == "orthogonalize_update":
+        return _Program("orthogonal", mars, palm, rule, fns[1])
+    return None
+
+
+def _program(opt) -> Optional[_Program]:
+    cached = opt._lowered
+    if cached is None:
+        cached = opt._lowered = _match(opt.fns) or False
+    return cached or None
+
+
+def _mark_initialized(tr: C.FunctionTransform, st: dict):
+    for layer in tr.layers:
+        if isinstance(layer, (C.ZeroSlots, C.CopySlots, C.InitSlots, C.Tag, C.PerTensor, C.Warmup)):
+            C._mark(st, layer.index)
+
+
+def _state_ready(tr: C.FunctionTransform, states: List[dict], ecc: bool) -> bool:
+    keys = list(tr._val_names.values())
+    warm = [(layer.counter, len(layer.warmup_fns)) for layer in tr.layers if isinstance(layer, C.Warmup)]
+    for st in states:
+        for k in keys:
+            if k not in st or (ecc and k + "::ecc" not in st):
+                return False
+        for counter, need in warm:
+            if st.get(counter, 0) < need:
+                return False
+    return True
+
+
+def _eligible(t: torch.Tensor) -> bool:
+    return t.is_cuda and t.is_contiguous() and t.dtype in (torch.float32, torch.bfloat16, torch.float16)
+
+
+def _seed(opt, group, launch: int) -> int:
+    base = getattr(opt, "_rng_base", None)
+    if base is None:
+        base = opt._rng_base = torch.initial_seed() & 0xFFFFFFFFFFFF
+    return (base * 0x9E3779B1 + group["step"] * 1315423911 + launch * 2654435761 + id(group) % 8191) & 0x7FFFFFFFFFFFFFFF
+
+
+def _slots(tr, states, names, ecc: bool):
+    """Kernel slot lists (s0, s0e, s1, s1e, s2, s2e) for a rule transform."""
+    out = []
+    for n in names + (None,) * (3 - len(names)):
+        if n is None:
+            out += [[], []]
+            continue
+        key = tr._val_names[n]
+        out.append([st[key] for st in states])
+        out.append([st[key + "::ecc"] for st in states] if ecc else [])
+    return out
+
+
+def _rule_scalars(rule_name, group):
+    """Host-side coefficients, computed exactly as the PyTorch definitions do."""
+    step = group["step"]
+    cfg = {"eps": group["eps"]}
+    algo = _RULES[rule_name][0]
+    if algo in (ops.ADAM, ops.LAPROP, ops.UNSCALED_ADAM):
+        cfg["b1"] = utils.beta_debias(utils.get_beta1(group), step)
+        cfg["b2"] = utils.beta_debias(utils.get_beta2(group), step)
+    elif algo == ops.ADOPT:
+        cfg["b1"] = utils.beta_debias(utils.get_beta1(group), step - 1)
+        cfg["b3"] = 1 - utils.beta_debias(utils.get_beta2(group), step)
+    elif algo == ops.ADEMAMIX:
+        b1, b2, b3, alpha = utils._compute_ademamix_hparams(
+            group["betas"], step, group["alpha"], group.get("beta3_warmup"), group.get("alpha_warmup")
+        )
+        cfg.update(b1=utils.beta_debias(b1, step), b2=utils.beta_debias(b2, step), b3=b3, alpha=alpha)
+    elif algo == ops.RMSPROP:
+        cfg["b2"] = utils.beta_debias(utils.get_beta2(group), step)
+    elif algo == ops.EXP_AVG:
+        cfg["b1"] = utils.beta_debias(utils.get_beta1(group), step)
+    else:  # momentum flavours use the raw coefficient
+        cfg["b1"] = utils.get_beta1(group)
+    return cfg
+
+
+def _weight_decay(rule_name, group):
+    if rule_name == "update_by_adamc":
+        return group["lr"] * group["weight_decay"] / group["max_lr"]
+    return group["weight_decay"]
+
+
+def try_run(opt, states, group, grads, params) -> bool:
+    if not enabled or not ops.available():
+        return False
+    prog = _program(opt)
+    if prog is None:
+        return False
+    if not all(_eligible(p) for p in params):
+        return False
+    ecc_mode, pecc_mode = group.get("ecc"), group.get("param_ecc")
+    if prog.kind == "orthogonal" and utils.zeroth_power_mode != "newtonschulz":
+        return False
+    if not _state_ready(prog.rule, states, bool(ecc_mode)):
+        return False
+    if prog.mars is not None and not _state_ready(prog.mars, states, bool(ecc_mode)):
+        return False
+    if pecc_mode and any("param::ecc" not in st for st in states):
+        return False
+    grads = [g if g.is_contiguous() else g.contiguous() for g in grads]
+    gdt = grads[0].dtype
+    if any(g.dtype != gdt or not g.is_cuda for g in grads) or gdt not in (torch.float32, torch.bfloat16, torch.float16):
+        return False
+    pdt = params[0].dtype
+    if any(p.dtype != pdt for p in params):
+        return False
+    rule_name = prog.rule.fn_name
+    algo, names = _RULES[rule_name]
+    key0 = prog.rule._val_names[next(n for n in names if n is not None)]
+    sdt = states[0][key0].dtype
+    if any(st[key0].dtype != sdt for st in states):
+        return False
+
+    if prog.palm is not None:
+        prog.palm(None, group, None, None, None)
+    for st in states:
+        _mark_initialized(prog.rule, st)
+        if prog.mars is not None:
+            _mark_initialized(prog.mars, st)
+        if prog.ortho is not None:
+            _mark_initialized(prog.ortho, st)
+
+    s0, s0e, s1, s1e, s2, s2e = _slots(prog.rule, states, names, bool(ecc_mode))
+    base = dict(
+        dt_g=ops.dtype_code(grads[0]), dt_s=ops.dtype_code(states[0][key0], ecc_mode),
+        dt_p=ops.dtype_code(params[0], pecc_mode), n_state=len(names), algo=algo,
+    )  # fmt: skip
+    base.update(_rule_scalars(rule_name, group))
+    mars_kw = {}
+    if prog.mars is not None:
+        mkey = prog.mars._val_names["mars_old_grad"]
+        gamma, beta1 = utils.get_beta1(group), group["mars_gamma"]  # argument order of the transform
+        mars_kw = dict(
+            mars=[st[mkey] for st in states], marse=[st[mkey + "::ecc"] for st in states] if ecc_mode else [],
+            mars_a=-gamma * beta1 / (1 - beta1),
+        )  # fmt: skip
+    pe = [st["param::ecc"] for st in states] if pecc_mode else []
+    epilogue = dict(
+        lr=group["lr"], wd=_weight_decay(rule_name, group), cautious_wd=int(bool(group.get("cautious_weight_decay", False)))
+    )
+    caution = bool(group["caution"])
+
+    launch = ops.fused_chain
+
+    if prog.kind == "elementwise":
+        if not caution:
+            launch(p=params, pe=pe, g=grads, s0=s0, s0e=s0e, s1=s1, s1e=s1e, s2=s2, s2e=s2e, out_mode=ops.OUT_PARAM,
+                   seed=_seed(opt, group, 0), **base, **epilogue, **mars_kw)  # fmt: skip
+            return True
+        scratch = _scratch(prog, params)
+        masked = torch.zeros(len(params), dtype=torch.int32, device=params[0].device)
+        launch(g=grads, u=scratch, s0=s0, s0e=s0e, s1=s1, s1e=s1e, s2=s2, s2e=s2e, masked=masked, count_caution=1,
+               out_mode=ops.OUT_UPDATE, dt_u=ops.F32, seed=_seed(opt, group, 0), **base, **mars_kw)  # fmt: skip
+        ops.fused_chain(p=params, pe=pe, u=scratch, masked=masked, algo=ops.IDENTITY, u_is_input=1, caution_apply=1,
+                        out_mode=ops.OUT_PARAM, dt_u=ops.F32, dt_p=base["dt_p"], dt_g=ops.NONE, dt_s=ops.NONE,
+                        seed=_seed(opt, group, 1), **epilogue)  # fmt: skip
+        return True
+
+    # ---- orthogonal program: momentum -> Newton–Schulz per shape bucket -> parameter update
+    scratch = _scratch(prog, params)
+    launch(g=grads, u=scratch, s0=s0, s0e=s0e, s1=s1, s1e=s1e, s2=s2, s2e=s2e, out_mode=ops.OUT_UPDATE, dt_u=ops.F32,
+           seed=_seed(opt, group, 0), **base, **mars_kw)  # fmt: skip
+    scale_mode = "scale"
+    buckets = {}
+    for i, u in enumerate(scratch):
+        if u.ndim >= 2:
+            buckets.setdefault((u.shape[0], u[0].numel()), []).append(i)
+    final = list(scratch)
+    for (R, Cc), idx in buckets.items():
+        if not ops.ns_supported(R, Cc):
+            for i in idx:
+                flat = scratch[i].view(R, Cc)
+                utils.inplace_orthogonal_(flat, out=flat, scale_mode=scale_mode)
+            continue
+        out = _bucket_out(prog, (R, Cc, len(idx)), params[0].device)
+        ops.newton_schulz_batched(
+            [scratch[i].view(R, Cc) for i in idx], utils.NS5_COEFFS, out=out, out_scale=max(1, R / Cc) ** 0.5,
+            seed=_seed(opt, group, 2 + len(final) + R),
+        )
+        for b, i in enumerate(idx):
+            final[i] = out[b].view(params[i].shape)
+    if caution:
+        masked = torch.zeros(len(params), dtype=torch.int32, device=params[0].device)
+        ops.fused_chain(g=grads, u=final, masked=masked, algo=ops.IDENTITY, u_is_input=1, count_caution=1,
+                        out_mode=ops.OUT_UPDATE, dt_u=ops.F32, dt_g=base["dt_g"], dt_s=ops.NONE, dt_p=ops.NONE,
+                        seed=_seed(opt, group, 1))  # fmt: skip
+        ops.fused_chain(p=params, pe=pe, u=final, masked=masked, algo=ops.IDENTITY, u_is_input=1, caution_apply=1,
+                        out_mode=ops.OUT_PARAM, dt_u=ops.F32, dt_p=base["dt_p"], dt_g=ops.NONE, dt_s=ops.NONE,
+                        seed=_seed(opt, group, 3), **epilogue)  # fmt: skip
+    else:
+        ops.fused_chain(p=params, pe=pe, u=final, algo=ops.IDENTITY, u_is_input=1, out_mode=ops.OUT_PARAM, dt_u=ops.F32,
+                        dt_p=base["dt_p"], dt_g=ops.NONE, dt_s=ops.NONE, seed=_seed(opt, group, 3), **epilogue)  # fmt: skip
+    return True
+
+
+def _scratch(prog: _Program, params) -> List[torch.Tensor]:
+    """fp32 update buffers, one per parameter, carved from one slab and cached on the program."""
+    key = ("u", tuple(p.data_ptr() for p in params))
+    hit = prog.workspace.get(key)
+    if hit is None:
+        sizes = [(p.numel() + 15) // 16 * 16 for p in params]
+        slab = torch.empty(sum(sizes), dtype=torch.float32, device=params[0].device)
+        hit, off = [], 0
+        for p, n in zip(params, sizes):
+            hit.append(slab[off : off + p.numel()].view(p.shape))
+            off += n
+        prog.workspace = {k: v for k, v in prog.workspace.items() if k[0] != "u"}
+        prog.workspace[key] = hit
+    return hit
+
+
+def _bucket_out(prog: _Program, key, device) -> torch.Tensor:
+    R, Cc, B = key
+    hit = prog.workspace.get(("ns", key))
+    if hit is None:
+        hit = prog.workspace[("ns", key)] = torch.empty(B, R, Cc, dtype=torch.float32, device=device)
+    return hit

@@ -1,0 +1,80 @@
+"""GPT-2-style decoder-only transformer."""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+@dataclass
+class GPTConfig:
+    n_layer: int = 12
+    n_head: int = 12
+    d_model: int = 768
+    d_ff: int = 0  # 0 -> 4 * d_model
+    vocab_size: int = 50257
+    seq_len: int = 1024
+    init_std: float = 0.02
+    tie_embeddings: bool = True
+
+
+class Block(nn.Module):
+    def __init__(self, cfg: GPTConfig):
+        super().__init__()
+        d, ff = cfg.d_model, cfg.d_ff or 4 * cfg.d_model
+        self.n_head = cfg.n_head
+        self.ln1 = nn.LayerNorm(d)
+        self.qkv = nn.Linear(d, 3 * d)
+        self.proj = nn.Linear(d, d)
+        self.ln2 = nn.LayerNorm(d)
+        self.fc = nn.Linear(d, ff)
+        self.out = nn.Linear(ff, d)
+
+    def forward(self, x):
+        B, T, D = x.shape
+        q, k, v = self.qkv(self.ln1(x)).view(B, T, 3, self.n_head, D // self.n_head).permute(2, 0, 3, 1, 4)
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        x = x + self.proj(a.transpose(1, 2).reshape(B, T, D))
+        return x + self.out(F.gelu(self.fc(self.ln2(x)), approximate="tanh"))
+
+
+class GPT(nn.Module):
+    def __init__(self, cfg: GPTConfig):
+        super().__init__()
+        self.cfg = cfg
+        self.wte = nn.Embedding(cfg.vocab_size, cfg.d_model)
+        self.wpe = nn.Embedding(cfg.seq_len, cfg.d_model)
+        self.blocks = nn.ModuleList(Block(cfg) for _ in range(cfg.n_layer))
+        self.ln_f = nn.LayerNorm(cfg.d_model)
+        self.head = nn.Linear(cfg.d_model, cfg.vocab_size, bias=False)
+        if cfg.tie_embeddings:
+            self.head.weight = self.wte.weight
+        self.apply(self._init)
+
+    def _init(self, m):
+        if isinstance(m, (nn.Linear, nn.Embedding)):
+            nn.init.normal_(m.weight, 0.0, self.cfg.init_std)
+            if getattr(m, "bias", None) is not None:
+                nn.init.zeros_(m.bias)
+
+    def forward(self, idx, targets=None):
+        B, T = idx.shape
+        x = self.wte(idx) + self.wpe(torch.arange(T, device=idx.device))
+        for blk in self.blocks:
+            x = blk(x)
+        logits = self.head(self.ln_f(x))
+        if targets is None:
+            return logits
+        return F.cross_entropy(logits.float().view(-1, logits.size(-1)), targets.reshape(-1))
+
+
+def gpt2_small(**kw):
+    return GPT(GPTConfig(n_layer=12, n_head=12, d_model=768, vocab_size=50257, seq_len=1024, **kw))
+
+
+def gpt_350m(**kw):
+    return GPT(GPTConfig(n_layer=24, n_head=16, d_model=1024, vocab_size=50257, seq_len=1024, **kw))

@@ -1,2 +1,248 @@
-def available():
-    return False
+"""sm_100a kernels and their Python entry points.
+
+The extension is compiled in-tree (``heavyball_b200/ops/_build``) for ``sm_100a`` only and loaded
+lazily.  On a machine with a CUDA device the kernels are *the* implementation: if the extension cannot
+be loaded or built, :func:`load` raises instead of silently falling back to PyTorch ops.
+
+Entry points
+------------
+``fused_chain``      one multi-tensor pass: decode -> MARS -> moment rule -> caution -> decay -> write
+``sumsq``            per-tensor sum of squares (segmented reduction)
+``newton_schulz``    batched quintic Newton–Schulz / Polar-Express chain on tcgen05 tensor cores
+"""
+
+from __future__ import annotations
+
+import importlib.util
+import os
+import threading
+from typing import List, Optional, Sequence
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SRC = os.path.join(_HERE, "csrc")
+_BUILD = os.path.join(_HERE, "_build")
+_NAME = "hb200_ops"
+_SOURCES = ["bindings.cpp", "fused_chain.cu", "ns_gemm.cu"]
+_lock = threading.Lock()
+_ext = None
+_load_error: Optional[BaseException] = None
+
+# storage kinds (mirror of hb::DType)
+F32, BF16, F16, BF16E8, BF16E16, F16E8, F16E16, NONE = range(8)
+# algorithms (mirror of hb::Algo)
+IDENTITY, ADAM, LAPROP, ADOPT, ADEMAMIX, RMSPROP, UNSCALED_ADAM, EXP_AVG, NESTEROV_EMA, HEAVYBALL, NESTEROV_MOM = range(11)
+OUT_PARAM, OUT_UPDATE = 0, 1
+MODE_GRAM, MODE_POLY, MODE_APPLY = 0, 1, 2
+
+CUDA_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
+    "-U__CUDA_NO_HALF_OPERATORS__", "-U__CUDA_NO_BFLOAT16_CONVERSIONS__",
+]  # fmt: skip
+
+
+def _sources():
+    return [os.path.join(_SRC, s) for s in _SOURCES]
+
+
+def build(verbose: bool = False):
+    """Compile the extension for sm_100a into the in-tree build directory (works without a GPU)."""
+    from torch.utils.cpp_extension import load
+
+    os.makedirs(_BUILD, exist_ok=True)
+    os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
+    mod = load(
+        name=_NAME, sources=_sources(), build_directory=_BUILD, extra_cuda_cflags=CUDA_FLAGS,
+        extra_cflags=["-O2", "-std=c++17"], extra_include_paths=[_SRC], verbose=verbose,
+    )  # fmt: skip
+    with open(os.path.join(_BUILD, "sources.sha256"), "w") as fh:
+        fh.write(_source_digest())
+    return mod
+
+
+def _source_digest() -> str:
+    import hashlib
+
+    h = hashlib.sha256()
+    for name in sorted(os.listdir(_SRC)):
+        with open(os.path.join(_SRC, name), "rb") as fh:
+            h.update(name.encode() + b"\0" + fh.read())
+    return h.hexdigest()
+
+
+def _import_prebuilt():
+    so = os.path.join(_BUILD, _NAME + ".so")
+    if not os.path.exists(so):
+        return None
+    stamp = os.path.join(_BUILD, "sources.sha256")
+    if not os.path.exists(stamp) or open(stamp).read().strip() != _source_digest():
+        return None  # sources changed since the library was built: rebuild
+    spec = importlib.util.spec_from_file_location(_NAME, so)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def load():
+    """Returns the extension module, importing the prebuilt library or compiling it."""
+    global _ext, _load_error
+    if _ext is not None:
+        return _ext
+    with _lock:
+        if _ext is not None:
+            return _ext
+        if _load_error is not None:
+            raise RuntimeError("heavyball_b200.ops: extension unavailable") from _load_error
+        try:
+            _ext = _import_prebuilt() or build()
+        except BaseException as err:  # noqa: BLE001
+            _load_error = err
+            raise RuntimeError(
+                "heavyball_b200.ops: the sm_100a extension could not be loaded or built; "
+                "run `python -c 'import __graft_entry__ as g; g.build()'` from the repository root"
+            ) from err
+    return _ext
+
+
+def available() -> bool:
+    """True when kernels can run here: a CUDA device of compute capability 10.x is present.  The
+    extension itself is loaded on first use and failure to load is an error, not a fallback."""
+    if os.environ.get("HB200_DISABLE_OPS") == "1":
+        return False
+    if not torch.cuda.is_available():
+        return False
+    major, _ = torch.cuda.get_device_capability()
+    return major == 10
+
+
+class _LaunchCounter:
+    """Counts kernel launches issued through this module (benchmarks report it)."""
+
+    def __init__(self):
+        self.count = 0
+
+    def reset(self):
+        self.count = 0
+
+
+launch_counter = _LaunchCounter()
+
+
+# ---------------------------------------------------------------------------------------- element-wise
+
+
+def dtype_code(t: Optional[torch.Tensor], ecc: Optional[str] = None) -> int:
+    if t is None:
+        return NONE
+    if ecc:
+        return {"bf16+8": BF16E8, "bf16+16": BF16E16, "fp16+8": F16E8, "fp16+16": F16E16}[ecc]
+    return {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}[t.dtype]
+
+
+_EMPTY: List = []
+
+
+def fused_chain(*, p=_EMPTY, pe=_EMPTY, g=_EMPTY, u=_EMPTY, s0=_EMPTY, s0e=_EMPTY, s1=_EMPTY, s1e=_EMPTY, s2=_EMPTY,
+                s2e=_EMPTY, mars=_EMPTY, marse=_EMPTY, scale=None, masked=None, **cfg):  # fmt: skip
+    cfg["mars"] = 1 if len(mars) else 0
+    launch_counter.count += 1
+    load().fused_chain(
+        list(p), list(pe), list(g), list(u), list(s0), list(s0e), list(s1), list(s1e), list(s2), list(s2e), list(mars),
+        list(marse), scale, masked, cfg,
+    )  # fmt: skip
+
+
+def sumsq(xs: Sequence[torch.Tensor]) -> torch.Tensor:
+    launch_counter.count += 1
+    return load().sumsq(list(xs), dtype_code(xs[0]))
+
+
+# ---------------------------------------------------------------------------------------- Newton–Schulz
+
+
+def _round_up(x, m):
+    return (x + m - 1) // m * m
+
+
+_status_cache = {}
+
+
+def _status(device):
+    st = _status_cache.get(device)
+    if st is None:
+        st = _status_cache[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return st
+
+
+def check_status(device=None):
+    """Raises if any tensor-core kernel reported an expired wait since the last check (host sync)."""
+    for dev, st in list(_status_cache.items()):
+        if device is not None and dev != device:
+            continue
+        if int(st.item()) != 0:
+            st.zero_()
+            raise RuntimeError("heavyball_b200.ops: a Newton–Schulz GEMM aborted on a bounded wait")
+
+
+def ns_supported(R: int, C: int) -> bool:
+    return min(R, C) >= 8 and max(R, C) >= 64
+
+
+def newton_schulz_batched(mats: Sequence[torch.Tensor], coeffs, out: Optional[torch.Tensor] = None, out_scale=1.0,
+                          eps: float = 1e-7, seed: Optional[int] = None) -> torch.Tensor:  # fmt: skip
+    """Orthogonalises a list of same-shape ``(R, C)`` fp32 / bf16 matrices; returns fp32 ``(B, R, C)``
+    holding ``out_scale * polar_factor``.  ``coeffs`` is a sequence of ``(a, b, c)`` per step."""
+    ext = load()
+    B = len(mats)
+    R, C = mats[0].shape
+    dev = mats[0].device
+    m, n = (R, C) if R <= C else (C, R)
+    ldx, ldxt, lds = _round_up(n, 8), _round_up(m, 8), _round_up(m, 8)
+    bf = dict(dtype=torch.bfloat16, device=dev)
+    X = [torch.empty(B, m, ldx, **bf) for _ in range(2)]
+    XT = [torch.empty(B, n, ldxt, **bf) for _ in range(2)]
+    S = torch.empty(B, m, lds, **bf)
+    Y = torch.empty(B, m, lds, **bf)
+    if out is None:
+        out = torch.empty(B, R, C, dtype=torch.float32, device=dev)
+    if seed is None:
+        seed = int(torch.randint(0, 2**62, (1,)).item())
+    norms = ext.sumsq([t.contiguous() for t in mats], dtype_code(mats[0]))
+    srcs = [t.contiguous() for t in mats]
+    if R <= C:
+        ext.ns_prepare(srcs, dtype_code(mats[0]), R, C, norms, eps, X[0], ldx, XT[0], ldxt, seed)
+    else:  # work on the transpose so that the Gram matrix is the small one
+        ext.ns_prepare(srcs, dtype_code(mats[0]), R, C, norms, eps, XT[0], ldxt, X[0], ldx, seed)
+    status = _status(dev)
+    launch_counter.count += 2 + 3 * len(coeffs)
+    cur = 0
+    for step, (a, b, c) in enumerate(coeffs):
+        last = step == len(coeffs) - 1
+        x, xt = X[cur], XT[cur]
+        ext.ns_gemm(x, ldx, m * ldx, x, ldx, m * ldx, m, m, n, B, MODE_GRAM, True, S, lds, m * lds, S, lds, m * lds,
+                    None, 0, 0, False, 1.0, None, 0, 0, 0.0, 0.0, 0.0, status)  # fmt: skip
+        ext.ns_gemm(S, lds, m * lds, S, lds, m * lds, m, m, m, B, MODE_POLY, True, Y, lds, m * lds, Y, lds, m * lds,
+                    None, 0, 0, False, 1.0, S, lds, m * lds, a, b, c, status)  # fmt: skip
+        if not last:
+            nx, nxt = X[1 - cur], XT[1 - cur]
+            ext.ns_gemm(Y, lds, m * lds, xt, ldxt, n * ldxt, m, n, m, B, MODE_APPLY, False, nx, ldx, m * ldx, nxt, ldxt,
+                        n * ldxt, None, 0, 0, False, 1.0, None, 0, 0, 0.0, 0.0, 0.0, status)  # fmt: skip
+            cur = 1 - cur
+        else:  # final product goes straight to fp32 in the caller's orientation
+            ext.ns_gemm(Y, lds, m * lds, xt, ldxt, n * ldxt, m, n, m, B, MODE_APPLY, False, None, 0, 0, None, 0, 0,
+                        out, C, R * C, R > C, out_scale, None, 0, 0, 0.0, 0.0, 0.0, status)  # fmt: skip
+    return out
+
+
+def newton_schulz(G: torch.Tensor, coeffs, out_scale: float = 1.0) -> Optional[torch.Tensor]:
+    """Drop-in for the PyTorch iteration on one ``(..., R, C)`` tensor; ``None`` if the shape is not
+    covered by the kernel (the caller then uses the PyTorch definition)."""
+    if G.ndim < 2 or G.dtype not in (torch.float32, torch.bfloat16):
+        return None
+    R, C = G.shape[-2:]
+    if not ns_supported(R, C):
+        return None
+    mats = list(G.reshape(-1, R, C).unbind(0))
+    res = newton_schulz_batched(mats, coeffs, out_scale=out_scale)
+    return res.reshape(G.shape).to(G.dtype)

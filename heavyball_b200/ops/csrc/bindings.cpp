@@ -1,0 +1,161 @@
+// Python bindings: translate torch tensors into the raw tables the kernels consume.
+// Kernels live in the .cu files and know nothing about torch; this file owns all torch-facing glue.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <optional>
+#include <vector>
+
+#include "fused_chain.h"
+#include "ns_gemm.h"
+
+namespace py = pybind11;
+using OptT = std::optional<at::Tensor>;
+using TList = std::vector<OptT>;
+
+namespace {
+
+void check(cudaError_t e, const char* what) {
+  TORCH_CHECK(e == cudaSuccess, what, ": ", cudaGetErrorString(e));
+}
+
+void* ptr_or_null(const TList& l, size_t i) {
+  if (l.empty() || !l[i].has_value() || !l[i]->defined()) return nullptr;
+  return l[i]->data_ptr();
+}
+
+bool aligned16(const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+struct Table {
+  at::Tensor device_blob;  // metas followed by the chunk prefix
+  const hb::TensorMeta* metas;
+  const int* prefix;
+  int total_chunks;
+  int n;
+};
+
+// Builds the per-tensor table and uploads it with one async copy on the current stream.
+Table upload(std::vector<hb::TensorMeta>& metas, const at::Device& dev) {
+  const int n = (int)metas.size();
+  const int chunk = hb::chain_chunk_elems();
+  std::vector<int> prefix(n + 1, 0);
+  for (int i = 0; i < n; ++i) prefix[i + 1] = prefix[i] + (int)((metas[i].numel + chunk - 1) / chunk);
+  const size_t meta_bytes = sizeof(hb::TensorMeta) * n, prefix_bytes = sizeof(int) * (n + 1);
+  std::vector<uint8_t> host(meta_bytes + prefix_bytes);
+  memcpy(host.data(), metas.data(), meta_bytes);
+  memcpy(host.data() + meta_bytes, prefix.data(), prefix_bytes);
+  Table t;
+  t.device_blob = at::empty({(int64_t)host.size()}, at::TensorOptions().dtype(at::kByte).device(dev));
+  auto stream = at::cuda::getCurrentCUDAStream();
+  check(cudaMemcpyAsync(t.device_blob.data_ptr(), host.data(), host.size(), cudaMemcpyHostToDevice, stream), "table upload");
+  t.metas = reinterpret_cast<const hb::TensorMeta*>(t.device_blob.data_ptr());
+  t.prefix = reinterpret_cast<const int*>((uint8_t*)t.device_blob.data_ptr() + meta_bytes);
+  t.total_chunks = prefix[n];
+  t.n = n;
+  return t;
+}
+
+}  // namespace
+
+// One fused pass over a param group.  Every list is either empty or has one entry per tensor.
+// `cfg`: algo, out_mode, n_state, dt_p, dt_g, dt_u, dt_s, u_is_input, mars, cautious_wd, caution_apply,
+// use_tensor_scale, count_caution (ints); lr, wd, eps, b1, b2, b3, alpha, mars_a (floats); seed.
+void fused_chain(const TList& p, const TList& pe, const TList& g, const TList& u, const TList& s0, const TList& s0e,
+                 const TList& s1, const TList& s1e, const TList& s2, const TList& s2e, const TList& mars,
+                 const TList& marse, const OptT& scale, const OptT& masked, const py::dict& cfg) {
+  const size_t n = !g.empty() ? g.size() : (!u.empty() ? u.size() : p.size());
+  if (n == 0) return;
+  const at::Tensor& ref = !g.empty() ? *g[0] : (!u.empty() ? *u[0] : *p[0]);
+  c10::cuda::CUDAGuard guard(ref.device());
+  std::vector<hb::TensorMeta> metas(n);
+  for (size_t i = 0; i < n; ++i) {
+    hb::TensorMeta& m = metas[i];
+    m.p = ptr_or_null(p, i); m.pe = ptr_or_null(pe, i); m.g = ptr_or_null(g, i); m.u = ptr_or_null(u, i);
+    m.s0 = ptr_or_null(s0, i); m.s0e = ptr_or_null(s0e, i); m.s1 = ptr_or_null(s1, i); m.s1e = ptr_or_null(s1e, i);
+    m.s2 = ptr_or_null(s2, i); m.s2e = ptr_or_null(s2e, i); m.mars = ptr_or_null(mars, i); m.marse = ptr_or_null(marse, i);
+    m.scale = scale.has_value() ? scale->data_ptr<float>() + i : nullptr;
+    m.masked = masked.has_value() ? masked->data_ptr<int>() + i : nullptr;
+    const at::Tensor& any = !g.empty() && g[i].has_value() ? *g[i] : (!u.empty() && u[i].has_value() ? *u[i] : *p[i]);
+    m.numel = any.numel();
+    bool ok = true;
+    for (void* q : {m.p, m.pe, m.g, m.u, m.s0, m.s0e, m.s1, m.s1e, m.s2, m.s2e, m.mars, m.marse}) ok = ok && aligned16(q);
+    m.vec_ok = ok ? 1 : 0;
+    m.pad = 0;
+  }
+  Table t = upload(metas, ref.device());
+  hb::ChainParams P{};
+  auto geti = [&](const char* k) { return cfg.contains(k) ? cfg[k].cast<int>() : 0; };
+  auto getf = [&](const char* k) { return cfg.contains(k) ? cfg[k].cast<float>() : 0.f; };
+  P.n_tensors = t.n;
+  P.algo = geti("algo"); P.out_mode = geti("out_mode"); P.n_state = geti("n_state");
+  P.dt_p = geti("dt_p"); P.dt_g = geti("dt_g"); P.dt_u = geti("dt_u"); P.dt_s = geti("dt_s");
+  P.u_is_input = geti("u_is_input"); P.mars = geti("mars"); P.cautious_wd = geti("cautious_wd");
+  P.caution_apply = geti("caution_apply"); P.use_tensor_scale = geti("use_tensor_scale");
+  P.lr = getf("lr"); P.wd = getf("wd"); P.eps = getf("eps");
+  P.b1 = getf("b1"); P.b2 = getf("b2"); P.b3 = getf("b3"); P.alpha = getf("alpha"); P.mars_a = getf("mars_a");
+  P.seed = cfg.contains("seed") ? cfg["seed"].cast<uint64_t>() : 0;
+  check(hb::launch_fused_chain(t.metas, t.prefix, t.total_chunks, P, geti("count_caution") != 0,
+                               at::cuda::getCurrentCUDAStream()), "fused_chain launch");
+}
+
+// out[i] = sum(x_i^2) in fp32.
+at::Tensor sumsq(const std::vector<at::Tensor>& xs, int dt) {
+  TORCH_CHECK(!xs.empty(), "sumsq: empty list");
+  c10::cuda::CUDAGuard guard(xs[0].device());
+  std::vector<hb::TensorMeta> metas(xs.size());
+  for (size_t i = 0; i < xs.size(); ++i) {
+    memset(&metas[i], 0, sizeof(hb::TensorMeta));
+    metas[i].u = xs[i].data_ptr();
+    metas[i].numel = xs[i].numel();
+    metas[i].vec_ok = aligned16(metas[i].u) ? 1 : 0;
+  }
+  Table t = upload(metas, xs[0].device());
+  at::Tensor out = at::zeros({(int64_t)xs.size()}, xs[0].options().dtype(at::kFloat));
+  check(hb::launch_sumsq(t.metas, t.prefix, t.total_chunks, t.n, dt, out.data_ptr<float>(),
+                         at::cuda::getCurrentCUDAStream()), "sumsq launch");
+  return out;
+}
+
+// Normalise + stochastically round a batch of same-shape matrices into the two bf16 work layouts.
+void ns_prepare(const std::vector<at::Tensor>& srcs, int src_dt, int64_t R, int64_t C, const at::Tensor& sumsq_t, double eps,
+                at::Tensor same, int64_t ld_same, at::Tensor trans, int64_t ld_trans, uint64_t seed) {
+  c10::cuda::CUDAGuard guard(same.device());
+  std::vector<const void*> ptrs(srcs.size());
+  for (size_t i = 0; i < srcs.size(); ++i) ptrs[i] = srcs[i].data_ptr();
+  at::Tensor dev = at::empty({(int64_t)(ptrs.size() * sizeof(void*))}, same.options().dtype(at::kByte));
+  auto stream = at::cuda::getCurrentCUDAStream();
+  check(cudaMemcpyAsync(dev.data_ptr(), ptrs.data(), ptrs.size() * sizeof(void*), cudaMemcpyHostToDevice, stream),
+        "pointer upload");
+  check(hb::launch_ns_prepare((const void* const*)dev.data_ptr(), src_dt, (int)R, (int)C, (int)srcs.size(),
+                              sumsq_t.data_ptr<float>(), (float)eps, same.data_ptr(), ld_same, R * ld_same,
+                              trans.data_ptr(), ld_trans, C * ld_trans, seed, stream), "ns_prepare launch");
+}
+
+// D = A * B^T (bf16, K-major operands, batched) with the fused epilogues described in ns_gemm.h.
+void ns_gemm(const at::Tensor& A, int64_t lda, int64_t strideA, const at::Tensor& B, int64_t ldb, int64_t strideB,
+             int64_t M, int64_t N, int64_t K, int64_t batch, int mode, bool symmetric, const OptT& C, int64_t ldc,
+             int64_t strideC, const OptT& CT, int64_t ldct, int64_t strideCT, const OptT& F, int64_t ldf, int64_t strideF,
+             bool f_transposed, double f_scale, const OptT& S, int64_t lds, int64_t strideS, double ca, double cb,
+             double cc, const at::Tensor& status) {
+  c10::cuda::CUDAGuard guard(A.device());
+  hb::GemmParams P{};
+  P.M = (int)M; P.N = (int)N; P.K = (int)K; P.batch = (int)batch; P.mode = mode; P.symmetric = symmetric ? 1 : 0;
+  P.C = C.has_value() ? (__nv_bfloat16*)C->data_ptr() : nullptr; P.ldc = ldc; P.strideC = strideC;
+  P.CT = CT.has_value() ? (__nv_bfloat16*)CT->data_ptr() : nullptr; P.ldct = ldct; P.strideCT = strideCT;
+  P.F = F.has_value() ? F->data_ptr<float>() : nullptr; P.ldf = ldf; P.strideF = strideF;
+  P.f_transposed = f_transposed ? 1 : 0; P.f_scale = (float)f_scale;
+  P.S = S.has_value() ? (const __nv_bfloat16*)S->data_ptr() : nullptr; P.lds = lds; P.strideS = strideS;
+  P.ca = (float)ca; P.cb = (float)cb; P.cc = (float)cc;
+  P.status = status.data_ptr<int>();
+  check(hb::launch_ns_gemm(A.data_ptr(), lda, strideA, B.data_ptr(), ldb, strideB, P, at::cuda::getCurrentCUDAStream()),
+        "ns_gemm launch");
+}
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("fused_chain", &fused_chain);
+  m.def("sumsq", &sumsq);
+  m.def("ns_prepare", &ns_prepare);
+  m.def("ns_gemm", &ns_gemm);
+  m.def("chunk_elems", &hb::chain_chunk_elems);
+}

@@ -1,0 +1,228 @@
+// Multi-tensor fused optimizer chain: one launch executes, for every element of every tensor of a
+// param group,  [ECC/bf16/fp32 decode] -> [MARS] -> [momentum / second-moment rule] -> [caution] ->
+// [weight decay] -> [parameter write | update write] -> [stochastic-rounding / ECC encode].
+//
+// Replaces the per-tensor compiled regions of the reference (heavyball/utils.py:1842-2334 Adam family,
+// 736-776 momentum, 3616-3627 MARS, 2373-2406 parameter update, 3652-3658 caution).  Arithmetic is
+// restated from heavyball_b200/utils/first_order.py, which is also the test oracle.
+//
+// Work decomposition: tensors are cut into CHUNK-element chunks; block b owns chunk b and finds its
+// tensor by binary search in a prefix table.  All tensor addresses come from a device-resident table,
+// so the launch count is independent of the number of tensors.
+#include "common.cuh"
+#include "fused_chain.h"
+
+namespace hb {
+
+constexpr int kThreads = 256;
+constexpr int kChunk = 8192;  // elements per block
+
+__device__ inline float lerp_to(float s, float x, float beta) {  // s*beta' + x*(1-beta') in the oracle's order
+  float w = 1.0f - beta;
+  return s * (1.0f - w) + x * w;
+}
+
+template <bool kCountCaution>
+__global__ void __launch_bounds__(kThreads) fused_chain_kernel(const TensorMeta* __restrict__ metas,
+                                                              const int* __restrict__ chunk_prefix, ChainParams P) {
+  // ---- locate (tensor, chunk)
+  int lo = 0, hi = P.n_tensors;
+  const int b = blockIdx.x;
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (chunk_prefix[mid] <= b) lo = mid; else hi = mid;
+  }
+  const int t = lo;
+  const TensorMeta M = metas[t];
+  const int64_t base = (int64_t)(b - chunk_prefix[t]) * kChunk;
+  const bool vec_ok = M.vec_ok != 0;
+  const Philox rng(P.seed);
+
+  float cscale = 1.0f;
+  if (P.use_tensor_scale && M.scale != nullptr) cscale = *M.scale;
+  if (P.caution_apply && M.masked != nullptr) {
+    float n = (float)M.numel;
+    cscale *= n / fmaxf(n - (float)(*M.masked), 1.0f);
+  }
+  int masked_local = 0;
+
+#pragma unroll 2
+  for (int it = 0; it < kChunk / (kThreads * 4); ++it) {
+    const int64_t i = base + ((int64_t)it * kThreads + threadIdx.x) * 4;
+    if (i >= M.numel) break;
+    const int nv = (int)min((int64_t)4, M.numel - i);
+    const uint32_t ctr = (uint32_t)(i >> 2), ctr_hi = (uint32_t)(i >> 34);
+
+    F4 g = load4(M.g, nullptr, P.dt_g, i, nv, vec_ok);
+    F4 u = P.u_is_input ? load4(M.u, nullptr, P.dt_u, i, nv, vec_ok) : g;
+    F4 s0 = load4(M.s0, M.s0e, P.dt_s, i, nv, vec_ok);
+    F4 s1 = load4(M.s1, M.s1e, P.dt_s, i, nv, vec_ok);
+    F4 s2 = load4(M.s2, M.s2e, P.dt_s, i, nv, vec_ok);
+    F4 p = P.out_mode == kOutParam ? load4(M.p, M.pe, P.dt_p, i, nv, vec_ok) : F4{};
+    F4 out;
+
+    if (P.mars) {  // g <- lerp(g, g_prev, a); g_prev <- raw g
+      F4 old = load4(M.mars, M.marse, P.dt_s, i, nv, vec_ok);
+      F4 raw = u;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        u.v[k] = u.v[k] * (1.0f - P.mars_a) + old.v[k] * P.mars_a;
+        g.v[k] = u.v[k];
+      }
+      store4(M.mars, M.marse, P.dt_s, i, nv, vec_ok, raw, rng(ctr, ctr_hi ^ 0x40000000u, (uint32_t)t, 4u));
+    }
+
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float x = u.v[k], r;
+      switch (P.algo) {
+        case kAdam: {
+          s0.v[k] = lerp_to(s0.v[k], x, P.b1);
+          s1.v[k] = lerp_to(s1.v[k], x * x, P.b2);
+          r = s0.v[k] / fmaxf(sqrtf(s1.v[k]), P.eps);
+        } break;
+        case kLaProp: {
+          s1.v[k] = lerp_to(s1.v[k], x * x, P.b2);
+          s0.v[k] = lerp_to(s0.v[k], x / fmaxf(sqrtf(s1.v[k]), P.eps), P.b1);
+          r = s0.v[k];
+        } break;
+        case kAdopt: {
+          s0.v[k] = lerp_to(s0.v[k], x / fmaxf(sqrtf(s1.v[k]), P.eps), P.b1);
+          r = s0.v[k];
+          s1.v[k] = s1.v[k] * (1.0f - P.b3) + x * x * P.b3;  // b3 = 1 - debiased beta2 of the next step
+        } break;
+        case kAdemamix: {
+          s0.v[k] = lerp_to(s0.v[k], x, P.b1);
+          s2.v[k] = lerp_to(s2.v[k], x, P.b3);
+          s1.v[k] = lerp_to(s1.v[k], x * x, P.b2);
+          r = (s0.v[k] + s2.v[k] * P.alpha) / fmaxf(sqrtf(s1.v[k]), P.eps);
+        } break;
+        case kRmsprop: {
+          s1.v[k] = lerp_to(s1.v[k], x * x, P.b2);
+          r = x / fmaxf(sqrtf(s1.v[k]), P.eps);
+        } break;
+        case kUnscaledAdam: {
+          s1.v[k] = lerp_to(s1.v[k], x * x, P.b2);
+          float d = fmaxf(sqrtf(s1.v[k]), P.eps);
+          s0.v[k] = lerp_to(s0.v[k], x / d, P.b1);
+          r = s0.v[k] * d;
+        } break;
+        case kExpAvg: {
+          s0.v[k] = lerp_to(s0.v[k], x, P.b1);
+          r = s0.v[k];
+        } break;
+        case kNesterovEma: {
+          s0.v[k] = lerp_to(s0.v[k], x, P.b1);
+          r = x + s0.v[k];
+        } break;
+        case kHeavyball: {
+          s0.v[k] = s0.v[k] * P.b1 + x;
+          r = s0.v[k];
+        } break;
+        case kNesterovMom: {
+          s0.v[k] = s0.v[k] * P.b1 + x;
+          r = x + s0.v[k] * P.b1;
+        } break;
+        default:
+          r = x;
+      }
+      out.v[k] = r;
+    }
+
+    if (P.n_state >= 1) store4(M.s0, M.s0e, P.dt_s, i, nv, vec_ok, s0, rng(ctr, ctr_hi, (uint32_t)t, 0u));
+    if (P.n_state >= 2) store4(M.s1, M.s1e, P.dt_s, i, nv, vec_ok, s1, rng(ctr, ctr_hi, (uint32_t)t, 1u));
+    if (P.n_state >= 3) store4(M.s2, M.s2e, P.dt_s, i, nv, vec_ok, s2, rng(ctr, ctr_hi, (uint32_t)t, 2u));
+
+    if (kCountCaution) {  // phase one of caution: mask, count, park the masked update
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        bool disagree = (__float_as_uint(g.v[k]) ^ __float_as_uint(out.v[k])) >> 31;
+        if (k < nv && disagree) { out.v[k] = 0.f; ++masked_local; }
+      }
+      store4(M.u, nullptr, P.dt_u, i, nv, vec_ok, out, rng(ctr, ctr_hi, (uint32_t)t, 5u));
+      continue;
+    }
+    if (P.out_mode == kOutUpdate) {
+      store4(M.u, nullptr, P.dt_u, i, nv, vec_ok, out, rng(ctr, ctr_hi, (uint32_t)t, 5u));
+      continue;
+    }
+    // parameter epilogue: p <- p (1 - d lr) - lr u
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float uu = out.v[k] * cscale;
+      float d = P.wd;
+      if (P.cautious_wd && ((__float_as_uint(p.v[k]) ^ __float_as_uint(uu)) >> 31)) d = 0.f;
+      p.v[k] = p.v[k] * (1.0f - d * P.lr) + uu * -P.lr;
+    }
+    store4(M.p, M.pe, P.dt_p, i, nv, vec_ok, p, rng(ctr, ctr_hi, (uint32_t)t, 3u));
+  }
+
+  if (kCountCaution) {
+    __shared__ int warp_sums[kThreads / 32];
+    int v = masked_local;
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xFFFFFFFFu, v, o);
+    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int tot = 0;
+      for (int w = 0; w < kThreads / 32; ++w) tot += warp_sums[w];
+      if (tot) atomicAdd(M.masked, tot);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Segmented sum of squares: out[t] += sum(x_t^2).  One block per chunk, one atomic per block.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) sumsq_kernel(const TensorMeta* __restrict__ metas,
+                                                        const int* __restrict__ chunk_prefix, int n_tensors, int dt,
+                                                        float* __restrict__ out) {
+  int lo = 0, hi = n_tensors;
+  const int b = blockIdx.x;
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (chunk_prefix[mid] <= b) lo = mid; else hi = mid;
+  }
+  const TensorMeta M = metas[lo];
+  const int64_t base = (int64_t)(b - chunk_prefix[lo]) * kChunk;
+  float acc = 0.f;
+#pragma unroll 2
+  for (int it = 0; it < kChunk / (kThreads * 4); ++it) {
+    const int64_t i = base + ((int64_t)it * kThreads + threadIdx.x) * 4;
+    if (i >= M.numel) break;
+    const int nv = (int)min((int64_t)4, M.numel - i);
+    F4 x = load4(M.u, nullptr, dt, i, nv, M.vec_ok != 0);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc += x.v[k] * x.v[k];
+  }
+  __shared__ float warp_sums[kThreads / 32];
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xFFFFFFFFu, acc, o);
+  if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int w = 0; w < kThreads / 32; ++w) tot += warp_sums[w];
+    atomicAdd(out + lo, tot);
+  }
+}
+
+int chain_chunk_elems() { return kChunk; }
+
+cudaError_t launch_fused_chain(const TensorMeta* metas, const int* chunk_prefix, int total_chunks, const ChainParams& P,
+                               bool count_caution, cudaStream_t stream) {
+  if (total_chunks <= 0) return cudaSuccess;
+  if (count_caution)
+    fused_chain_kernel<true><<<total_chunks, kThreads, 0, stream>>>(metas, chunk_prefix, P);
+  else
+    fused_chain_kernel<false><<<total_chunks, kThreads, 0, stream>>>(metas, chunk_prefix, P);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_sumsq(const TensorMeta* metas, const int* chunk_prefix, int total_chunks, int n_tensors, int dt,
+                         float* out, cudaStream_t stream) {
+  if (total_chunks <= 0) return cudaSuccess;
+  sumsq_kernel<<<total_chunks, kThreads, 0, stream>>>(metas, chunk_prefix, n_tensors, dt, out);
+  return cudaGetLastError();
+}
+
+}  // namespace hb

@@ -1,0 +1,59 @@
+// Host-visible declarations for the multi-tensor element-wise kernels (fused_chain.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace hb {
+
+// One entry per tensor of the group.  Unused pointers are null.  `u` is the update buffer: an input
+// when ChainParams::u_is_input, an output for kOutUpdate / caution phase one.
+struct TensorMeta {
+  void* p;      // parameter (primary)
+  void* pe;     // parameter ECC residual
+  void* g;      // gradient
+  void* u;      // update buffer
+  void* s0;     // first state slot (exp_avg / momentum / exp_avg_fast)
+  void* s0e;
+  void* s1;     // second state slot (exp_avg_sq)
+  void* s1e;
+  void* s2;     // third state slot (exp_avg_slow)
+  void* s2e;
+  void* mars;   // previous gradient for MARS
+  void* marse;
+  float* scale; // optional per-tensor multiplier applied to the update
+  int* masked;  // caution: number of masked elements (written by phase one, read by phase two)
+  int64_t numel;
+  int32_t vec_ok;  // all buffers of this tensor are aligned for 4-wide access
+  int32_t pad;
+};
+
+enum Algo : int {
+  kIdentity = 0, kAdam, kLaProp, kAdopt, kAdemamix, kRmsprop, kUnscaledAdam, kExpAvg, kNesterovEma, kHeavyball,
+  kNesterovMom
+};
+enum OutMode : int { kOutParam = 0, kOutUpdate = 1 };
+
+struct ChainParams {
+  int n_tensors;
+  int algo;
+  int out_mode;
+  int n_state;       // how many of s0..s2 are live
+  int dt_p, dt_g, dt_u, dt_s;
+  int u_is_input;    // read the incoming update from `u` instead of from `g`
+  int mars;
+  int cautious_wd;
+  int caution_apply; // phase two: rescale by numel / (numel - masked)
+  int use_tensor_scale;
+  float lr, wd, eps;
+  float b1, b2, b3, alpha;  // already debiased / scheduled on the host
+  float mars_a;
+  uint64_t seed;
+};
+
+int chain_chunk_elems();
+cudaError_t launch_fused_chain(const TensorMeta* metas, const int* chunk_prefix, int total_chunks, const ChainParams& P,
+                               bool count_caution, cudaStream_t stream);
+cudaError_t launch_sumsq(const TensorMeta* metas, const int* chunk_prefix, int total_chunks, int n_tensors, int dt,
+                         float* out, cudaStream_t stream);
+
+}  // namespace hb

@@ -1,0 +1,373 @@
+// Newton–Schulz / Polar-Express building blocks for sm_100a.
+//
+// One polynomial step X <- (a I + b S + c S^2) X with S = X X^T (heavyball/utils.py:550-577, 605-631)
+// is executed as three batched bf16 GEMMs with fp32 accumulation in tensor memory:
+//     gram : S  = X  X^T                       (symmetric: upper-triangular tiles only, mirrored)
+//     poly : Y  = c S S + b S + a I            (symmetric; S is both operands and an epilogue input)
+//     apply: X' = Y X                          (also writes X'^T, the K-major operand of the next step)
+// All three are "TN" products D[M,N] = A[M,K] * B[N,K]^T with both operands K-major, so a single
+// kernel serves them; only the epilogue differs.  Keeping X^T alongside X is what makes the third
+// product K-major as well.
+//
+// Kernel structure (one 128x128 output tile per CTA, 192 threads, two CTAs resident per SM so one
+// CTA's epilogue overlaps the other's main loop):
+//   warp 0      : TMA producer  - cp.async.bulk.tensor (3-D maps, 128B swizzle) into a 3-stage ring
+//   warp 1      : MMA issuer    - tcgen05.mma.cta_group::1.kind::f16, 128x128x16 per instruction,
+//                                 accumulator = 128 TMEM columns; tcgen05.commit releases ring slots
+//   warps 2..5  : epilogue      - tcgen05.ld 32x32b from their TMEM lane quarter, fused scalar math,
+//                                 direct global stores (normal, mirrored / transposed, fp32 final)
+// Every mbarrier wait is bounded; on expiry the CTA raises a flag in global memory, drains what it
+// issued, frees its TMEM columns and returns, so a protocol bug cannot wedge the device.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+#include "ns_gemm.h"
+
+namespace hb {
+
+constexpr int BM = 128, BN = 128, BK = 64;
+constexpr int kStages = 3;
+constexpr int kTileBytes = BM * BK * 2;            // 16 KiB per operand tile
+constexpr int kStageBytes = 2 * kTileBytes;        // A + B
+constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + slack for 1 KiB alignment
+constexpr int kGemmThreads = 192;
+constexpr uint32_t kTmemCols = 128;
+constexpr uint32_t kSpinLimit = 1u << 18;          // bounded waits (each try_wait itself blocks briefly)
+
+// ------------------------------------------------------------------------------------------ PTX wrappers
+__device__ inline uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ inline void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ inline void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ inline bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Returns false if the wait expired or another role already aborted.
+__device__ inline bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ inline void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ inline void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols));
+}
+__device__ inline void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;"); }
+__device__ inline void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols));
+}
+__device__ inline void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ inline void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ inline void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ inline void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+__device__ inline void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ inline void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile, 128-byte swizzle: rows are 128 B apart inside an 8-row (1 KiB) group, groups
+// are 1 KiB apart (stride byte offset); the leading byte offset is unused for swizzled K-major tiles.
+__device__ inline uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);  // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                       // leading byte offset (ignored)
+  d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset
+  d |= (uint64_t)1 << 46;                       // descriptor version for sm_100
+  d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
+  return d;
+}
+// bf16 x bf16 -> fp32, both operands K-major, M = 128, N = 128.
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+// ------------------------------------------------------------------------------------------ kernel
+__global__ void __launch_bounds__(kGemmThreads, 2)
+ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kStages];
+  __shared__ __align__(8) uint64_t empty_bar[kStages];
+  __shared__ __align__(8) uint64_t accum_bar;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  // a previous CTA of this stream already gave up on a wait: do not pile more work on a broken pipeline
+  if (P.status != nullptr && *(volatile const int*)P.status != 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+
+  // ---- tile coordinates
+  const int tiles_m = (P.M + BM - 1) / BM, tiles_n = (P.N + BN - 1) / BN;
+  int tm, tn;
+  if (P.symmetric) {
+    int idx = blockIdx.x;
+    tm = 0;
+    while (idx >= tiles_m - tm) { idx -= tiles_m - tm; ++tm; }
+    tn = tm + idx;
+  } else {
+    tm = blockIdx.x / tiles_n;
+    tn = blockIdx.x % tiles_n;
+  }
+  const int batch = blockIdx.y;
+  const int num_kb = (P.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(&accum_bar, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) { tmem_alloc(&tmem_base_slot, kTmemCols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  int issued = 0;  // producer: k-blocks whose loads were issued
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % kStages, round = kb / kStages;
+        if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &abort_flag)) break;
+        mbar_expect_tx(&full_bar[s], kStageBytes);
+        uint8_t* a_dst = tiles + s * kStageBytes;
+        tma_load_3d(a_dst, &map_a, &full_bar[s], kb * BK, tm * BM, batch);
+        tma_load_3d(a_dst + kTileBytes, &map_b, &full_bar[s], kb * BK, tn * BN, batch);
+        issued = kb + 1;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % kStages, round = kb / kStages;
+        ok = mbar_wait(&full_bar[s], round & 1, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(tiles + s * kStageBytes);
+        const uint64_t a_desc = make_smem_desc(a_addr), b_desc = make_smem_desc(a_addr + kTileBytes);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k) {
+          // advancing 16 bf16 (32 B) along K inside the swizzle atom = +2 in 16-byte address units
+          tc_mma_bf16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, kInstrDesc, (kb | k) ? 1u : 0u);
+        }
+        tc_commit(&empty_bar[s]);
+      }
+      if (ok) tc_commit(&accum_bar);
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue warps
+    const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
+    const int row = tm * BM + quarter * 32 + lane;  // output row of this thread
+    const bool have = (num_kb == 0) || mbar_wait(&accum_bar, 0, &abort_flag);
+    tc_fence_after();
+    if (have) {
+      const int64_t b64 = batch;
+      for (int cb = 0; cb < BN / 32; ++cb) {
+        uint32_t acc[32];
+        if (num_kb > 0) {
+          tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cb * 32), acc);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[j] = 0u;
+        }
+        const int col0 = tn * BN + cb * 32;
+        if (row >= P.M) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]);
+
+        if (P.mode == kModePoly) {
+          const __nv_bfloat16* srow = P.S + b64 * P.strideS + (int64_t)row * P.lds + col0;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = col0 + j;
+            float s = (col < P.N) ? __bfloat162float(srow[j]) : 0.f;
+            v[j] = P.cc * v[j] + P.cb * s + ((col == row) ? P.ca : 0.f);
+          }
+        }
+        // bf16 outputs are rounded once so that the normal and the mirrored copy agree bit for bit
+        __nv_bfloat16 h[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) h[j] = __float2bfloat16_rn(v[j]);
+
+        if (P.C != nullptr) {
+          __nv_bfloat16* crow = P.C + b64 * P.strideC + (int64_t)row * P.ldc + col0;
+          if (col0 + 32 <= P.N && ((P.ldc & 7) == 0)) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) *(uint4*)(crow + q * 8) = *(const uint4*)(h + q * 8);
+          } else {
+            for (int j = 0; j < 32 && col0 + j < P.N; ++j) crow[j] = h[j];
+          }
+        }
+        const bool mirror = P.symmetric ? (tn != tm) : true;
+        if (P.CT != nullptr && mirror) {  // consecutive lanes hold consecutive rows: coalesced along CT rows
+          __nv_bfloat16* ct = P.CT + b64 * P.strideCT + row;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < P.N) ct[(int64_t)(col0 + j) * P.ldct] = h[j];
+        }
+        if (P.F != nullptr) {
+          float* f = P.F + b64 * P.strideF;
+          if (P.f_transposed) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < P.N) f[(int64_t)(col0 + j) * P.ldf + row] = __bfloat162float(h[j]) * P.f_scale;
+          } else {
+            float* frow = f + (int64_t)row * P.ldf + col0;
+            for (int j = 0; j < 32 && col0 + j < P.N; ++j) frow[j] = __bfloat162float(h[j]) * P.f_scale;
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+
+  // ---- teardown: the producer makes sure nothing it issued is still landing in shared memory
+  if (warp == 0 && lane == 0 && abort_flag) {
+    for (int kb = max(0, issued - kStages); kb < issued; ++kb) {
+      const int s = kb % kStages, round = kb / kStages;
+      for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+        if (mbar_try_wait(&full_bar[s], round & 1)) break;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && abort_flag && P.status != nullptr) atomicExch(P.status, 1);
+  if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
+}
+
+// ------------------------------------------------------------------------------------------ prologue
+// X = SR_bf16(G / max(||G||_F, eps)) written twice: in the working orientation (rows <= cols) and
+// transposed.  `sumsq[b]` holds ||G_b||_F^2.  Grid: (ceil(C/32), ceil(R/32), batch), block 32x8.
+__global__ void __launch_bounds__(256) ns_prepare_kernel(const void* const* __restrict__ srcs, int src_dt, int R, int C,
+                                                        const float* __restrict__ sumsq, float eps,
+                                                        __nv_bfloat16* __restrict__ same, int64_t ld_same,
+                                                        int64_t stride_same, __nv_bfloat16* __restrict__ trans,
+                                                        int64_t ld_trans, int64_t stride_trans, uint64_t seed) {
+  __shared__ uint16_t tile[32][33];
+  const int b = blockIdx.z;
+  const void* src = srcs[b];
+  const float inv = 1.0f / fmaxf(sqrtf(sumsq[b]), eps);
+  const Philox rng(seed);
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  for (int rr = threadIdx.y; rr < 32; rr += 8) {
+    const int r = blockIdx.y * 32 + rr;
+    uint16_t bits = 0;
+    if (r < R && c < C) {
+      const int64_t idx = (int64_t)r * C + c;
+      float x = src_dt == kF32 ? ((const float*)src)[idx] : bf16_bits_to_float(((const uint16_t*)src)[idx]);
+      uint4 rnd = rng((uint32_t)idx, (uint32_t)(idx >> 32), (uint32_t)b, 7u);
+      bits = sr_bf16_bits(x * inv, rnd.x);
+      same[(int64_t)b * stride_same + (int64_t)r * ld_same + c] = __ushort_as_bfloat16(bits);
+    }
+    tile[rr][threadIdx.x] = bits;
+  }
+  __syncthreads();
+  const int tr = blockIdx.y * 32 + threadIdx.x;  // source row handled by this lane on the way out
+  for (int cc = threadIdx.y; cc < 32; cc += 8) {
+    const int tc = blockIdx.x * 32 + cc;
+    if (tr < R && tc < C)
+      trans[(int64_t)b * stride_trans + (int64_t)tc * ld_trans + tr] = __ushort_as_bfloat16(tile[threadIdx.x][cc]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  }
+  return fn;
+}
+
+// bf16 tensor [batch, rows, cols] with leading dimension `ld` elements; box = 64 cols x 128 rows.
+static bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int64_t ld, int64_t batch_stride, int batch) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)batch_stride * 2};
+  cuuint32_t box[3] = {BK, BM, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+cudaError_t launch_ns_gemm(const void* A, int64_t lda, int64_t strideA, const void* B, int64_t ldb, int64_t strideB,
+                           const GemmParams& P, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(ns_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, A, P.M, P.K, lda, strideA, P.batch) || !make_map(&mb, B, P.N, P.K, ldb, strideB, P.batch))
+    return cudaErrorInvalidValue;
+  const int tiles_m = (P.M + BM - 1) / BM, tiles_n = (P.N + BN - 1) / BN;
+  const int tiles = P.symmetric ? tiles_m * (tiles_m + 1) / 2 : tiles_m * tiles_n;
+  dim3 grid(tiles, P.batch);
+  ns_gemm_kernel<<<grid, kGemmThreads, kSmemBytes, stream>>>(ma, mb, P);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ns_prepare(const void* const* srcs, int src_dt, int R, int C, int batch, const float* sumsq, float eps,
+                              void* same, int64_t ld_same, int64_t stride_same, void* trans, int64_t ld_trans,
+                              int64_t stride_trans, uint64_t seed, cudaStream_t stream) {
+  dim3 grid((C + 31) / 32, (R + 31) / 32, batch), block(32, 8);
+  ns_prepare_kernel<<<grid, block, 0, stream>>>(srcs, src_dt, R, C, sumsq, eps, (__nv_bfloat16*)same, ld_same,
+                                                stride_same, (__nv_bfloat16*)trans, ld_trans, stride_trans, seed);
+  return cudaGetLastError();
+}
+
+}  // namespace hb

@@ -1,0 +1,202 @@
+"""GPU numerics tests for the sm_100a kernels.  Each kernel is compared with a plain PyTorch fp32
+restatement of the same operation (the definitions in ``heavyball_b200.utils`` with lowering off)."""
+
+import copy
+
+import pytest
+import torch
+
+import heavyball_b200 as hb
+from heavyball_b200 import lowering, ops, utils
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _params(shapes, dtype=torch.float32, seed=0):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    return [torch.nn.Parameter(torch.randn(*s, device=DEV, generator=g, dtype=torch.float32).to(dtype)) for s in shapes]
+
+
+def _run(cls, kwargs, shapes, steps, lowered, pdtype=torch.float32, gdtype=None, seed=0):
+    torch.manual_seed(seed)
+    params = _params(shapes, pdtype, seed)
+    opt = cls(params, **kwargs)
+    gen = torch.Generator(device=DEV).manual_seed(seed + 1)
+    old = lowering.enabled
+    lowering.enabled = lowered
+    try:
+        for _ in range(steps):
+            for p in params:
+                g = torch.randn(p.shape, device=DEV, generator=gen, dtype=torch.float32) * 0.1
+                p.grad = g.to(gdtype or p.dtype)
+            opt.step()
+    finally:
+        lowering.enabled = old
+    return params, opt
+
+
+SHAPES = [(257,), (64, 33), (3, 5, 7), (8193,), (128, 256), (1,)]
+
+FIRST_ORDER = [
+    (hb.AdamW, {"lr": 1e-2, "weight_decay": 0.1}),
+    (hb.AdamW, {"lr": 1e-2, "caution": True}),
+    (hb.AdamW, {"lr": 1e-2, "mars": True, "cautious_weight_decay": True, "weight_decay": 0.1}),
+    (hb.AdamW, {"lr": 1e-2, "palm": True, "warmup_steps": 3}),
+    (hb.LaProp, {"lr": 1e-2}),
+    (hb.ADOPT, {"lr": 1e-2}),
+    (hb.AdEMAMix, {"lr": 1e-2, "alpha_warmup": 10, "beta3_warmup": 10}),
+    (hb.RMSprop, {"lr": 1e-2}),
+    (hb.UnscaledAdamW, {"lr": 1e-2}),
+    (hb.SGD, {"lr": 1e-2, "caution": True}),
+    (hb.AdamC, {"lr": 1e-2, "max_lr": 2e-2, "weight_decay": 0.1}),
+]
+
+
+@pytest.mark.parametrize("cls,kw", FIRST_ORDER, ids=lambda x: getattr(x, "__name__", str(x))[:40])
+def test_fused_chain_matches_pytorch_fp32(cls, kw):
+    ref, _ = _run(cls, kw, SHAPES, 6, lowered=False)
+    got, opt = _run(cls, kw, SHAPES, 6, lowered=True)
+    assert lowering._program(opt) is not None
+    for a, b in zip(ref, got):
+        torch.testing.assert_close(b.data, a.data, rtol=2e-5, atol=2e-6)
+
+
+def test_fused_chain_state_matches():
+    _, o1 = _run(hb.AdamW, {"lr": 1e-2}, SHAPES, 5, lowered=False)
+    _, o2 = _run(hb.AdamW, {"lr": 1e-2}, SHAPES, 5, lowered=True)
+    s1, s2 = o1.state_dict()["state"], o2.state_dict()["state"]
+    for k in s1:
+        for name, v in s1[k][0].items():
+            if isinstance(v, torch.Tensor) and v.is_floating_point():
+                torch.testing.assert_close(s2[k][0][name], v, rtol=2e-5, atol=1e-7)
+            elif name == "is_initialized":
+                assert s2[k][0][name] == v
+
+
+@pytest.mark.parametrize("kw", [{"storage_dtype": "bfloat16"}, {"ecc": "bf16+8"}, {"ecc": "bf16+16"}, {"ecc": "fp16+8"},
+                                {"ecc": "bf16+8", "param_ecc": "bf16+8"}], ids=str)
+def test_fused_chain_low_precision_storage(kw):
+    """Stochastic rounding / ECC encode use different random streams than PyTorch, so compare
+    statistically: results must agree to well within the storage format's noise."""
+    ref, _ = _run(hb.AdamW, {"lr": 1e-2}, SHAPES, 8, lowered=False)  # fp32 everything
+    low_ref, _ = _run(hb.AdamW, {"lr": 1e-2, **kw}, SHAPES, 8, lowered=False)
+    got, opt = _run(hb.AdamW, {"lr": 1e-2, **kw}, SHAPES, 8, lowered=True)
+    for r, a, b in zip(ref, low_ref, got):
+        err_ref = (a.data.float() - r.data).abs().mean().item()
+        err_got = (b.data.float() - r.data).abs().mean().item()
+        assert err_got <= 2.0 * err_ref + 1e-4, (kw, err_got, err_ref)
+    if "ecc" in kw:  # the decoded state must track the fp32 state closely (ULP / (2 smax) resolution)
+        _, o32 = _run(hb.AdamW, {"lr": 1e-2}, SHAPES, 8, lowered=True)
+        key = "update_by_adam_exp_avg_0"
+        for p32, pl in zip(o32.param_groups[0]["params"], opt.param_groups[0]["params"]):
+            st = opt.state[pl][0]
+            cfgecc = hb.chainable.ECCConfig(kw["ecc"])
+            dec = utils._ULPState(st[key + "::ecc"], cfgecc.smax).decode(st[key])
+            want = o32.state[p32][0][key]
+            # one encode resolves ulp / (2 smax); after eight noisy re-encodes of a decaying EMA the
+            # RMS error must still sit far below what the 16-bit primary alone could resolve (~ulp / 4)
+            ulp_rel = 2.0 ** (-7 if "bf16" in kw["ecc"] else -10)
+            rms_err = (dec - want).square().mean().sqrt().item()
+            rms_val = want.square().mean().sqrt().item()
+            assert rms_err <= 0.02 * ulp_rel * rms_val + 1e-9, (kw, rms_err, rms_val)
+
+
+def test_bf16_params_stochastic_rounding_is_unbiased():
+    shapes = [(4096,)]
+    acc = torch.zeros(4096, device=DEV)
+    base = None
+    n = 24
+    for seed in range(n):
+        torch.manual_seed(seed)
+        p = torch.nn.Parameter(torch.full((4096,), 1.0, device=DEV, dtype=torch.bfloat16))
+        opt = hb.SGD([p], lr=1e-3, beta=0.0)
+        for i in range(2):
+            p.grad = torch.full_like(p, 0.37)
+            opt.step()
+        acc += p.data.float()
+    mean = (acc / n).mean().item()
+    # exact: 1 - 2 * 1e-3 * 0.37 (first step runs in PyTorch, second in the kernel); bf16 spacing near 1 is 2^-7
+    assert abs(mean - (1 - 2 * 1e-3 * 0.37)) < 2e-4, mean
+
+
+# ----------------------------------------------------------------------------------------- Newton–Schulz
+
+
+def _ns_reference(G, coeffs, eps=1e-7):
+    x = G.float() / G.float().norm(dim=(-2, -1), keepdim=True).clamp(min=eps)
+    tall = G.shape[-2] > G.shape[-1]
+    if tall:
+        x = x.mT
+    for a, b, c in coeffs:
+        s = x @ x.mT
+        eye = torch.eye(s.shape[-1], device=G.device)
+        x = (a * eye + b * s + c * (s @ s)) @ x
+    return x.mT if tall else x
+
+
+@pytest.mark.parametrize("shape", [(128, 128), (768, 3072), (3072, 768), (200, 136), (96, 1000), (768, 768)], ids=str)
+@pytest.mark.parametrize("batch", [1, 3])
+def test_newton_schulz_kernel_vs_fp32(shape, batch):
+    torch.manual_seed(0)
+    mats = [torch.randn(*shape, device=DEV) for _ in range(batch)]
+    out = ops.newton_schulz_batched(mats, utils.NS5_COEFFS, out_scale=1.0)
+    torch.cuda.synchronize()
+    ops.check_status()
+    for m, o in zip(mats, out):
+        want = _ns_reference(m, utils.NS5_COEFFS)
+        rel = ((o - want).norm() / want.norm()).item()
+        assert rel < 4e-2, (shape, rel)  # bf16 operands through 15 chained GEMMs
+        sv, sv_want = torch.linalg.svdvals(o.float()), torch.linalg.svdvals(want)
+        assert sv.max().item() < 1.3, sv.max().item()
+        # wide matrices are well conditioned and must come out near-orthogonal; square Gaussian ones keep
+        # a tail of tiny singular values after five steps, in the kernel exactly as in fp32
+        assert abs(sv.median().item() - sv_want.median().item()) < 0.05
+
+
+def test_ns_gemm_modes_vs_matmul():
+    ext = ops.load()
+    torch.manual_seed(1)
+    B, m, n = 2, 256, 384
+    x = (torch.randn(B, m, n, device=DEV) / n**0.5).bfloat16()
+    xt = x.mT.contiguous()
+    S = torch.empty(B, m, m, device=DEV, dtype=torch.bfloat16)
+    Y = torch.empty_like(S)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ext.ns_gemm(x, n, m * n, x, n, m * n, m, m, n, B, ops.MODE_GRAM, True, S, m, m * m, S, m, m * m,
+                None, 0, 0, False, 1.0, None, 0, 0, 0.0, 0.0, 0.0, status)
+    want_S = x.float() @ x.float().mT
+    torch.testing.assert_close(S.float(), want_S, rtol=2e-2, atol=2e-2)
+    a, b, c = 3.0, -4.0, 2.0
+    ext.ns_gemm(S, m, m * m, S, m, m * m, m, m, m, B, ops.MODE_POLY, True, Y, m, m * m, Y, m, m * m,
+                None, 0, 0, False, 1.0, S, m, m * m, a, b, c, status)
+    Sf = S.float()
+    want_Y = c * (Sf @ Sf) + b * Sf + a * torch.eye(m, device=DEV)
+    torch.testing.assert_close(Y.float(), want_Y, rtol=3e-2, atol=3e-2)
+    nx, nxt = torch.empty_like(x), torch.empty_like(xt)
+    F = torch.empty(B, m, n, device=DEV)
+    ext.ns_gemm(Y, m, m * m, xt, m, n * m, m, n, m, B, ops.MODE_APPLY, False, nx, n, m * n, nxt, m, n * m,
+                F, n, m * n, False, 0.5, None, 0, 0, 0.0, 0.0, 0.0, status)
+    want_X = Y.float() @ x.float()
+    torch.testing.assert_close(nx.float(), want_X, rtol=3e-2, atol=3e-2)
+    assert torch.equal(nxt, nx.mT.contiguous())
+    torch.testing.assert_close(F, nx.float() * 0.5, rtol=0, atol=0)
+    assert int(status.item()) == 0
+
+
+def test_muon_lowered_matches_pytorch():
+    shapes = [(256, 512), (512, 256), (256, 512), (64,), (128, 128)]
+    ref, _ = _run(hb.Muon, {"lr": 0.02, "weight_decay": 0.01}, shapes, 4, lowered=False)
+    got, opt = _run(hb.Muon, {"lr": 0.02, "weight_decay": 0.01}, shapes, 4, lowered=True)
+    ops.check_status()
+    assert lowering._program(opt).kind == "orthogonal"
+    for a, b in zip(ref, got):
+        d0 = 4 * 0.02 * (max(1, a.shape[0] / a.shape[-1]) ** 0.5 if a.ndim > 1 else 1)
+        # both paths orthogonalise with bf16 operands and different rounding noise
+        assert ((a.data - b.data).norm() / (a.data.numel() ** 0.5)).item() < 0.05 * d0
+
+
+def test_graft_smoke():
+    import __graft_entry__ as entry
+
+    entry.smoke()

@@ -84,105 +84,131 @@ struct F4 {
   float v[4];
 };
 
+// All loops below have compile-time trip counts and constant indices so that the 4-element
+// temporaries live in registers (dynamic indexing would push them to local memory).
+__device__ inline void unpack_h4(const void* src, int n_valid, bool fast, uint16_t (&h)[4]) {
+  const uint16_t* hp = (const uint16_t*)src;
+  if (fast) {
+    uint2 t = *(const uint2*)hp;
+    h[0] = t.x & 0xFFFF; h[1] = t.x >> 16; h[2] = t.y & 0xFFFF; h[3] = t.y >> 16;
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) h[k] = (k < n_valid) ? hp[k] : (uint16_t)0;
+  }
+}
+
 __device__ inline F4 load4(const void* p, const void* c, int dt, int64_t i, int n_valid, bool vec_ok) {
   F4 r;
 #pragma unroll
   for (int k = 0; k < 4; ++k) r.v[k] = 0.f;
   if (dt == kNone || p == nullptr) return r;
+  const bool fast = vec_ok && n_valid == 4;
   if (dt == kF32) {
     const float* f = (const float*)p + i;
-    if (vec_ok && n_valid == 4) {
+    if (fast) {
       float4 t = *(const float4*)f;
       r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w;
     } else {
-      for (int k = 0; k < n_valid; ++k) r.v[k] = f[k];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (k < n_valid) r.v[k] = f[k];
     }
     return r;
   }
-  uint16_t h[4] = {0, 0, 0, 0};
-  const uint16_t* hp = (const uint16_t*)p + i;
-  if (vec_ok && n_valid == 4) {
-    uint2 t = *(const uint2*)hp;
-    h[0] = t.x & 0xFFFF; h[1] = t.x >> 16; h[2] = t.y & 0xFFFF; h[3] = t.y >> 16;
-  } else {
-    for (int k = 0; k < n_valid; ++k) h[k] = hp[k];
-  }
-  bool bf = is_bf16_like(dt);
+  uint16_t h[4];
+  unpack_h4((const uint16_t*)p + i, n_valid, fast, h);
+  const bool bf = is_bf16_like(dt);
   if (!is_ecc(dt)) {
 #pragma unroll
     for (int k = 0; k < 4; ++k) r.v[k] = bf ? bf16_bits_to_float(h[k]) : f16_bits_to_float(h[k]);
     return r;
   }
-  int corr[4] = {0, 0, 0, 0};
+  int corr[4];
   if (ecc_wide(dt)) {
-    const int16_t* cp = (const int16_t*)c + i;
-    for (int k = 0; k < n_valid; ++k) corr[k] = cp[k];
+    uint16_t w[4];
+    unpack_h4((const uint16_t*)c + i, n_valid, fast, w);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) corr[k] = (int)(int16_t)w[k];
   } else {
     const int8_t* cp = (const int8_t*)c + i;
-    if (vec_ok && n_valid == 4) {
+    if (fast) {
       uint32_t t = *(const uint32_t*)cp;
 #pragma unroll
       for (int k = 0; k < 4; ++k) corr[k] = (int)(int8_t)((t >> (8 * k)) & 0xFF);
     } else {
-      for (int k = 0; k < n_valid; ++k) corr[k] = cp[k];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) corr[k] = (k < n_valid) ? (int)cp[k] : 0;
     }
   }
-  float inv = ecc_wide(dt) ? (1.0f / 32767.0f) : (1.0f / 127.0f);
+  const float inv = ecc_wide(dt) ? (1.0f / 32767.0f) : (1.0f / 127.0f);
 #pragma unroll
   for (int k = 0; k < 4; ++k) r.v[k] = ecc_decode(h[k], corr[k], bf, inv);
   return r;
+}
+
+__device__ inline void pack_h4(void* dst, int n_valid, bool fast, const uint16_t (&h)[4]) {
+  uint16_t* hp = (uint16_t*)dst;
+  if (fast) {
+    uint2 t;
+    t.x = (uint32_t)h[0] | ((uint32_t)h[1] << 16);
+    t.y = (uint32_t)h[2] | ((uint32_t)h[3] << 16);
+    *(uint2*)hp = t;
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      if (k < n_valid) hp[k] = h[k];
+  }
 }
 
 // rnd supplies 4 x 32 random bits: low 16 bits feed bf16 stochastic rounding, the 24 high bits the
 // stochastic floor of the ECC residual.
 __device__ inline void store4(void* p, void* c, int dt, int64_t i, int n_valid, bool vec_ok, const F4& x, uint4 rnd) {
   if (dt == kNone || p == nullptr) return;
-  uint32_t rr[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+  const bool fast = vec_ok && n_valid == 4;
+  const uint32_t rr[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
   if (dt == kF32) {
     float* f = (float*)p + i;
-    if (vec_ok && n_valid == 4) {
+    if (fast) {
       *(float4*)f = make_float4(x.v[0], x.v[1], x.v[2], x.v[3]);
     } else {
-      for (int k = 0; k < n_valid; ++k) f[k] = x.v[k];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (k < n_valid) f[k] = x.v[k];
     }
     return;
   }
-  bool bf = is_bf16_like(dt);
+  const bool bf = is_bf16_like(dt);
   uint16_t h[4];
-  int corr[4];
   if (!is_ecc(dt)) {
 #pragma unroll
     for (int k = 0; k < 4; ++k) h[k] = bf ? sr_bf16_bits(x.v[k], rr[k]) : rne_f16_bits(x.v[k]);
-  } else {
-    float smax = ecc_wide(dt) ? 32767.0f : 127.0f;
+    pack_h4((uint16_t*)p + i, n_valid, fast, h);
+    return;
+  }
+  int corr[4];
+  const float smax = ecc_wide(dt) ? 32767.0f : 127.0f;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      h[k] = bf ? rne_bf16_bits(x.v[k]) : rne_f16_bits(x.v[k]);
-      corr[k] = ecc_residual(x.v[k], h[k], bf, smax, u32_to_unit(rr[k]));
-    }
+  for (int k = 0; k < 4; ++k) {
+    h[k] = bf ? rne_bf16_bits(x.v[k]) : rne_f16_bits(x.v[k]);
+    corr[k] = ecc_residual(x.v[k], h[k], bf, smax, u32_to_unit(rr[k]));
   }
-  uint16_t* hp = (uint16_t*)p + i;
-  if (vec_ok && n_valid == 4) {
-    uint2 t;
-    t.x = (uint32_t)h[0] | ((uint32_t)h[1] << 16);
-    t.y = (uint32_t)h[2] | ((uint32_t)h[3] << 16);
-    *(uint2*)hp = t;
-  } else {
-    for (int k = 0; k < n_valid; ++k) hp[k] = h[k];
-  }
-  if (!is_ecc(dt)) return;
+  pack_h4((uint16_t*)p + i, n_valid, fast, h);
   if (ecc_wide(dt)) {
-    int16_t* cp = (int16_t*)c + i;
-    for (int k = 0; k < n_valid; ++k) cp[k] = (int16_t)corr[k];
+    uint16_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) w[k] = (uint16_t)(int16_t)corr[k];
+    pack_h4((uint16_t*)c + i, n_valid, fast, w);
   } else {
     int8_t* cp = (int8_t*)c + i;
-    if (vec_ok && n_valid == 4) {
+    if (fast) {
       uint32_t t = 0;
 #pragma unroll
       for (int k = 0; k < 4; ++k) t |= ((uint32_t)(uint8_t)(int8_t)corr[k]) << (8 * k);
       *(uint32_t*)cp = t;
     } else {
-      for (int k = 0; k < n_valid; ++k) cp[k] = (int8_t)corr[k];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (k < n_valid) cp[k] = (int8_t)corr[k];
     }
   }
 }

@@ -17,13 +17,19 @@ namespace hb {
 constexpr int kThreads = 256;
 constexpr int kChunk = 8192;  // elements per block
 
+// Random bits are only generated for storage kinds that consume them (bf16 rounding, ECC residuals).
+__device__ inline uint4 draw(int dt, const Philox& rng, uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3) {
+  if (dt == kF32 || dt == kF16 || dt == kNone) return make_uint4(0u, 0u, 0u, 0u);
+  return rng(c0, c1, c2, c3);
+}
+
 __device__ inline float lerp_to(float s, float x, float beta) {  // s*beta' + x*(1-beta') in the oracle's order
   float w = 1.0f - beta;
   return s * (1.0f - w) + x * w;
 }
 
 template <bool kCountCaution>
-__global__ void __launch_bounds__(kThreads) fused_chain_kernel(const TensorMeta* __restrict__ metas,
+__global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMeta* __restrict__ metas,
                                                               const int* __restrict__ chunk_prefix, ChainParams P) {
   // ---- locate (tensor, chunk)
   int lo = 0, hi = P.n_tensors;
@@ -69,7 +75,7 @@ __global__ void __launch_bounds__(kThreads) fused_chain_kernel(const TensorMeta*
         u.v[k] = u.v[k] * (1.0f - P.mars_a) + old.v[k] * P.mars_a;
         g.v[k] = u.v[k];
       }
-      store4(M.mars, M.marse, P.dt_s, i, nv, vec_ok, raw, rng(ctr, ctr_hi ^ 0x40000000u, (uint32_t)t, 4u));
+      store4(M.mars, M.marse, P.dt_s, i, nv, vec_ok, raw, draw(P.dt_s, rng, ctr, ctr_hi ^ 0x40000000u, (uint32_t)t, 4u));
     }
 
 #pragma unroll
@@ -129,9 +135,9 @@ __global__ void __launch_bounds__(kThreads) fused_chain_kernel(const TensorMeta*
       out.v[k] = r;
     }
 
-    if (P.n_state >= 1) store4(M.s0, M.s0e, P.dt_s, i, nv, vec_ok, s0, rng(ctr, ctr_hi, (uint32_t)t, 0u));
-    if (P.n_state >= 2) store4(M.s1, M.s1e, P.dt_s, i, nv, vec_ok, s1, rng(ctr, ctr_hi, (uint32_t)t, 1u));
-    if (P.n_state >= 3) store4(M.s2, M.s2e, P.dt_s, i, nv, vec_ok, s2, rng(ctr, ctr_hi, (uint32_t)t, 2u));
+    if (P.n_state >= 1) store4(M.s0, M.s0e, P.dt_s, i, nv, vec_ok, s0, draw(P.dt_s, rng, ctr, ctr_hi, (uint32_t)t, 0u));
+    if (P.n_state >= 2) store4(M.s1, M.s1e, P.dt_s, i, nv, vec_ok, s1, draw(P.dt_s, rng, ctr, ctr_hi, (uint32_t)t, 1u));
+    if (P.n_state >= 3) store4(M.s2, M.s2e, P.dt_s, i, nv, vec_ok, s2, draw(P.dt_s, rng, ctr, ctr_hi, (uint32_t)t, 2u));
 
     if (kCountCaution) {  // phase one of caution: mask, count, park the masked update
 #pragma unroll
@@ -139,11 +145,11 @@ __global__ void __launch_bounds__(kThreads) fused_chain_kernel(const TensorMeta*
         bool disagree = (__float_as_uint(g.v[k]) ^ __float_as_uint(out.v[k])) >> 31;
         if (k < nv && disagree) { out.v[k] = 0.f; ++masked_local; }
       }
-      store4(M.u, nullptr, P.dt_u, i, nv, vec_ok, out, rng(ctr, ctr_hi, (uint32_t)t, 5u));
+      store4(M.u, nullptr, P.dt_u, i, nv, vec_ok, out, draw(P.dt_u, rng, ctr, ctr_hi, (uint32_t)t, 5u));
       continue;
     }
     if (P.out_mode == kOutUpdate) {
-      store4(M.u, nullptr, P.dt_u, i, nv, vec_ok, out, rng(ctr, ctr_hi, (uint32_t)t, 5u));
+      store4(M.u, nullptr, P.dt_u, i, nv, vec_ok, out, draw(P.dt_u, rng, ctr, ctr_hi, (uint32_t)t, 5u));
       continue;
     }
     // parameter epilogue: p <- p (1 - d lr) - lr u
@@ -154,7 +160,7 @@ __global__ void __launch_bounds__(kThreads) fused_chain_kernel(const TensorMeta*
       if (P.cautious_wd && ((__float_as_uint(p.v[k]) ^ __float_as_uint(uu)) >> 31)) d = 0.f;
       p.v[k] = p.v[k] * (1.0f - d * P.lr) + uu * -P.lr;
     }
-    store4(M.p, M.pe, P.dt_p, i, nv, vec_ok, p, rng(ctr, ctr_hi, (uint32_t)t, 3u));
+    store4(M.p, M.pe, P.dt_p, i, nv, vec_ok, p, draw(P.dt_p, rng, ctr, ctr_hi, (uint32_t)t, 3u));
   }
 
   if (kCountCaution) {

@@ -14,8 +14,10 @@
 //   warp 0      : TMA producer  - cp.async.bulk.tensor (3-D maps, 128B swizzle) into a 3-stage ring
 //   warp 1      : MMA issuer    - tcgen05.mma.cta_group::1.kind::f16, 128x128x16 per instruction,
 //                                 accumulator = 128 TMEM columns; tcgen05.commit releases ring slots
-//   warps 2..5  : epilogue      - tcgen05.ld 32x32b from their TMEM lane quarter, fused scalar math,
-//                                 direct global stores (normal, mirrored / transposed, fp32 final)
+//   warps 2..5  : epilogue      - tcgen05.ld 32x32b from their TMEM lane quarter, fused scalar math (the
+//                                 S tile of the polynomial arrives by TMA in a freed ring slot), bf16
+//                                 tile and its transpose staged in swizzled shared memory and written
+//                                 with cp.async.bulk.tensor stores; fp32 final output stored directly
 // Every mbarrier wait is bounded; on expiry the CTA raises a flag in global memory, drains what it
 // issued, frees its TMEM columns and returns, so a protocol bug cannot wedge the device.
 #include <cuda.h>
@@ -123,8 +125,18 @@ __device__ inline uint64_t make_smem_desc(uint32_t smem_addr) {
 constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
 // ------------------------------------------------------------------------------------------ kernel
+__device__ inline void tma_store_3d(const CUtensorMap* map, const void* src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+// byte offset of 16-byte chunk q of row r inside a [128 rows x 64 bf16] tile stored with the 128-byte
+// swizzle that TMA and the MMA descriptors use (tile base 1 KiB aligned)
+__device__ inline uint32_t swz(int r, int q) { return (uint32_t)(r * 128 + ((q ^ (r & 7)) << 4)); }
+
 __global__ void __launch_bounds__(kGemmThreads, 2)
-ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams P) {
+ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_ct, const GemmParams P) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kStages];
   __shared__ __align__(8) uint64_t empty_bar[kStages];
@@ -151,6 +163,13 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
   const int batch = blockIdx.y;
   const int num_kb = (P.K + BK - 1) / BK;
+  const bool poly = P.mode == kModePoly;
+  // after the main loop the ring is reused: slot sx receives the S tile (poly), the next two stage
+  // the output tile and its transpose for the bulk stores
+  const int sx = num_kb % kStages;
+  uint8_t* s_tile = tiles + sx * kStageBytes;
+  uint8_t* c_stage = tiles + ((sx + 1) % kStages) * kStageBytes;
+  uint8_t* ct_stage = tiles + ((sx + 2) % kStages) * kStageBytes;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -164,16 +183,22 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
 
-  int issued = 0;  // producer: k-blocks whose loads were issued
+  int issued = 0;  // producer: ring fills whose loads were issued
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
+      const int total = num_kb + (poly ? 1 : 0);
+      for (int kb = 0; kb < total; ++kb) {
         const int s = kb % kStages, round = kb / kStages;
         if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &abort_flag)) break;
         mbar_expect_tx(&full_bar[s], kStageBytes);
         uint8_t* a_dst = tiles + s * kStageBytes;
-        tma_load_3d(a_dst, &map_a, &full_bar[s], kb * BK, tm * BM, batch);
-        tma_load_3d(a_dst + kTileBytes, &map_b, &full_bar[s], kb * BK, tn * BN, batch);
+        if (kb < num_kb) {
+          tma_load_3d(a_dst, &map_a, &full_bar[s], kb * BK, tm * BM, batch);
+          tma_load_3d(a_dst + kTileBytes, &map_b, &full_bar[s], kb * BK, tn * BN, batch);
+        } else {  // S[tm-block, tn-block] for the polynomial epilogue, as two 64-column halves
+          tma_load_3d(a_dst, &map_a, &full_bar[s], tn * BN, tm * BM, batch);
+          tma_load_3d(a_dst + kTileBytes, &map_a, &full_bar[s], tn * BN + BK, tm * BM, batch);
+        }
         issued = kb + 1;
       }
     }
@@ -197,13 +222,18 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (ok) tc_commit(&accum_bar);
     }
   } else {
-    // ---------------------------------------------------------------- epilogue warps
-    const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
-    const int row = tm * BM + quarter * 32 + lane;  // output row of this thread
-    const bool have = (num_kb == 0) || mbar_wait(&accum_bar, 0, &abort_flag);
+    // ---------------------------------------------------------------- epilogue warps (128 threads)
+    const int quarter = warp & 3;            // TMEM lane quarter this warp may read
+    const int r = quarter * 32 + lane;       // row inside the tile
+    const int row = tm * BM + r;             // global output row
+    bool have = (num_kb == 0) || mbar_wait(&accum_bar, 0, &abort_flag);
+    if (have && poly) have = mbar_wait(&full_bar[sx], (num_kb / kStages) & 1, &abort_flag);
     tc_fence_after();
+    const bool mirror = P.symmetric ? (tn != tm) : true;
+    const bool want_c = P.C != nullptr, want_ct = P.CT != nullptr && mirror;
     if (have) {
       const int64_t b64 = batch;
+#pragma unroll 1
       for (int cb = 0; cb < BN / 32; ++cb) {
         uint32_t acc[32];
         if (num_kb > 0) {
@@ -213,56 +243,86 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 32; ++j) acc[j] = 0u;
         }
+        const int half = cb >> 1, q0 = (cb & 1) * 4;  // 64-column half of the tile, first 16-byte chunk in it
         const int col0 = tn * BN + cb * 32;
-        if (row >= P.M) continue;
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]);
 
-        if (P.mode == kModePoly) {
-          const __nv_bfloat16* srow = P.S + b64 * P.strideS + (int64_t)row * P.lds + col0;
+        if (poly) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int col = col0 + j;
-            float s = (col < P.N) ? __bfloat162float(srow[j]) : 0.f;
-            v[j] = P.cc * v[j] + P.cb * s + ((col == row) ? P.ca : 0.f);
+          for (int q = 0; q < 4; ++q) {
+            const uint4 sv = *(const uint4*)(s_tile + half * kTileBytes + swz(r, q0 + q));
+            const uint32_t w[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int j = q * 8 + e;
+              const float sval = bf16_bits_to_float((uint16_t)((w[e >> 1] >> ((e & 1) * 16)) & 0xFFFF));
+              v[j] = P.cc * v[j] + P.cb * sval + ((col0 + j == row) ? P.ca : 0.f);
+            }
           }
         }
-        // bf16 outputs are rounded once so that the normal and the mirrored copy agree bit for bit
-        __nv_bfloat16 h[32];
+        // rounded once, so that the tile and its mirrored / transposed copy agree bit for bit
+        uint16_t h[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) h[j] = __float2bfloat16_rn(v[j]);
+        for (int j = 0; j < 32; ++j) h[j] = rne_bf16_bits(v[j]);
 
-        if (P.C != nullptr) {
-          __nv_bfloat16* crow = P.C + b64 * P.strideC + (int64_t)row * P.ldc + col0;
-          if (col0 + 32 <= P.N && ((P.ldc & 7) == 0)) {
+        if (want_c) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) *(uint4*)(crow + q * 8) = *(const uint4*)(h + q * 8);
-          } else {
-            for (int j = 0; j < 32 && col0 + j < P.N; ++j) crow[j] = h[j];
+          for (int q = 0; q < 4; ++q) {
+            uint4 o;
+            o.x = (uint32_t)h[q * 8 + 0] | ((uint32_t)h[q * 8 + 1] << 16);
+            o.y = (uint32_t)h[q * 8 + 2] | ((uint32_t)h[q * 8 + 3] << 16);
+            o.z = (uint32_t)h[q * 8 + 4] | ((uint32_t)h[q * 8 + 5] << 16);
+            o.w = (uint32_t)h[q * 8 + 6] | ((uint32_t)h[q * 8 + 7] << 16);
+            *(uint4*)(c_stage + half * kTileBytes + swz(r, q0 + q)) = o;
           }
         }
-        const bool mirror = P.symmetric ? (tn != tm) : true;
-        if (P.CT != nullptr && mirror) {  // consecutive lanes hold consecutive rows: coalesced along CT rows
-          __nv_bfloat16* ct = P.CT + b64 * P.strideCT + row;
+        if (want_ct) {  // transposed tile: row = column of the accumulator, column = r
+          uint8_t* dst = ct_stage + (r >> 6) * kTileBytes + (r & 7) * 2;
+          const int qr = (r & 63) >> 3;
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (col0 + j < P.N) ct[(int64_t)(col0 + j) * P.ldct] = h[j];
+          for (int j = 0; j < 32; ++j) *(uint16_t*)(dst + swz(cb * 32 + j, qr)) = h[j];
         }
-        if (P.F != nullptr) {
+        if (P.F != nullptr && row < P.M) {
           float* f = P.F + b64 * P.strideF;
           if (P.f_transposed) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (col0 + j < P.N) f[(int64_t)(col0 + j) * P.ldf + row] = __bfloat162float(h[j]) * P.f_scale;
+              if (col0 + j < P.N) f[(int64_t)(col0 + j) * P.ldf + row] = bf16_bits_to_float(h[j]) * P.f_scale;
           } else {
             float* frow = f + (int64_t)row * P.ldf + col0;
-            for (int j = 0; j < 32 && col0 + j < P.N; ++j) frow[j] = __bfloat162float(h[j]) * P.f_scale;
+            if (col0 + 32 <= P.N && (P.ldf & 3) == 0 && (((uintptr_t)f) & 15) == 0) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                *(float4*)(frow + q * 4) =
+                    make_float4(bf16_bits_to_float(h[q * 4]) * P.f_scale, bf16_bits_to_float(h[q * 4 + 1]) * P.f_scale,
+                                bf16_bits_to_float(h[q * 4 + 2]) * P.f_scale, bf16_bits_to_float(h[q * 4 + 3]) * P.f_scale);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < P.N) frow[j] = bf16_bits_to_float(h[j]) * P.f_scale;
+            }
           }
         }
       }
     }
     tc_fence_before();
+    if (want_c || want_ct) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the bulk copy
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (have && warp == 2 && lane == 0) {
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          if (want_c && tn * BN + hh * BK < P.N)
+            tma_store_3d(&map_c, c_stage + hh * kTileBytes, tn * BN + hh * BK, tm * BM, batch);
+          if (want_ct && tm * BM + hh * BK < P.M)
+            tma_store_3d(&map_ct, ct_stage + hh * kTileBytes, tm * BM + hh * BK, tn * BN, batch);
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      }
+    }
   }
 
   // ---- teardown: the producer makes sure nothing it issued is still landing in shared memory
@@ -351,13 +411,17 @@ cudaError_t launch_ns_gemm(const void* A, int64_t lda, int64_t strideA, const vo
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  CUtensorMap ma, mb;
+  CUtensorMap ma, mb, mc, mct;
   if (!make_map(&ma, A, P.M, P.K, lda, strideA, P.batch) || !make_map(&mb, B, P.N, P.K, ldb, strideB, P.batch))
     return cudaErrorInvalidValue;
+  mc = ma;
+  mct = ma;  // placeholders when an output is absent (never dereferenced by the kernel then)
+  if (P.C != nullptr && !make_map(&mc, P.C, P.M, P.N, P.ldc, P.strideC, P.batch)) return cudaErrorInvalidValue;
+  if (P.CT != nullptr && !make_map(&mct, P.CT, P.N, P.M, P.ldct, P.strideCT, P.batch)) return cudaErrorInvalidValue;
   const int tiles_m = (P.M + BM - 1) / BM, tiles_n = (P.N + BN - 1) / BN;
   const int tiles = P.symmetric ? tiles_m * (tiles_m + 1) / 2 : tiles_m * tiles_n;
   dim3 grid(tiles, P.batch);
-  ns_gemm_kernel<<<grid, kGemmThreads, kSmemBytes, stream>>>(ma, mb, P);
+  ns_gemm_kernel<<<grid, kGemmThreads, kSmemBytes, stream>>>(ma, mb, mc, mct, P);
   return cudaGetLastError();
 }
 

@@ -86,7 +86,8 @@ def test_fused_chain_low_precision_storage(kw):
         err_ref = (a.data.float() - r.data).abs().mean().item()
         err_got = (b.data.float() - r.data).abs().mean().item()
         assert err_got <= 2.0 * err_ref + 1e-4, (kw, err_got, err_ref)
-    if "ecc" in kw:  # the decoded state must track the fp32 state closely (ULP / (2 smax) resolution)
+    if "ecc" in kw and "param_ecc" not in kw:  # (bf16 parameters get bf16 gradients here, a different input)
+        # the decoded state must track the fp32 state closely (ULP / (2 smax) resolution)
         _, o32 = _run(hb.AdamW, {"lr": 1e-2}, SHAPES, 8, lowered=True)
         key = "update_by_adam_exp_avg_0"
         for p32, pl in zip(o32.param_groups[0]["params"], opt.param_groups[0]["params"]):

@@ -159,6 +159,23 @@ def _weight_decay(rule_name, group):
     return group["weight_decay"]
 
 
+def _materialize_zero_state(tr: C.FunctionTransform, states, group, params):
+    """Allocates the (all-zero) state of a rule without running it; used when gradients must not be
+    consumed by the PyTorch path (peer data parallelism reduces them inside the kernels)."""
+    for depth, layer in enumerate(tr.layers):
+        if isinstance(layer, C.ZeroSlots):
+            if len(params) > 1:
+                layer._slab_init(states, group, params)
+            for st, p in zip(states, params):
+                layer.init(st, group, None, None, p)
+    for st in states:
+        _mark_initialized(tr, st)
+
+
+def _cut(t, seg):
+    return t if seg is None else t.view(-1)[seg[0] : seg[1]]
+
+
 def try_run(opt, states, group, grads, params) -> bool:
     if not enabled or not ops.available():
         return False
@@ -170,6 +187,13 @@ def try_run(opt, states, group, grads, params) -> bool:
     ecc_mode, pecc_mode = group.get("ecc"), group.get("param_ecc")
     if prog.kind == "orthogonal" and utils.zeroth_power_mode != "newtonschulz":
         return False
+    peer = getattr(opt, "_peer", None)
+    plan = peer.plan_for(group) if peer is not None else None
+    if plan is not None:  # state is created here: the PyTorch path would see unreduced gradients
+        if not _state_ready(prog.rule, states, False):
+            _materialize_zero_state(prog.rule, states, group, params)
+        if prog.mars is not None and not _state_ready(prog.mars, states, False):
+            _materialize_zero_state(prog.mars, states, group, params)
     if not _state_ready(prog.rule, states, bool(ecc_mode)):
         return False
     if prog.mars is not None and not _state_ready(prog.mars, states, bool(ecc_mode)):
@@ -199,7 +223,24 @@ def try_run(opt, states, group, grads, params) -> bool:
         if prog.ortho is not None:
             _mark_initialized(prog.ortho, st)
 
-    s0, s0e, s1, s1e, s2, s2e = _slots(prog.rule, states, names, bool(ecc_mode))
+    # ---- selection: everything (single process / replicated) or this rank's share (peer data parallelism)
+    peer_in, peer_out = {}, {}
+    if plan is not None:
+        by_id = {id(p): i for i, p in enumerate(params)}
+        group_pos = {id(p): j for j, p in enumerate(group["params"])}
+        pos_to_local = {group_pos[pid]: i for pid, i in by_id.items() if pid in group_pos}
+        sel = [(pos_to_local[j], seg) for j, seg in plan["sel"] if j in pos_to_local]
+        args = peer.peer_args()
+        peer_in = {"g_delta": args["g_delta"], "g_scale": args["g_scale"]}
+        peer_out = {"p_delta": args["p_delta"]}
+    else:
+        sel = [(i, None) for i in range(len(params))]
+    pick = lambda xs: [_cut(xs[i], seg) for i, seg in sel] if len(xs) else []  # noqa: E731
+    params_v, grads_v = pick(params), pick(grads)
+    sub_states = [states[i] for i, _ in sel]
+    s0, s0e, s1, s1e, s2, s2e = (
+        [_cut(t, seg) for t, (_, seg) in zip(lst, sel)] for lst in _slots(prog.rule, sub_states, names, bool(ecc_mode))
+    )
     base = dict(
         dt_g=ops.dtype_code(grads[0]), dt_s=ops.dtype_code(states[0][key0], ecc_mode),
         dt_p=ops.dtype_code(params[0], pecc_mode), n_state=len(names), algo=algo,
@@ -210,35 +251,37 @@ def try_run(opt, states, group, grads, params) -> bool:
         mkey = prog.mars._val_names["mars_old_grad"]
         gamma, beta1 = utils.get_beta1(group), group["mars_gamma"]  # argument order of the transform
         mars_kw = dict(
-            mars=[st[mkey] for st in states], marse=[st[mkey + "::ecc"] for st in states] if ecc_mode else [],
+            mars=[_cut(st[mkey], seg) for st, (_, seg) in zip(sub_states, sel)],
+            marse=[_cut(st[mkey + "::ecc"], seg) for st, (_, seg) in zip(sub_states, sel)] if ecc_mode else [],
             mars_a=-gamma * beta1 / (1 - beta1),
         )  # fmt: skip
-    pe = [st["param::ecc"] for st in states] if pecc_mode else []
+    pe = [_cut(st["param::ecc"], seg) for st, (_, seg) in zip(sub_states, sel)] if pecc_mode else []
     epilogue = dict(
         lr=group["lr"], wd=_weight_decay(rule_name, group), cautious_wd=int(bool(group.get("cautious_weight_decay", False)))
     )
     caution = bool(group["caution"])
-
     launch = ops.fused_chain
+    if not params_v:
+        return True  # this rank owns nothing in this group
 
     if prog.kind == "elementwise":
         if not caution:
-            launch(p=params, pe=pe, g=grads, s0=s0, s0e=s0e, s1=s1, s1e=s1e, s2=s2, s2e=s2e, out_mode=ops.OUT_PARAM,
-                   seed=_seed(opt, group, 0), **base, **epilogue, **mars_kw)  # fmt: skip
+            launch(p=params_v, pe=pe, g=grads_v, s0=s0, s0e=s0e, s1=s1, s1e=s1e, s2=s2, s2e=s2e, out_mode=ops.OUT_PARAM,
+                   seed=_seed(opt, group, 0), **base, **epilogue, **mars_kw, **peer_in, **peer_out)  # fmt: skip
             return True
-        scratch = _scratch(prog, params)
-        masked = torch.zeros(len(params), dtype=torch.int32, device=params[0].device)
-        launch(g=grads, u=scratch, s0=s0, s0e=s0e, s1=s1, s1e=s1e, s2=s2, s2e=s2e, masked=masked, count_caution=1,
+        scratch = _scratch(prog, params_v)
+        masked = torch.zeros(len(params_v), dtype=torch.int32, device=params[0].device)
+        launch(g=grads_v, u=scratch, s0=s0, s0e=s0e, s1=s1, s1e=s1e, s2=s2, s2e=s2e, masked=masked, count_caution=1,
                out_mode=ops.OUT_UPDATE, dt_u=ops.F32, seed=_seed(opt, group, 0), **base, **mars_kw)  # fmt: skip
-        ops.fused_chain(p=params, pe=pe, u=scratch, masked=masked, algo=ops.IDENTITY, u_is_input=1, caution_apply=1,
+        ops.fused_chain(p=params_v, pe=pe, u=scratch, masked=masked, algo=ops.IDENTITY, u_is_input=1, caution_apply=1,
                         out_mode=ops.OUT_PARAM, dt_u=ops.F32, dt_p=base["dt_p"], dt_g=ops.NONE, dt_s=ops.NONE,
                         seed=_seed(opt, group, 1), **epilogue)  # fmt: skip
         return True
 
     # ---- orthogonal program: momentum -> Newton–Schulz per shape bucket -> parameter update
-    scratch = _scratch(prog, params)
-    launch(g=grads, u=scratch, s0=s0, s0e=s0e, s1=s1, s1e=s1e, s2=s2, s2e=s2e, out_mode=ops.OUT_UPDATE, dt_u=ops.F32,
-           seed=_seed(opt, group, 0), **base, **mars_kw)  # fmt: skip
+    scratch = _scratch(prog, params_v)
+    launch(g=grads_v, u=scratch, s0=s0, s0e=s0e, s1=s1, s1e=s1e, s2=s2, s2e=s2e, out_mode=ops.OUT_UPDATE, dt_u=ops.F32,
+           seed=_seed(opt, group, 0), **base, **mars_kw, **peer_in)  # fmt: skip
     scale_mode = "scale"
     buckets = {}
     for i, u in enumerate(scratch):
@@ -257,18 +300,19 @@ def try_run(opt, states, group, grads, params) -> bool:
             seed=_seed(opt, group, 2 + len(final) + R),
         )
         for b, i in enumerate(idx):
-            final[i] = out[b].view(params[i].shape)
+            final[i] = out[b].view(params_v[i].shape)
     if caution:
-        masked = torch.zeros(len(params), dtype=torch.int32, device=params[0].device)
-        ops.fused_chain(g=grads, u=final, masked=masked, algo=ops.IDENTITY, u_is_input=1, count_caution=1,
+        masked = torch.zeros(len(params_v), dtype=torch.int32, device=params[0].device)
+        ops.fused_chain(g=grads_v, u=final, masked=masked, algo=ops.IDENTITY, u_is_input=1, count_caution=1,
                         out_mode=ops.OUT_UPDATE, dt_u=ops.F32, dt_g=base["dt_g"], dt_s=ops.NONE, dt_p=ops.NONE,
                         seed=_seed(opt, group, 1))  # fmt: skip
-        ops.fused_chain(p=params, pe=pe, u=final, masked=masked, algo=ops.IDENTITY, u_is_input=1, caution_apply=1,
+        ops.fused_chain(p=params_v, pe=pe, u=final, masked=masked, algo=ops.IDENTITY, u_is_input=1, caution_apply=1,
                         out_mode=ops.OUT_PARAM, dt_u=ops.F32, dt_p=base["dt_p"], dt_g=ops.NONE, dt_s=ops.NONE,
                         seed=_seed(opt, group, 3), **epilogue)  # fmt: skip
     else:
-        ops.fused_chain(p=params, pe=pe, u=final, algo=ops.IDENTITY, u_is_input=1, out_mode=ops.OUT_PARAM, dt_u=ops.F32,
-                        dt_p=base["dt_p"], dt_g=ops.NONE, dt_s=ops.NONE, seed=_seed(opt, group, 3), **epilogue)  # fmt: skip
+        ops.fused_chain(p=params_v, pe=pe, u=final, algo=ops.IDENTITY, u_is_input=1, out_mode=ops.OUT_PARAM, dt_u=ops.F32,
+                        dt_p=base["dt_p"], dt_g=ops.NONE, dt_s=ops.NONE, seed=_seed(opt, group, 3), **epilogue,
+                        **peer_out)  # fmt: skip
     return True
 
 

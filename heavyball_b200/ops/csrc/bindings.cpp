@@ -9,6 +9,7 @@
 
 #include "fused_chain.h"
 #include "ns_gemm.h"
+#include "peer_sync.h"
 
 namespace py = pybind11;
 using OptT = std::optional<at::Tensor>;
@@ -95,6 +96,19 @@ void fused_chain(const TList& p, const TList& pe, const TList& g, const TList& u
   P.lr = getf("lr"); P.wd = getf("wd"); P.eps = getf("eps");
   P.b1 = getf("b1"); P.b2 = getf("b2"); P.b3 = getf("b3"); P.alpha = getf("alpha"); P.mars_a = getf("mars_a");
   P.seed = cfg.contains("seed") ? cfg["seed"].cast<uint64_t>() : 0;
+  if (cfg.contains("g_delta")) {
+    auto d = cfg["g_delta"].cast<std::vector<int64_t>>();
+    TORCH_CHECK((int)d.size() <= hb::kMaxPeers, "too many gradient sources");
+    P.n_src = (int)d.size();
+    for (size_t i = 0; i < d.size(); ++i) P.g_delta[i] = d[i];
+    P.g_scale = getf("g_scale");
+  }
+  if (cfg.contains("p_delta")) {
+    auto d = cfg["p_delta"].cast<std::vector<int64_t>>();
+    TORCH_CHECK((int)d.size() <= hb::kMaxPeers, "too many parameter destinations");
+    P.n_dst = (int)d.size();
+    for (size_t i = 0; i < d.size(); ++i) P.p_delta[i] = d[i];
+  }
   check(hb::launch_fused_chain(t.metas, t.prefix, t.total_chunks, P, geti("count_caution") != 0,
                                at::cuda::getCurrentCUDAStream()), "fused_chain launch");
 }
@@ -152,7 +166,26 @@ void ns_gemm(const at::Tensor& A, int64_t lda, int64_t strideA, const at::Tensor
         "ns_gemm launch");
 }
 
+// Store `epoch` into slot[rank] of every peer's flag array (after a system-scope fence).
+void peer_signal(const std::vector<int64_t>& flag_ptrs, int slot, int rank, int epoch) {
+  hb::PeerPtrs ptrs{};
+  TORCH_CHECK((int)flag_ptrs.size() <= hb::kMaxWorld, "world size above kMaxWorld");
+  for (size_t i = 0; i < flag_ptrs.size(); ++i) ptrs.ptr[i] = (uint64_t)flag_ptrs[i];
+  check(hb::launch_peer_signal(ptrs, slot, rank, (int)flag_ptrs.size(), epoch, at::cuda::getCurrentCUDAStream()),
+        "peer_signal launch");
+}
+
+// Wait (bounded) until every rank has stored `epoch` into `slot` of this rank's flag array.
+void peer_wait(const at::Tensor& my_flags, int slot, int world, int epoch, double timeout_s, const at::Tensor& status) {
+  c10::cuda::CUDAGuard guard(my_flags.device());
+  check(hb::launch_peer_wait(my_flags.data_ptr<int>(), slot, world, epoch, timeout_s, status.data_ptr<int>(),
+                             at::cuda::getCurrentCUDAStream()), "peer_wait launch");
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("peer_signal", &peer_signal);
+  m.def("peer_wait", &peer_wait);
+  m.attr("MAX_WORLD") = hb::kMaxWorld;
   m.def("fused_chain", &fused_chain);
   m.def("sumsq", &sumsq);
   m.def("ns_prepare", &ns_prepare);

@@ -59,7 +59,20 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
     const int nv = (int)min((int64_t)4, M.numel - i);
     const uint32_t ctr = (uint32_t)(i >> 2), ctr_hi = (uint32_t)(i >> 34);
 
-    F4 g = load4(M.g, nullptr, P.dt_g, i, nv, vec_ok);
+    F4 g;
+    if (P.n_src > 0) {  // reduce the same element over every rank's gradient slab (peer loads over NVLink)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) g.v[k] = 0.f;
+      for (int r = 0; r < P.n_src; ++r) {
+        F4 part = load4((const char*)M.g + P.g_delta[r], nullptr, P.dt_g, i, nv, vec_ok);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) g.v[k] += part.v[k];
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) g.v[k] *= P.g_scale;
+    } else {
+      g = load4(M.g, nullptr, P.dt_g, i, nv, vec_ok);
+    }
     F4 u = P.u_is_input ? load4(M.u, nullptr, P.dt_u, i, nv, vec_ok) : g;
     F4 s0 = load4(M.s0, M.s0e, P.dt_s, i, nv, vec_ok);
     F4 s1 = load4(M.s1, M.s1e, P.dt_s, i, nv, vec_ok);
@@ -160,7 +173,13 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
       if (P.cautious_wd && ((__float_as_uint(p.v[k]) ^ __float_as_uint(uu)) >> 31)) d = 0.f;
       p.v[k] = p.v[k] * (1.0f - d * P.lr) + uu * -P.lr;
     }
-    store4(M.p, M.pe, P.dt_p, i, nv, vec_ok, p, draw(P.dt_p, rng, ctr, ctr_hi, (uint32_t)t, 3u));
+    const uint4 prnd = draw(P.dt_p, rng, ctr, ctr_hi, (uint32_t)t, 3u);
+    if (P.n_dst > 0) {  // single writer per element: every replica receives bit-identical parameters
+      for (int r = 0; r < P.n_dst; ++r)
+        store4((char*)M.p + P.p_delta[r], nullptr, P.dt_p, i, nv, vec_ok, p, prnd);
+    } else {
+      store4(M.p, M.pe, P.dt_p, i, nv, vec_ok, p, prnd);
+    }
   }
 
   if (kCountCaution) {

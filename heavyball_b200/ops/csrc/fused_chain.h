@@ -27,6 +27,8 @@ struct TensorMeta {
   int32_t pad;
 };
 
+constexpr int kMaxPeers = 16;
+
 enum Algo : int {
   kIdentity = 0, kAdam, kLaProp, kAdopt, kAdemamix, kRmsprop, kUnscaledAdam, kExpAvg, kNesterovEma, kHeavyball,
   kNesterovMom
@@ -48,6 +50,13 @@ struct ChainParams {
   float b1, b2, b3, alpha;  // already debiased / scheduled on the host
   float mars_a;
   uint64_t seed;
+  // Peer-memory data parallelism (n_src / n_dst = 0 turns it off).  Gradient = g_scale * sum over sources
+  // of the same element in every source's gradient slab; parameters (and their ECC residuals) are
+  // written to every destination.  Deltas are byte offsets from this rank's address to the peer's.
+  int n_src, n_dst;
+  float g_scale;
+  int64_t g_delta[kMaxPeers];
+  int64_t p_delta[kMaxPeers];
 };
 
 int chain_chunk_elems();

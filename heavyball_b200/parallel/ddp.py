@@ -1,22 +1,248 @@
-"""Data-parallel training wrapper.
+"""Data-parallel training without a separate gradient all-reduce.
 
-``wrap(model, optimizer)`` returns a module whose backward leaves identical, averaged gradients on
-every rank before ``optimizer.step()`` runs.  The collective path is NCCL (``DistributedDataParallel``
-with gradient-as-bucket-view); see ``heavyball_b200.parallel.fused_reduce`` for the peer-memory
-kernels that replace it on NVLink-connected GPUs.
+``wrap(model, optimizer)`` re-homes parameters and gradients into two slabs of *symmetric memory*
+(every rank can address every other rank's copy over NVLink) and partitions the optimizer work:
+
+* element-wise chains (AdamW, LaProp, ...): the flat element range of a param group is cut into
+  ``world`` contiguous pieces; rank ``r`` updates piece ``r`` only.  Its kernel reads the matching
+  gradient elements from **all** ranks' slabs (peer loads, summed and scaled by ``1/world`` in
+  registers - the reduce-scatter), runs the transform chain on its state, and stores the new
+  parameter elements into **all** ranks' slabs (peer stores - the all-gather).  One kernel does the
+  collective and the optimizer math; no reduced gradient is ever materialised.
+* orthogonalising chains (Muon, MuonLaProp): every matrix has one owner rank (balanced by estimated
+  Newton–Schulz cost).  The owner's momentum kernel reduces the gradient from all ranks on load, the
+  batched Newton–Schulz runs on the owned matrices only, and the parameter-update kernel stores the
+  result into all ranks' slabs.
+* anything else (SOAP, PSGD, user chains): gradients of those parameters are averaged with a
+  ``torch.distributed`` all-reduce and the optimizer runs replicated, as the reference does under
+  ``DistributedDataParallel`` (``examples/ddp_training.py:47-52`` there).
+
+Synchronisation is two epoch-flag barriers per step in symmetric memory (``ops/csrc/peer_sync.cu``):
+"my gradients are complete" before the first optimizer kernel and "I am done reading your gradients and
+writing your parameters" after the last.  Waits are bounded; :meth:`PeerContext.check` raises if a peer
+never arrived.  Every parameter element has exactly one writer, so replicas stay bit-identical.
+
+``mode="nccl"`` (or a single process) falls back to ``DistributedDataParallel``.
 """
 
 from __future__ import annotations
 
+import math
+from typing import Dict, List, Optional, Tuple
+
 import torch
 import torch.distributed as dist
 
+from .. import ops
 
-def wrap(model: torch.nn.Module, optimizer=None, **kwargs):
-    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+
+def _world():
+    return dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+
+
+def _inner_optimizers(optimizer):
+    return list(getattr(optimizer, "optimizers", None) or [optimizer])
+
+
+class PeerContext:
+    """Owns the symmetric slabs, the work partition and the step barriers."""
+
+    def __init__(self, model: torch.nn.Module, optimizer, group=None, timeout_s: float = 10.0):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from .. import lowering
+
+        self.group = group or dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        if self.world > ops.load().MAX_WORLD:
+            raise ValueError(f"peer data parallelism supports at most {ops.load().MAX_WORLD} ranks per node")
+        self.timeout_s = timeout_s
+        self.epoch = 0
+        self.optimizer = optimizer
+
+        params = [p for p in model.parameters() if p.requires_grad]
+        if not params:
+            raise ValueError("model has no trainable parameters")
+        self.device = params[0].device
+        self.dtype = params[0].dtype
+        if any(p.dtype != self.dtype or p.device != self.device for p in params):
+            raise ValueError("peer data parallelism needs all parameters on one device with one dtype")
+        self.params = params
+
+        # ---- slab layout: 16-element aligned segments, identical on every rank
+        self.offsets: Dict[int, int] = {}
+        total = 0
+        for p in params:
+            self.offsets[id(p)] = total
+            total += (p.numel() + 15) // 16 * 16
+        self.total = total
+        try:
+            symm_mem.enable_symm_mem_for_group(self.group.group_name)
+        except Exception:  # noqa: BLE001  (newer releases enable it implicitly)
+            pass
+        self.P = symm_mem.empty(total, dtype=self.dtype, device=self.device)
+        self.G = symm_mem.empty(total, dtype=self.dtype, device=self.device)
+        self.flags = symm_mem.empty(4 * ops.load().MAX_WORLD, dtype=torch.int32, device=self.device)
+        self.P.zero_()
+        self.G.zero_()
+        self.flags.zero_()
+        self._hdl = [symm_mem.rendezvous(t, self.group) for t in (self.P, self.G, self.flags)]
+        self.p_ptrs, self.g_ptrs, self.f_ptrs = (list(h.buffer_ptrs) for h in self._hdl)
+        self.p_delta = [ptr - self.p_ptrs[self.rank] for ptr in self.p_ptrs]
+        self.g_delta = [ptr - self.g_ptrs[self.rank] for ptr in self.g_ptrs]
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+        with torch.no_grad():
+            for p in params:
+                view = self.P[self.offsets[id(p)] : self.offsets[id(p)] + p.numel()].view(p.shape)
+                view.copy_(p.data)
+                p.data = view
+            dist.broadcast(self.P, src=dist.get_global_rank(self.group, 0), group=self.group)
+        self._attach_grads()
+
+        # ---- which parameters are handled by peer kernels, which by the all-reduce fallback
+        self.plans: Dict[int, dict] = {}
+        self.fallback_ranges: List[Tuple[int, int]] = []
+        for opt in _inner_optimizers(optimizer):
+            prog = lowering._program(opt) if hasattr(opt, "_lowered") else None
+            supported = prog is not None and opt.__class__.__name__ != "ADOPT"
+            for g in getattr(opt, "param_groups", []):
+                if g.get("ecc") or g.get("param_ecc") or g.get("caution"):
+                    supported_here = False
+                else:
+                    supported_here = supported and all(id(p) in self.offsets for p in g["params"])
+                if supported_here:
+                    self.plans[id(g)] = self._plan_group(g, prog.kind)
+                else:
+                    for p in g["params"]:
+                        if id(p) in self.offsets:
+                            self.fallback_ranges.append((self.offsets[id(p)], p.numel()))
+            if hasattr(opt, "consume_grad"):
+                opt.consume_grad = False  # gradients live in the slab for the whole run
+            opt._peer = self
+        self.fallback_ranges = self._coalesce(self.fallback_ranges)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+
+    # ------------------------------------------------------------------ layout helpers
+    def _attach_grads(self):
+        for p in self.params:
+            off = self.offsets[id(p)]
+            p.grad = self.G[off : off + p.numel()].view(p.shape)
+
+    @staticmethod
+    def _coalesce(ranges):
+        out = []
+        for off, n in sorted(ranges):
+            if out and out[-1][0] + out[-1][1] + 15 >= off:
+                out[-1] = (out[-1][0], off + n - out[-1][0])
+            else:
+                out.append((off, n))
+        return out
+
+    def _plan_group(self, group, kind):
+        ps = group["params"]
+        if kind == "orthogonal":  # whole tensors, balanced by matrix-stage cost
+            loads, owned = [0.0] * self.world, []
+            order = sorted(range(len(ps)), key=lambda i: -ps[i].numel())
+            owner_of = {}
+            for i in order:
+                p = ps[i]
+                cost = p.numel() * (min(p.shape[0], p[0].numel()) if p.ndim >= 2 else 1)
+                r = min(range(self.world), key=loads.__getitem__)
+                loads[r] += cost
+                owner_of[i] = r
+            owned = [(i, None) for i in range(len(ps)) if owner_of[i] == self.rank]
+            return {"kind": kind, "sel": owned}
+        # flat element partition
+        starts, total = [], 0
+        for p in ps:
+            starts.append(total)
+            total += p.numel()
+        lo = total * self.rank // self.world
+        hi = total * (self.rank + 1) // self.world
+        sel = []
+        for i, p in enumerate(ps):
+            a = max(lo, starts[i]) - starts[i]
+            b = min(hi, starts[i] + p.numel()) - starts[i]
+            # keep segment starts 16-byte aligned relative to the tensor: boundaries move down to a multiple of 8
+            a = a // 8 * 8 if a > 0 else 0
+            b = b // 8 * 8 if b < p.numel() else p.numel()
+            if b > a:
+                sel.append((i, (a, b)))
+        return {"kind": kind, "sel": sel}
+
+    # ------------------------------------------------------------------ step protocol
+    def _barrier(self, slot):
+        ext = ops.load()
+        ext.peer_signal(self.f_ptrs, slot, self.rank, self.epoch)
+        ext.peer_wait(self.flags, slot, self.world, self.epoch, self.timeout_s, self.status)
+        ops.launch_counter.count += 2
+
+    def begin_step(self):
+        """After backward: publish "my gradients are complete" and wait for every peer's."""
+        self.epoch += 1
+        self._barrier(0)
+        for off, n in self.fallback_ranges:
+            dist.all_reduce(self.G[off : off + n], op=dist.ReduceOp.AVG, group=self.group)
+
+    def end_step(self):
+        """After the last optimizer kernel: wait until every peer has finished reading this rank's
+        gradients and writing this rank's parameters, then clear the gradient slab."""
+        self._barrier(1)
+        self.G.zero_()
+        self._attach_grads()
+
+    def check(self):
+        """Host-synchronising health check: raises if a bounded wait expired."""
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            raise RuntimeError(f"peer barrier timed out waiting for rank {code - 2} (epoch {self.epoch})")
+
+    def plan_for(self, group) -> Optional[dict]:
+        return self.plans.get(id(group))
+
+    def peer_args(self):
+        return {"g_delta": self.g_delta, "g_scale": 1.0 / self.world, "p_delta": self.p_delta}
+
+
+class _PeerModule(torch.nn.Module):
+    """Thin module wrapper; all the work happens in the optimizer step."""
+
+    def __init__(self, module, ctx: PeerContext):
+        super().__init__()
+        self.module = module
+        self.peer = ctx
+
+    def forward(self, *args, **kwargs):
+        return self.module(*args, **kwargs)
+
+
+def wrap(model: torch.nn.Module, optimizer=None, mode: str = "peer", **kwargs):
+    """Prepare ``model`` (and ``optimizer``) for data-parallel training on the ranks of the default
+    process group.  ``mode="peer"`` (default on CUDA with an optimizer from this package) uses the
+    symmetric-memory scheme described in the module docstring; ``mode="nccl"`` uses
+    ``DistributedDataParallel``."""
+    if _world() == 1:
         return model
+    cuda = next(model.parameters()).is_cuda
+    if mode == "peer" and cuda and optimizer is not None and ops.available():
+        ctx = PeerContext(model, optimizer, **kwargs)
+        real_step = optimizer.step
+
+        def step(closure=None):
+            ctx.begin_step()
+            try:
+                return real_step(closure)
+            finally:
+                ctx.end_step()
+
+        optimizer.step = step
+        optimizer.zero_grad = lambda set_to_none=True: None  # the slab is cleared by end_step
+        return _PeerModule(model, ctx)
     from torch.nn.parallel import DistributedDataParallel
 
-    device_ids = [torch.cuda.current_device()] if next(model.parameters()).is_cuda else None
+    kwargs.pop("timeout_s", None)
     kwargs.setdefault("gradient_as_bucket_view", True)
-    return DistributedDataParallel(model, device_ids=device_ids, **kwargs)
+    return DistributedDataParallel(model, device_ids=[torch.cuda.current_device()] if cuda else None, **kwargs)

@@ -1,0 +1,71 @@
+"""Worker for the multi-GPU data-parallel test (launched by ``torch.distributed.run``).
+
+Trains a small GPT for a few steps on rank-specific data twice: with the peer-memory scheme and with
+``DistributedDataParallel`` + replicated optimizer.  Checks that (a) replicas are bit-identical under the
+peer scheme, (b) both schemes agree to rounding noise, (c) no bounded wait expired.
+"""
+
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import heavyball_b200 as hb  # noqa: E402
+from heavyball_b200.models import GPT, GPTConfig, split_param_groups  # noqa: E402
+from heavyball_b200.parallel import ddp  # noqa: E402
+
+
+def run(mode, steps, rank, world, device):
+    torch.manual_seed(0)
+    model = GPT(GPTConfig(n_layer=2, n_head=4, d_model=256, vocab_size=512, seq_len=64)).to(device)
+    mats, rest = split_param_groups(model)
+    opt = hb.SplitOpt([
+        {"params": mats, "optimizer": hb.Muon, "lr": 0.02, "weight_decay": 0.01},
+        {"params": rest, "optimizer": hb.AdamW, "lr": 3e-3},
+    ])
+    wrapped = ddp.wrap(model, opt, mode=mode)
+    gen = torch.Generator().manual_seed(100 + rank)
+    losses = []
+    for _ in range(steps):
+        tokens = torch.randint(0, 512, (4, 65), generator=gen).to(device)
+        loss = wrapped(tokens[:, :-1], tokens[:, 1:])
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        losses.append(loss.detach())
+    if hasattr(wrapped, "peer"):
+        wrapped.peer.check()
+    hb.ops.check_status()
+    flat = torch.cat([p.detach().flatten().float() for p in model.parameters()])
+    return flat, torch.stack(losses)
+
+
+def main():
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=device)
+    steps = 4
+    peer_flat, peer_loss = run("peer", steps, rank, world, device)
+    nccl_flat, nccl_loss = run("nccl", steps, rank, world, device)
+
+    gathered = [torch.empty_like(peer_flat) for _ in range(world)]
+    dist.all_gather(gathered, peer_flat)
+    identical = all(torch.equal(gathered[0], g) for g in gathered)
+    diff = (peer_flat - nccl_flat).abs().max().item()
+    scale = nccl_flat.abs().max().item()
+    rms = ((peer_flat - nccl_flat).square().mean().sqrt() / nccl_flat.square().mean().sqrt()).item()
+    if rank == 0:
+        print(f"RESULT identical={identical} max_abs_diff={diff:.3e} max_abs={scale:.3e} rel_rms={rms:.3e} "
+              f"loss_peer={peer_loss.tolist()} loss_nccl={nccl_loss.tolist()}")
+    ok = identical and rms < 2e-2
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if ok else 1)
+
+
+if __name__ == "__main__":
+    main()

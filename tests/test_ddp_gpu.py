@@ -1,0 +1,23 @@
+"""Multi-GPU test of the peer-memory data-parallel step (needs two CUDA devices on one node)."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_data_parallel_matches_ddp():
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ddp_worker.py")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    proc = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+         "--master-port", "29541", worker],
+        capture_output=True, text=True, timeout=600, env=env,
+    )  # fmt: skip
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert "identical=True" in proc.stdout, proc.stdout[-2000:]

@@ -39,6 +39,7 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="gpt2-small", choices=sorted(CONFIGS))
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end phase")
+    ap.add_argument("--ddp-mode", default="peer", choices=["peer", "nccl"], help="gradient path of the 'ours' arm")
     return ap.parse_args()
 
 
@@ -160,7 +161,7 @@ def main():
         if args.impl == "ours":
             from heavyball_b200.parallel import ddp as hb_ddp
 
-            train_model = hb_ddp.wrap(model, opt)
+            train_model = hb_ddp.wrap(model, opt, mode=args.ddp_mode)
         else:
             from torch.nn.parallel import DistributedDataParallel
 
@@ -257,6 +258,8 @@ def main():
         from heavyball_b200 import ops
 
         ops.check_status()
+        if hasattr(train_model, "peer"):
+            train_model.peer.check()
     if rank == 0:
         value = B * T * world / (step_ms * 1e-3)
         out = {
@@ -276,6 +279,7 @@ def main():
             "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
             "config": {
                 "model": args.config, "global_batch": B * world, "seq_len": T, "parallelism": f"dp{world}",
+                "gradient_path": (args.ddp_mode if (args.impl == "ours" and world > 1) else ("nccl-ddp" if world > 1 else "none")),
                 "optimizer": "SplitOpt(Muon lr=0.02 NS5 on 2-D block weights, AdamW lr=3e-4 on the rest)",
                 "precision": "bf16 autocast, fp32 master weights and optimizer state",
                 "l2": "per-step working set (activations, 124M fp32 params + state) exceeds the 126 MB L2",

@@ -21,3 +21,17 @@ def test_peer_data_parallel_matches_ddp():
     )  # fmt: skip
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert "identical=True" in proc.stdout, proc.stdout[-2000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("name,width,tol", [("AdamW", 64, 1e-5), ("Muon", 64, 3e-2), ("SOAP", 63, 3e-2), ("PSGDKron", 64, 3e-2)])
+def test_real_fsdp_matches_single_process(name, width, tol):
+    """``FullyShardedDataParallel(use_orig_params=True)`` + owner repartitioning vs an un-sharded run."""
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "fsdp_worker.py")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    proc = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+         "--master-port", "29543", worker, name, str(width), "2", "3", str(tol), "norm"],
+        capture_output=True, text=True, timeout=600, env=env,
+    )  # fmt: skip
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]

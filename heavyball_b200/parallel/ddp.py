@@ -76,10 +76,14 @@ class PeerContext:
             self.offsets[id(p)] = total
             total += (p.numel() + 15) // 16 * 16
         self.total = total
-        try:
-            symm_mem.enable_symm_mem_for_group(self.group.group_name)
-        except Exception:  # noqa: BLE001  (newer releases enable it implicitly)
-            pass
+        import warnings
+
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            try:  # required by older releases, a deprecated no-op in newer ones
+                symm_mem.enable_symm_mem_for_group(self.group.group_name)
+            except Exception:  # noqa: BLE001
+                pass
         self.P = symm_mem.empty(total, dtype=self.dtype, device=self.device)
         self.G = symm_mem.empty(total, dtype=self.dtype, device=self.device)
         self.flags = symm_mem.empty(4 * ops.load().MAX_WORLD, dtype=torch.int32, device=self.device)

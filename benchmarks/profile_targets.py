@@ -27,19 +27,31 @@ def opt_step_gpt2(steps=3):
         {"params": rest, "optimizer": hb.AdamW, "lr": 3e-4},
     ])
     grads = [torch.randn_like(p) * 0.01 for p in m.parameters()]
-    for _ in range(steps + 1):  # first step initialises state through the PyTorch path
+
+    def one_step():
         for p, g in zip(m.parameters(), grads):
             p.grad = g
         opt.step()
+
+    one_step()  # the first step initialises state through the PyTorch path
+    one_step()
     torch.cuda.synchronize()
+    torch.cuda.profiler.start()  # with `ncu --profile-from-start off` only the steady-state steps are captured
+    for _ in range(steps):
+        one_step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
     ops.check_status()
 
 
 def ns_small():
     mats = [torch.randn(1024, 4096, device="cuda") for _ in range(8)]
-    for _ in range(2):
-        out = ops.newton_schulz_batched(mats, utils.NS5_COEFFS)
+    out = ops.newton_schulz_batched(mats, utils.NS5_COEFFS)
     torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    out = ops.newton_schulz_batched(mats, utils.NS5_COEFFS)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
     ops.check_status()
     print(float(out.abs().mean()))
 
@@ -49,9 +61,13 @@ def adam_small():
     opt = hb.AdamW(params, lr=1e-3, consume_grad=False)
     for p in params:
         p.grad = torch.randn_like(p)
-    for _ in range(4):
+    for _ in range(3):
         opt.step()
     torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    opt.step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
 
 
 if __name__ == "__main__":

@@ -280,27 +280,47 @@ def try_run(opt, states, group, grads, params) -> bool:
 
     # ---- orthogonal program: momentum -> Newton–Schulz per shape bucket -> parameter update
     scratch = _scratch(prog, params_v)
+    dev = params[0].device
+    sq = torch.zeros(len(scratch), dtype=torch.float32, device=dev)  # squared norms, accumulated by the momentum kernel
     launch(g=grads_v, u=scratch, s0=s0, s0e=s0e, s1=s1, s1e=s1e, s2=s2, s2e=s2e, out_mode=ops.OUT_UPDATE, dt_u=ops.F32,
-           seed=_seed(opt, group, 0), **base, **mars_kw, **peer_in)  # fmt: skip
+           scale=sq, accum_sumsq=1, seed=_seed(opt, group, 0), **base, **mars_kw, **peer_in)  # fmt: skip
     scale_mode = "scale"
     buckets = {}
     for i, u in enumerate(scratch):
         if u.ndim >= 2:
             buckets.setdefault((u.shape[0], u[0].numel()), []).append(i)
     final = list(scratch)
-    for (R, Cc), idx in buckets.items():
+    # shape buckets are independent chains of small launches: run them on side streams so they share the GPU
+    main = torch.cuda.current_stream(dev)
+    streams = prog.workspace.get("streams")
+    if streams is None:
+        streams = prog.workspace["streams"] = [torch.cuda.Stream(device=dev) for _ in range(4)]
+    ready = torch.cuda.Event()
+    ready.record(main)
+    used = []
+    for k, ((R, Cc), idx) in enumerate(buckets.items()):
         if not ops.ns_supported(R, Cc):
             for i in idx:
                 flat = scratch[i].view(R, Cc)
                 utils.inplace_orthogonal_(flat, out=flat, scale_mode=scale_mode)
             continue
-        out = _bucket_out(prog, (R, Cc, len(idx)), params[0].device)
-        ops.newton_schulz_batched(
-            [scratch[i].view(R, Cc) for i in idx], utils.NS5_COEFFS, out=out, out_scale=max(1, R / Cc) ** 0.5,
-            seed=_seed(opt, group, 2 + len(final) + R),
-        )
+        out = _bucket_out(prog, (R, Cc, len(idx)), dev)
+        sel_idx = prog.workspace.get(("idx", R, Cc, tuple(idx)))
+        if sel_idx is None:
+            sel_idx = prog.workspace[("idx", R, Cc, tuple(idx))] = torch.tensor(idx, dtype=torch.long, device=dev)
+        side = streams[k % len(streams)] if len(buckets) > 1 else main
+        if side is not main:
+            side.wait_event(ready)
+            used.append(side)
+        with torch.cuda.stream(side):
+            ops.newton_schulz_batched(
+                [scratch[i].view(R, Cc) for i in idx], utils.NS5_COEFFS, out=out, out_scale=max(1, R / Cc) ** 0.5,
+                seed=_seed(opt, group, 2 + len(final) + R), sumsq=sq.index_select(0, sel_idx),
+            )
         for b, i in enumerate(idx):
             final[i] = out[b].view(params_v[i].shape)
+    for side in used:
+        main.wait_stream(side)
     if caution:
         masked = torch.zeros(len(params_v), dtype=torch.int32, device=params[0].device)
         ops.fused_chain(g=grads_v, u=final, masked=masked, algo=ops.IDENTITY, u_is_input=1, count_caution=1,

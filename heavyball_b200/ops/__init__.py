@@ -190,9 +190,10 @@ def ns_supported(R: int, C: int) -> bool:
 
 
 def newton_schulz_batched(mats: Sequence[torch.Tensor], coeffs, out: Optional[torch.Tensor] = None, out_scale=1.0,
-                          eps: float = 1e-7, seed: Optional[int] = None) -> torch.Tensor:  # fmt: skip
+                          eps: float = 1e-7, seed: Optional[int] = None, sumsq: Optional[torch.Tensor] = None) -> torch.Tensor:  # fmt: skip
     """Orthogonalises a list of same-shape ``(R, C)`` fp32 / bf16 matrices; returns fp32 ``(B, R, C)``
-    holding ``out_scale * polar_factor``.  ``coeffs`` is a sequence of ``(a, b, c)`` per step."""
+    holding ``out_scale * polar_factor``.  ``coeffs`` is a sequence of ``(a, b, c)`` per step.  ``sumsq``
+    (fp32, one squared Frobenius norm per matrix) skips the reduction pass when the caller already has it."""
     ext = load()
     B = len(mats)
     R, C = mats[0].shape
@@ -208,14 +209,18 @@ def newton_schulz_batched(mats: Sequence[torch.Tensor], coeffs, out: Optional[to
         out = torch.empty(B, R, C, dtype=torch.float32, device=dev)
     if seed is None:
         seed = int(torch.randint(0, 2**62, (1,)).item())
-    norms = ext.sumsq([t.contiguous() for t in mats], dtype_code(mats[0]))
     srcs = [t.contiguous() for t in mats]
+    if sumsq is None:
+        norms = ext.sumsq(srcs, dtype_code(mats[0]))
+        launch_counter.count += 1
+    else:
+        norms = sumsq.contiguous()
     if R <= C:
         ext.ns_prepare(srcs, dtype_code(mats[0]), R, C, norms, eps, X[0], ldx, XT[0], ldxt, seed)
     else:  # work on the transpose so that the Gram matrix is the small one
         ext.ns_prepare(srcs, dtype_code(mats[0]), R, C, norms, eps, XT[0], ldxt, X[0], ldx, seed)
     status = _status(dev)
-    launch_counter.count += 2 + 3 * len(coeffs)
+    launch_counter.count += 1 + 3 * len(coeffs)
     cur = 0
     for step, (a, b, c) in enumerate(coeffs):
         last = step == len(coeffs) - 1

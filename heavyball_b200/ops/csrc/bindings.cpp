@@ -93,6 +93,7 @@ void fused_chain(const TList& p, const TList& pe, const TList& g, const TList& u
   P.dt_p = geti("dt_p"); P.dt_g = geti("dt_g"); P.dt_u = geti("dt_u"); P.dt_s = geti("dt_s");
   P.u_is_input = geti("u_is_input"); P.mars = geti("mars"); P.cautious_wd = geti("cautious_wd");
   P.caution_apply = geti("caution_apply"); P.use_tensor_scale = geti("use_tensor_scale");
+  P.accum_sumsq = geti("accum_sumsq");
   P.lr = getf("lr"); P.wd = getf("wd"); P.eps = getf("eps");
   P.b1 = getf("b1"); P.b2 = getf("b2"); P.b3 = getf("b3"); P.alpha = getf("alpha"); P.mars_a = getf("mars_a");
   P.seed = cfg.contains("seed") ? cfg["seed"].cast<uint64_t>() : 0;

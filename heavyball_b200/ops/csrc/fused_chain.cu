@@ -51,6 +51,7 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
     cscale *= n / fmaxf(n - (float)(*M.masked), 1.0f);
   }
   int masked_local = 0;
+  float sumsq_local = 0.f;
 
 #pragma unroll 2
   for (int it = 0; it < kChunk / (kThreads * 4); ++it) {
@@ -163,6 +164,11 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
     }
     if (P.out_mode == kOutUpdate) {
       store4(M.u, nullptr, P.dt_u, i, nv, vec_ok, out, draw(P.dt_u, rng, ctr, ctr_hi, (uint32_t)t, 5u));
+      if (P.accum_sumsq) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (k < nv) sumsq_local += out.v[k] * out.v[k];
+      }
       continue;
     }
     // parameter epilogue: p <- p (1 - d lr) - lr u
@@ -182,6 +188,18 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
     }
   }
 
+  if (P.accum_sumsq && M.scale != nullptr) {  // per-tensor squared norm of the update just written (feeds Newton–Schulz)
+    __shared__ float warp_sq[kThreads / 32];
+    float v = sumsq_local;
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xFFFFFFFFu, v, o);
+    if ((threadIdx.x & 31) == 0) warp_sq[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float tot = 0.f;
+      for (int w = 0; w < kThreads / 32; ++w) tot += warp_sq[w];
+      atomicAdd(M.scale, tot);
+    }
+  }
   if (kCountCaution) {
     __shared__ int warp_sums[kThreads / 32];
     int v = masked_local;

@@ -46,6 +46,7 @@ struct ChainParams {
   int cautious_wd;
   int caution_apply; // phase two: rescale by numel / (numel - masked)
   int use_tensor_scale;
+  int accum_sumsq;   // kOutUpdate: add sum(update^2) of every tensor into its `scale` slot
   float lr, wd, eps;
   float b1, b2, b3, alpha;  // already debiased / scheduled on the host
   float mars_a;

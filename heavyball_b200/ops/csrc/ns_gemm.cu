@@ -339,37 +339,76 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ------------------------------------------------------------------------------------------ prologue
-// X = SR_bf16(G / max(||G||_F, eps)) written twice: in the working orientation (rows <= cols) and
-// transposed.  `sumsq[b]` holds ||G_b||_F^2.  Grid: (ceil(C/32), ceil(R/32), batch), block 32x8.
+// X = SR_bf16(G / max(||G||_F, eps)) written twice: in the source orientation and transposed (one of the
+// two is the K-major operand X, the other X^T).  `sumsq[b]` holds ||G_b||_F^2.
+// One block handles a 64 x 64 tile: 256 threads as 16 column-groups (4 columns each) x 16 rows, four row
+// passes.  Loads are 16 B (fp32) / 8 B (bf16), both outputs are written with 8-byte stores; the
+// transpose goes through shared memory.  Grid: (ceil(C/64), ceil(R/64), batch).
 __global__ void __launch_bounds__(256) ns_prepare_kernel(const void* const* __restrict__ srcs, int src_dt, int R, int C,
                                                         const float* __restrict__ sumsq, float eps,
                                                         __nv_bfloat16* __restrict__ same, int64_t ld_same,
                                                         int64_t stride_same, __nv_bfloat16* __restrict__ trans,
                                                         int64_t ld_trans, int64_t stride_trans, uint64_t seed) {
-  __shared__ uint16_t tile[32][33];
+  __shared__ uint16_t tile[64][66];
   const int b = blockIdx.z;
   const void* src = srcs[b];
   const float inv = 1.0f / fmaxf(sqrtf(sumsq[b]), eps);
   const Philox rng(seed);
-  const int c = blockIdx.x * 32 + threadIdx.x;
-  for (int rr = threadIdx.y; rr < 32; rr += 8) {
-    const int r = blockIdx.y * 32 + rr;
-    uint16_t bits = 0;
-    if (r < R && c < C) {
-      const int64_t idx = (int64_t)r * C + c;
-      float x = src_dt == kF32 ? ((const float*)src)[idx] : bf16_bits_to_float(((const uint16_t*)src)[idx]);
-      uint4 rnd = rng((uint32_t)idx, (uint32_t)(idx >> 32), (uint32_t)b, 7u);
-      bits = sr_bf16_bits(x * inv, rnd.x);
-      same[(int64_t)b * stride_same + (int64_t)r * ld_same + c] = __ushort_as_bfloat16(bits);
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int c0 = blockIdx.x * 64 + tx * 4;
+  const bool vec = (C & 3) == 0 && (((uintptr_t)src) & 15) == 0;
+  uint16_t* same_b = (uint16_t*)same + (int64_t)b * stride_same;
+  uint16_t* trans_b = (uint16_t*)trans + (int64_t)b * stride_trans;
+#pragma unroll
+  for (int pass = 0; pass < 4; ++pass) {
+    const int rl = ty + 16 * pass, r = blockIdx.y * 64 + rl;
+    float x[4] = {0.f, 0.f, 0.f, 0.f};
+    if (r < R && c0 < C) {
+      const int64_t idx = (int64_t)r * C + c0;
+      if (vec) {
+        if (src_dt == kF32) {
+          const float4 t = *(const float4*)((const float*)src + idx);
+          x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w;
+        } else {
+          const uint2 t = *(const uint2*)((const uint16_t*)src + idx);
+          x[0] = bf16_bits_to_float(t.x & 0xFFFF); x[1] = bf16_bits_to_float(t.x >> 16);
+          x[2] = bf16_bits_to_float(t.y & 0xFFFF); x[3] = bf16_bits_to_float(t.y >> 16);
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (c0 + k < C)
+            x[k] = src_dt == kF32 ? ((const float*)src)[idx + k] : bf16_bits_to_float(((const uint16_t*)src)[idx + k]);
+      }
     }
-    tile[rr][threadIdx.x] = bits;
+    uint16_t h[4] = {0, 0, 0, 0};
+    if (r < R && c0 < C) {
+      const int64_t idx = (int64_t)r * C + c0;
+      const uint4 rnd = rng((uint32_t)idx, (uint32_t)(idx >> 32), (uint32_t)b, 7u);
+      const uint32_t rr[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (c0 + k < C) h[k] = sr_bf16_bits(x[k] * inv, rr[k]);
+      uint2 o;
+      o.x = (uint32_t)h[0] | ((uint32_t)h[1] << 16);
+      o.y = (uint32_t)h[2] | ((uint32_t)h[3] << 16);
+      *(uint2*)(same_b + (int64_t)r * ld_same + c0) = o;  // columns past C land in the row padding (ld is a multiple of 8)
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) tile[rl][tx * 4 + k] = h[k];
   }
   __syncthreads();
-  const int tr = blockIdx.y * 32 + threadIdx.x;  // source row handled by this lane on the way out
-  for (int cc = threadIdx.y; cc < 32; cc += 8) {
-    const int tc = blockIdx.x * 32 + cc;
-    if (tr < R && tc < C)
-      trans[(int64_t)b * stride_trans + (int64_t)tc * ld_trans + tr] = __ushort_as_bfloat16(tile[threadIdx.x][cc]);
+  // transposed output: this thread owns source rows r0..r0+3 (consecutive in the output row) of four source columns
+  const int r0 = blockIdx.y * 64 + tx * 4;
+#pragma unroll
+  for (int pass = 0; pass < 4; ++pass) {
+    const int cl = ty + 16 * pass, c = blockIdx.x * 64 + cl;
+    if (c < C && r0 < R) {
+      uint2 o;
+      o.x = (uint32_t)tile[tx * 4 + 0][cl] | ((uint32_t)tile[tx * 4 + 1][cl] << 16);
+      o.y = (uint32_t)tile[tx * 4 + 2][cl] | ((uint32_t)tile[tx * 4 + 3][cl] << 16);
+      *(uint2*)(trans_b + (int64_t)c * ld_trans + r0) = o;
+    }
   }
 }
 
@@ -428,7 +467,7 @@ cudaError_t launch_ns_gemm(const void* A, int64_t lda, int64_t strideA, const vo
 cudaError_t launch_ns_prepare(const void* const* srcs, int src_dt, int R, int C, int batch, const float* sumsq, float eps,
                               void* same, int64_t ld_same, int64_t stride_same, void* trans, int64_t ld_trans,
                               int64_t stride_trans, uint64_t seed, cudaStream_t stream) {
-  dim3 grid((C + 31) / 32, (R + 31) / 32, batch), block(32, 8);
+  dim3 grid((C + 63) / 64, (R + 63) / 64, batch), block(256);
   ns_prepare_kernel<<<grid, block, 0, stream>>>(srcs, src_dt, R, C, sumsq, eps, (__nv_bfloat16*)same, ld_same,
                                                 stride_same, (__nv_bfloat16*)trans, ld_trans, stride_trans, seed);
   return cudaGetLastError();

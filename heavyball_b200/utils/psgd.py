@@ -388,6 +388,37 @@ def casted_einsum(expr: str, *args: Tensor) -> Tensor:
     return compiled_einsum(expr, *[promote(a) for a in args]).to(args[-1].dtype)
 
 
+def _kron_apply(g: Tensor, factors, twice: bool) -> Tensor:
+    """Applies one Kronecker factor per non-slot mode of ``g``: ``Q_i g`` (``twice=False``) or
+    ``Q_i^T Q_i g`` (``twice=True``); 2-D factors are diagonals, 1-D ones per-slot scalars.
+
+    Equivalent to the multi-operand einsums of :func:`cached_precond_grad_expr` /
+    :func:`precond_grad_expr`, but contracted one mode at a time starting from ``g``: a left-to-right
+    einsum over ``(Q_1, Q_2, ..., g)`` would first form the outer product of the factors
+    (``slots x d1^2 x d2^2`` elements) unless an external contraction-path optimiser is installed."""
+    out = g
+    for i, q in enumerate(factors):
+        dim = i + 1
+        if q.ndim == 3:
+            moved = out.movedim(dim, -1)
+            lead = moved.shape
+            flat = moved.reshape(lead[0], -1, lead[-1])
+            flat = flat @ q.mT
+            if twice:
+                flat = flat @ q
+            out = flat.reshape(*lead[:-1], flat.shape[-1]).movedim(-1, dim)
+        else:
+            scale = q * q if twice else q
+            if q.ndim == 2 and out.ndim > 1:
+                shape = [q.shape[0]] + [1] * (out.ndim - 1)
+                shape[dim] = -1
+                scale = scale.view(shape)
+            elif out.ndim > 1:
+                scale = scale.view(-1, *([1] * (out.ndim - 1)))
+            out = out * scale
+    return out
+
+
 # ---------------------------------------------------------------------------------------- Kron: update
 
 
@@ -422,7 +453,7 @@ def psgd_calc_A_and_conjB(G: Tensor, Q, conjB: Optional[Tensor]):
     triangular solve per mode)."""
     if conjB is None:
         conjB = torch.randn_like(G)
-    A = casted_einsum(cached_precond_grad_expr(ndim_tuple(Q), G.ndim), *Q, G)
+    A = _kron_apply(promote(G), [promote(q) for q in Q], twice=False).to(G.dtype)
     conjB = promote(conjB)
     tri = []
     for i, q in enumerate(Q):
@@ -513,8 +544,7 @@ def psgd_pro_update_precond(G, precond_lr, Q, running_lower_bound, lower_bount_b
 def precond_grad_cached_(ea: Tensor, cached_q: List[Tensor], caution: bool = False, grad: Optional[Tensor] = None):
     if caution:
         ea = _core._caution_impl(grad, ea)
-    expr = cached_precond_grad_expr(ndim_tuple(cached_q), ea.ndim)
-    return compiled_einsum(expr, *[promote(q) for q in cached_q], promote(ea))
+    return _kron_apply(promote(ea), [promote(q) for q in cached_q], twice=False)
 
 
 def psgd_precond_grad(ea: Tensor, preconds, caution: bool = False, grad: Optional[Tensor] = None,
@@ -525,9 +555,7 @@ def psgd_precond_grad(ea: Tensor, preconds, caution: bool = False, grad: Optiona
     if store_triu_as_line:
         preconds = line_to_triu(preconds)
     qs = [promote(q) for q in preconds]
-    if sqrt:
-        return compiled_einsum(cached_precond_grad_expr(ndim_tuple(qs), ea.ndim), *qs, promote(ea))
-    return compiled_einsum(precond_grad_expr(ndim_tuple(qs), ea.ndim), *[q for q in qs for _ in (0, 1)], promote(ea))
+    return _kron_apply(promote(ea), qs, twice=not sqrt)
 
 
 def fused_precond_grad_cached_(ea, param, lr, grad, decay, caution, cached_q, cautious_decay: bool = False):
@@ -547,7 +575,8 @@ def fused_psgd_precond_grad(ea, param, lr, grad, decay, caution, preconds, store
 def low_rank_mm(U: Tensor, V: Tensor, x: Tensor) -> Tensor:
     """``(I + U V^T) x`` without forming the matrix."""
     dtype = min_dtype([U, V, x])
-    return x + compiled_einsum("br,gr,g->b", U.to(dtype), V.to(dtype), x.to(dtype)).to(x.dtype)
+    # contracted right to left (V^T x first): the intermediate is rank-sized, never numel x numel
+    return x + (U.to(dtype) @ (V.to(dtype).T @ x.to(dtype))).to(x.dtype)
 
 
 def lra_precond(U: Tensor, V: Tensor, d: Tensor, g: Tensor):

@@ -32,6 +32,9 @@ def main():
     ap.add_argument("--windows", type=int, default=6)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--kwargs", default="{}", help="JSON dict of extra optimizer kwargs")
+    ap.add_argument("--compile-mode", default=None,
+                    help="reference arm only: value for heavyball.utils.compile_mode ('none' = eager); default = stock")
+    ap.add_argument("--profile", action="store_true", help="print a torch.profiler table of a few steps (ours / reference)")
     args = ap.parse_args()
 
     import torch
@@ -39,6 +42,9 @@ def main():
     if args.impl == "reference":
         sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
         import heavyball as lib
+
+        if args.compile_mode is not None:
+            lib.utils.compile_mode = None if args.compile_mode.lower() == "none" else args.compile_mode
     elif args.impl == "ours":
         sys.path.insert(0, ROOT)
         import heavyball_b200 as lib
@@ -58,6 +64,15 @@ def main():
         for _ in range(args.warmup):
             opt.step()
         torch.cuda.synchronize()
+        if args.profile:
+            from torch.profiler import ProfilerActivity, profile
+
+            with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+                for _ in range(4):
+                    opt.step()
+                torch.cuda.synchronize()
+            print(prof.key_averages().table(sort_by="self_cuda_time_total", row_limit=18, max_name_column_width=60))
+            print(prof.key_averages().table(sort_by="self_cpu_time_total", row_limit=12, max_name_column_width=60))
         dev_us, host_us = [], []
         for _ in range(args.windows):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

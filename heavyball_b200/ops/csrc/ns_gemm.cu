@@ -164,6 +164,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int batch = blockIdx.y;
   const int num_kb = (P.K + BK - 1) / BK;
   const bool poly = P.mode == kModePoly;
+  const bool same_ab = P.same_operand && tm == tn;  // A and B tiles coincide
   // after the main loop the ring is reused: slot sx receives the S tile (poly), the next two stage
   // the output tile and its transpose for the bulk stores
   const int sx = num_kb % kStages;
@@ -190,12 +191,14 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       for (int kb = 0; kb < total; ++kb) {
         const int s = kb % kStages, round = kb / kStages;
         if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &abort_flag)) break;
-        mbar_expect_tx(&full_bar[s], kStageBytes);
         uint8_t* a_dst = tiles + s * kStageBytes;
         if (kb < num_kb) {
+          // diagonal tiles of a symmetric product multiply a row block with itself: one load feeds both operands
+          mbar_expect_tx(&full_bar[s], same_ab ? kTileBytes : kStageBytes);
           tma_load_3d(a_dst, &map_a, &full_bar[s], kb * BK, tm * BM, batch);
-          tma_load_3d(a_dst + kTileBytes, &map_b, &full_bar[s], kb * BK, tn * BN, batch);
-        } else {  // S[tm-block, tn-block] for the polynomial epilogue, as two 64-column halves
+          if (!same_ab) tma_load_3d(a_dst + kTileBytes, &map_b, &full_bar[s], kb * BK, tn * BN, batch);
+        } else {
+          mbar_expect_tx(&full_bar[s], kStageBytes);  // S[tm-block, tn-block] for the polynomial epilogue, as two 64-column halves
           tma_load_3d(a_dst, &map_a, &full_bar[s], tn * BN, tm * BM, batch);
           tma_load_3d(a_dst + kTileBytes, &map_a, &full_bar[s], tn * BN + BK, tm * BM, batch);
         }
@@ -211,7 +214,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (!ok) break;
         tc_fence_after();
         const uint32_t a_addr = smem_u32(tiles + s * kStageBytes);
-        const uint64_t a_desc = make_smem_desc(a_addr), b_desc = make_smem_desc(a_addr + kTileBytes);
+        const uint64_t a_desc = make_smem_desc(a_addr), b_desc = same_ab ? a_desc : make_smem_desc(a_addr + kTileBytes);
 #pragma unroll
         for (int k = 0; k < BK / 16; ++k) {
           // advancing 16 bf16 (32 B) along K inside the swizzle atom = +2 in 16-byte address units
@@ -450,6 +453,8 @@ cudaError_t launch_ns_gemm(const void* A, int64_t lda, int64_t strideA, const vo
     if (e != cudaSuccess) return e;
     configured = true;
   }
+  GemmParams Q = P;
+  Q.same_operand = (A == B && lda == ldb && strideA == strideB && P.M == P.N) ? 1 : 0;
   CUtensorMap ma, mb, mc, mct;
   if (!make_map(&ma, A, P.M, P.K, lda, strideA, P.batch) || !make_map(&mb, B, P.N, P.K, ldb, strideB, P.batch))
     return cudaErrorInvalidValue;
@@ -460,7 +465,7 @@ cudaError_t launch_ns_gemm(const void* A, int64_t lda, int64_t strideA, const vo
   const int tiles_m = (P.M + BM - 1) / BM, tiles_n = (P.N + BN - 1) / BN;
   const int tiles = P.symmetric ? tiles_m * (tiles_m + 1) / 2 : tiles_m * tiles_n;
   dim3 grid(tiles, P.batch);
-  ns_gemm_kernel<<<grid, kGemmThreads, kSmemBytes, stream>>>(ma, mb, mc, mct, P);
+  ns_gemm_kernel<<<grid, kGemmThreads, kSmemBytes, stream>>>(ma, mb, mc, mct, Q);
   return cudaGetLastError();
 }
 

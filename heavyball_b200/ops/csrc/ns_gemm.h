@@ -13,6 +13,7 @@ struct GemmParams {
   int M, N, K, batch;
   int mode;
   int symmetric;            // compute tiles with tile_n >= tile_m only and mirror them through CT
+  int same_operand;         // A and B are the same matrix (set by the launcher): diagonal tiles load it once
   __nv_bfloat16* C;         // bf16 output [M, N] (may be null)
   int64_t ldc, strideC;
   __nv_bfloat16* CT;        // bf16 transposed output [N, M] (may be null; equals C for symmetric results)

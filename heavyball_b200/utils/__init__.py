@@ -7,6 +7,7 @@ switches, which are read at call time:
 * ``zeroth_power_mode`` / ``precise_zeroth_power_mode`` — orthogonalisation method
 * ``default_division_backend`` / ``atan2_scale`` — guarded division flavour
 * ``dither_steps`` — number of uniform draws summed for stochastic rounding
+* ``fast_qr`` — on CUDA, orthogonalise eigenbasis refreshes with batched panel-wise Cholesky QR instead of Householder QR
 * ``compile_mode`` / ``dynamic`` / ``compile_mode_recommended_to_none`` — accepted for source
   compatibility; there is no tracing compiler here, fused execution is done by the sm_100a kernels
   in ``heavyball_b200.ops``.
@@ -22,6 +23,7 @@ precise_zeroth_power_mode = "qr"
 default_division_backend = "eps_clamp"
 atan2_scale = 16.0
 dither_steps = 1
+fast_qr = True  # CUDA: eigenbasis refreshes use batched panel-wise Cholesky QR (Householder QR when that fails, and on CPU)
 tiny_bf16 = torch.finfo(torch.bfloat16).tiny
 
 from .core import *  # noqa: E402,F401,F403

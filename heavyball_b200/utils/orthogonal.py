@@ -137,6 +137,58 @@ def _compilable_grafting(magnitude: Tensor, direction: Tensor) -> Tensor:
     return direction * (magnitude.norm() / direction.norm().clamp(min=1e-6))
 
 
+_QR_PANEL = 32
+_QR_PASSES = 3
+
+
+def _panel_cholesky_qr(x: Tensor):
+    """Orthonormal basis of the columns of ``x`` (``... x n x k``, ``n >= k``), equal to the Q factor of
+    Householder QR up to the sign of each column, built from batched GEMM / POTRF / TRSM only.
+
+    Householder QR on the GPU factorises one matrix of a batch at a time, column by column, and
+    synchronises with the host; an eigenbasis refresh spends nearly all of its time there.  Here the
+    columns are taken in panels of 32.  A panel is projected off the basis found so far (block
+    Gram-Schmidt), its columns are normalised, and the panel itself is orthogonalised by Cholesky QR
+    (``W^T W = L L^T``, ``W <- W L^-T``); the three steps are repeated three times.  Plain Cholesky QR
+    of the whole matrix squares its condition number and fails for the matrices met here (``GG @ Q_old``
+    with eigenvalues spread over many decades); within a panel, after the projection has removed the
+    dominant directions, the columns are of similar size and nearly orthogonal.  Three passes keep
+    ``|Q^T Q - I|`` at fp32 rounding level for spectra spanning 20 decades with an arbitrary ``Q_old``.
+
+    Returns ``None`` when a panel's Gram matrix is not positive definite or the result is not finite
+    (e.g. an all-zero input); the caller then uses Householder QR.  One host synchronisation, at the end."""
+    batch, (n, k) = x.shape[:-2], x.shape[-2:]
+    a = x.reshape(-1, n, k)
+    tiny = torch.finfo(a.dtype).tiny
+    a = a / a.norm(dim=-2, keepdim=True).clamp_(min=tiny)
+    q = torch.empty_like(a)
+    bad = torch.zeros((), dtype=torch.int32, device=a.device)
+    for j in range(0, k, _QR_PANEL):
+        w = a[..., j : j + _QR_PANEL]
+        done = q[..., :j]
+        for _ in range(_QR_PASSES):
+            if j:
+                w = torch.baddbmm(w, done, done.mT @ w, alpha=-1.0)
+            w = w / w.norm(dim=-2, keepdim=True).clamp_(min=tiny)
+            chol, info = torch.linalg.cholesky_ex(w.mT @ w)
+            bad += info.ne(0).sum()
+            w = torch.linalg.solve_triangular(chol.mT, w, upper=True, left=False)
+        q[..., j : j + _QR_PANEL] = w
+    bad += (~torch.isfinite(q)).any()
+    if int(bad):
+        return None
+    return q.reshape(*batch, n, k)
+
+
+def _qr_basis(x: Tensor) -> Tensor:
+    x32 = promote(x)
+    if x32.is_cuda and _settings().fast_qr and x32.shape[-2] >= x32.shape[-1] >= 2 * _QR_PANEL:
+        q = _panel_cholesky_qr(x32)
+        if q is not None:
+            return q
+    return torch.linalg.qr(x32).Q
+
+
 def _compilable_orthogonal_(x: Tensor, mode, out, scale_mode):
     mode = mode if isinstance(mode, ZerothPowerMode) else ZerothPowerMode(mode)
     scale_mode = scale_mode if isinstance(scale_mode, OrthoScaleMode) else OrthoScaleMode(scale_mode)
@@ -147,7 +199,7 @@ def _compilable_orthogonal_(x: Tensor, mode, out, scale_mode):
     elif mode is ZerothPowerMode.legacy_newtonschulz:
         y = legacy_zeropower_via_newtonschulz5(x, 5)
     elif mode is ZerothPowerMode.qr:
-        y = torch.linalg.qr(promote(x)).Q
+        y = _qr_basis(x)
     elif mode is ZerothPowerMode.svd:
         u, _, vt = torch.linalg.svd(promote(x))
         y = u @ vt

@@ -21,7 +21,7 @@ import torch
 from torch import Tensor
 
 from .core import copy_stochastic_, promote, stochastic_lerp_
-from .orthogonal import inplace_orthogonal_
+from .orthogonal import _qr_basis, inplace_orthogonal_
 
 einsum_base = string.ascii_lowercase
 
@@ -372,7 +372,7 @@ def get_psgd_eigenbasis(Q: List[Tensor], prev: List[Optional[Tensor]]):
         if old is None:
             raise ValueError("get_psgd_eigenbasis requires a previous basis for matrix blocks; use init_psgd_eigenbasis")
         q32, old32 = promote(q), promote(old)
-        raw = torch.linalg.qr(q32.mT @ (q32 @ old32), mode="reduced").Q.to(dtype=q.dtype)
+        raw = _qr_basis(q32.mT @ (q32 @ old32)).to(dtype=q.dtype)
         proj = q32 @ promote(raw)
         order = torch.argsort(compiled_einsum("...ij,...ij->...j", proj, proj), descending=True)
         raw = raw.gather(-1, order.unsqueeze(-2).expand_as(raw))

@@ -1,4 +1,8 @@
-"""GPT-2-style decoder-only transformer."""
+"""GPT-2-style decoder-only transformer.
+
+The embedding table and the output head are stored with their row count rounded up to a multiple of 64
+(50 257 -> 50 304): the head's three GEMMs then run on the aligned tensor-core kernels instead of a legacy
+unaligned path that is about 9x slower on B200.  The loss is ``ops.nn.linear_cross_entropy``."""
 
 from __future__ import annotations
 
@@ -8,6 +12,8 @@ from dataclasses import dataclass
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
+
+from ..ops.nn import LayerNorm, linear_cross_entropy
 
 
 @dataclass
@@ -20,6 +26,11 @@ class GPTConfig:
     seq_len: int = 1024
     init_std: float = 0.02
     tie_embeddings: bool = True
+    vocab_multiple: int = 64  # embedding / head rows are rounded up to this; the extra rows stay zero
+
+
+def padded_vocab(vocab_size: int, multiple: int) -> int:
+    return -(-vocab_size // max(multiple, 1)) * max(multiple, 1)
 
 
 class Block(nn.Module):
@@ -27,10 +38,10 @@ class Block(nn.Module):
         super().__init__()
         d, ff = cfg.d_model, cfg.d_ff or 4 * cfg.d_model
         self.n_head = cfg.n_head
-        self.ln1 = nn.LayerNorm(d)
+        self.ln1 = LayerNorm(d)
         self.qkv = nn.Linear(d, 3 * d)
         self.proj = nn.Linear(d, d)
-        self.ln2 = nn.LayerNorm(d)
+        self.ln2 = LayerNorm(d)
         self.fc = nn.Linear(d, ff)
         self.out = nn.Linear(ff, d)
 
@@ -46,14 +57,18 @@ class GPT(nn.Module):
     def __init__(self, cfg: GPTConfig):
         super().__init__()
         self.cfg = cfg
-        self.wte = nn.Embedding(cfg.vocab_size, cfg.d_model)
+        rows = padded_vocab(cfg.vocab_size, cfg.vocab_multiple)
+        self.wte = nn.Embedding(rows, cfg.d_model)
         self.wpe = nn.Embedding(cfg.seq_len, cfg.d_model)
         self.blocks = nn.ModuleList(Block(cfg) for _ in range(cfg.n_layer))
-        self.ln_f = nn.LayerNorm(cfg.d_model)
-        self.head = nn.Linear(cfg.d_model, cfg.vocab_size, bias=False)
+        self.ln_f = LayerNorm(cfg.d_model)
+        self.head = nn.Linear(cfg.d_model, rows, bias=False)
         if cfg.tie_embeddings:
             self.head.weight = self.wte.weight
         self.apply(self._init)
+        with torch.no_grad():  # padding rows: never indexed, zero probability, zero gradient
+            self.wte.weight[cfg.vocab_size :].zero_()
+            self.head.weight[cfg.vocab_size :].zero_()
 
     def _init(self, m):
         if isinstance(m, (nn.Linear, nn.Embedding)):
@@ -66,10 +81,10 @@ class GPT(nn.Module):
         x = self.wte(idx) + self.wpe(torch.arange(T, device=idx.device))
         for blk in self.blocks:
             x = blk(x)
-        logits = self.head(self.ln_f(x))
+        h = self.ln_f(x)
         if targets is None:
-            return logits
-        return F.cross_entropy(logits.float().view(-1, logits.size(-1)), targets.reshape(-1))
+            return self.head(h)[..., : self.cfg.vocab_size]
+        return linear_cross_entropy(h, self.head.weight, targets, self.cfg.vocab_size)
 
 
 def gpt2_small(**kw):

@@ -8,6 +8,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..ops.nn import linear_cross_entropy
+
 
 @dataclass
 class LlamaConfig:
@@ -90,10 +92,10 @@ class Llama(nn.Module):
         cos, sin = self._angles(idx.shape[1], idx.device, x.dtype)
         for layer in self.layers:
             x = layer(x, cos, sin)
-        logits = self.head(self.norm(x))
+        h = self.norm(x)
         if targets is None:
-            return logits
-        return F.cross_entropy(logits.float().view(-1, logits.size(-1)), targets.reshape(-1))
+            return self.head(h)
+        return linear_cross_entropy(h, self.head.weight, targets)
 
 
 def llama_1p3b(**kw):

@@ -7,7 +7,9 @@
 #include <optional>
 #include <vector>
 
+#include "cross_entropy.h"
 #include "fused_chain.h"
+#include "layer_norm.h"
 #include "ns_gemm.h"
 #include "peer_sync.h"
 
@@ -183,7 +185,69 @@ void peer_wait(const at::Tensor& my_flags, int slot, int world, int epoch, doubl
                              at::cuda::getCurrentCUDAStream()), "peer_wait launch");
 }
 
+// In-place softmax cross-entropy: `logits` ([rows, ld] bf16) becomes the gradient of sum(loss) * scale[0];
+// returns the per-row losses.
+at::Tensor cross_entropy_(at::Tensor& logits, const at::Tensor& targets, const at::Tensor& scale, int64_t vocab,
+                          int64_t ignore_index) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.scalar_type() == at::kBFloat16, "logits: 2-D bf16 CUDA tensor");
+  TORCH_CHECK(logits.is_contiguous() && logits.size(1) % 8 == 0 && aligned16(logits.data_ptr()),
+              "logits must be contiguous with a row length that is a multiple of 8 (pad the vocabulary)");
+  TORCH_CHECK(vocab > 0 && vocab <= logits.size(1), "vocab out of range");
+  TORCH_CHECK(targets.is_cuda() && targets.scalar_type() == at::kLong && targets.is_contiguous() &&
+                  targets.numel() == logits.size(0), "targets: contiguous int64, one per row");
+  TORCH_CHECK(scale.is_cuda() && scale.scalar_type() == at::kFloat && scale.numel() == 1, "scale: fp32 device scalar");
+  c10::cuda::CUDAGuard guard(logits.device());
+  at::Tensor loss = at::empty({logits.size(0)}, logits.options().dtype(at::kFloat));
+  check(hb::launch_cross_entropy(logits.data_ptr(), reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()),
+                                 loss.data_ptr<float>(), scale.data_ptr<float>(), logits.size(0), (int)vocab,
+                                 (int)logits.size(1), ignore_index, at::cuda::getCurrentCUDAStream()),
+        "cross_entropy launch");
+  return loss;
+}
+
+// LayerNorm over the last dimension of a contiguous fp32 tensor.  Returns (y, mean, rstd); y is bf16 when asked.
+std::vector<at::Tensor> layer_norm_fwd(const at::Tensor& x, const at::Tensor& gamma, const at::Tensor& beta, double eps,
+                                       bool out_bf16) {
+  const int64_t D = x.size(-1);
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.is_contiguous(), "x: contiguous fp32 CUDA tensor");
+  TORCH_CHECK(hb::layer_norm_supported((int)D), "row length must be a multiple of 128, at most 1024");
+  TORCH_CHECK(gamma.scalar_type() == at::kFloat && beta.scalar_type() == at::kFloat && gamma.numel() == D &&
+                  beta.numel() == D && gamma.is_contiguous() && beta.is_contiguous(), "gamma / beta: fp32 [D]");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t rows = x.numel() / D;
+  at::Tensor y = at::empty(x.sizes(), x.options().dtype(out_bf16 ? at::kBFloat16 : at::kFloat));
+  at::Tensor mean = at::empty({rows}, x.options()), rstd = at::empty({rows}, x.options());
+  check(hb::launch_layer_norm_fwd(x.data_ptr<float>(), gamma.data_ptr<float>(), beta.data_ptr<float>(), y.data_ptr(),
+                                  out_bf16, mean.data_ptr<float>(), rstd.data_ptr<float>(), rows, (int)D, (float)eps,
+                                  at::cuda::getCurrentCUDAStream()), "layer_norm_fwd launch");
+  return {y, mean, rstd};
+}
+
+// Returns (dx, dgamma, dbeta) for dy in fp32 or bf16.
+std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& gamma,
+                                       const at::Tensor& mean, const at::Tensor& rstd) {
+  const int64_t D = x.size(-1);
+  TORCH_CHECK(dy.is_cuda() && dy.is_contiguous() && dy.numel() == x.numel() &&
+                  (dy.scalar_type() == at::kFloat || dy.scalar_type() == at::kBFloat16), "dy: contiguous fp32 / bf16");
+  TORCH_CHECK(x.scalar_type() == at::kFloat && x.is_contiguous() && hb::layer_norm_supported((int)D), "x: contiguous fp32");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t rows = x.numel() / D;
+  const int n_cta = hb::layer_norm_partial_ctas(rows);
+  at::Tensor dx = at::empty_like(x), dgamma = at::empty_like(gamma), dbeta = at::empty_like(gamma);
+  at::Tensor partial = at::empty({n_cta, 2 * D}, x.options());
+  check(hb::launch_layer_norm_bwd(dy.data_ptr(), dy.scalar_type() == at::kBFloat16, x.data_ptr<float>(),
+                                  gamma.data_ptr<float>(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                                  dx.data_ptr<float>(), dgamma.data_ptr<float>(), dbeta.data_ptr<float>(),
+                                  partial.data_ptr<float>(), n_cta, rows, (int)D, at::cuda::getCurrentCUDAStream()),
+        "layer_norm_bwd launch");
+  return {dx, dgamma, dbeta};
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("layer_norm_fwd", &layer_norm_fwd);
+  m.def("layer_norm_bwd", &layer_norm_bwd);
+  m.def("layer_norm_supported", &hb::layer_norm_supported);
+  m.def("cross_entropy_", &cross_entropy_);
   m.def("peer_signal", &peer_signal);
   m.def("peer_wait", &peer_wait);
   m.attr("MAX_WORLD") = hb::kMaxWorld;

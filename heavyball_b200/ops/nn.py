@@ -1,0 +1,113 @@
+"""Model-side fused ops used by ``heavyball_b200.models``: the output head's projection + softmax
+cross-entropy with the loss kernel writing the logits' gradient in place.
+
+The forward pass computes ``logits = h @ W^T`` once in bf16 (library GEMM), then one kernel
+(``csrc/cross_entropy.cu``) reads each row twice (the second read hits L2), returns the per-row loss and
+overwrites the logits with ``(softmax - onehot) / n_valid``.  The backward pass is two GEMMs on that
+buffer.  Compared with ``F.cross_entropy(logits.float(), targets)`` under autocast this removes the fp32
+copy of the logits, ``log_softmax`` and its backward, and the cast back: about 26 GB of HBM traffic per
+step for 16 x 1024 tokens and a 50k vocabulary, against 3.3 GB here.
+
+``W`` may have more rows than the vocabulary (rows rounded up to a multiple of 64 keep the GEMMs on their
+aligned tensor-core kernels: a 50 257-row head runs on a legacy unaligned path about 9x slower); the
+extra columns get zero probability and zero gradient.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from . import available, launch_counter, load
+
+
+def _mm_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    try:
+        return torch.mm(a, b, out_dtype=torch.float32)
+    except (TypeError, RuntimeError):
+        return torch.mm(a, b).float()
+
+
+class _LinearCrossEntropy(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, weight, targets, vocab, ignore_index):
+        h16 = h.detach().reshape(-1, h.shape[-1]).to(torch.bfloat16)
+        w16 = weight.detach().to(torch.bfloat16)
+        flat_targets = targets.reshape(-1).contiguous()
+        n_valid = (flat_targets != ignore_index).sum().clamp_(min=1)
+        scale = n_valid.to(torch.float32).reciprocal_().reshape(1)
+        logits = h16 @ w16.mT
+        losses = load().cross_entropy_(logits, flat_targets, scale, vocab, ignore_index)
+        launch_counter.count += 1
+        ctx.save_for_backward(logits, h16, w16)
+        ctx.h_meta, ctx.w_dtype = (h.shape, h.dtype), weight.dtype
+        return losses.sum() * scale[0]
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        dlogits, h16, w16 = ctx.saved_tensors
+        (h_shape, h_dtype), w_dtype = ctx.h_meta, ctx.w_dtype
+        dh = dw = None
+        if ctx.needs_input_grad[0]:
+            dh = (dlogits @ w16).mul_(grad_out).reshape(h_shape).to(h_dtype)
+        if ctx.needs_input_grad[1]:
+            dw = _mm_f32(dlogits.mT, h16).mul_(grad_out).to(w_dtype)
+        return dh, dw, None, None, None
+
+
+def linear_cross_entropy(h: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, vocab: int | None = None,
+                         ignore_index: int = -100) -> torch.Tensor:  # fmt: skip
+    """Mean cross-entropy of ``softmax((h @ weight^T)[..., :vocab])`` against ``targets``.
+
+    ``h``: ``[..., d]``; ``weight``: ``[rows >= vocab, d]``; ``targets``: integer tensor with ``h``'s leading
+    shape.  On sm_100a the fused kernel path runs (``weight.shape[0]`` must be a multiple of 8); elsewhere the
+    same quantity is computed with PyTorch ops."""
+    vocab = weight.shape[0] if vocab is None else vocab
+    if h.is_cuda and available() and weight.shape[0] % 8 == 0:
+        return _LinearCrossEntropy.apply(h, weight, targets, vocab, ignore_index)
+    logits = F.linear(h, weight)[..., :vocab]
+    return F.cross_entropy(logits.float().reshape(-1, vocab), targets.reshape(-1), ignore_index=ignore_index)
+
+
+class _LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps, out_bf16):
+        y, mean, rstd = load().layer_norm_fwd(x, weight, bias, eps, out_bf16)
+        launch_counter.count += 1
+        ctx.save_for_backward(x, weight, mean, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight, mean, rstd = ctx.saved_tensors
+        dx, dw, db = load().layer_norm_bwd(dy.contiguous(), x, weight, mean, rstd)
+        launch_counter.count += 2
+        return dx, dw, db, None, None
+
+
+def _ln_kernel_applies(x: torch.Tensor, weight, bias) -> bool:
+    d = x.shape[-1]
+    return (
+        x.is_cuda and x.dtype == torch.float32 and weight is not None and bias is not None
+        and weight.dtype == torch.float32 and d % 128 == 0 and d <= 1024 and x.numel() > 0 and available()
+    )  # fmt: skip
+
+
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    """LayerNorm over the last dimension.  For fp32 CUDA activations with a row length that is a multiple
+    of 128 (up to 1024) one kernel each way runs; inside a bf16 autocast region the output is written in
+    bf16 directly (the dtype the following linear layer would cast it to) and the backward kernel takes the
+    bf16 gradient.  Other inputs go to ``F.layer_norm``."""
+    if _ln_kernel_applies(x, weight, bias):
+        out_bf16 = torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16
+        return _LayerNormFn.apply(x.contiguous(), weight, bias, eps, out_bf16)
+    return F.layer_norm(x, (x.shape[-1],), weight, bias, eps)
+
+
+class LayerNorm(torch.nn.LayerNorm):
+    """``torch.nn.LayerNorm`` (same parameters and state dict) running :func:`layer_norm`."""
+
+    def forward(self, x):
+        if len(self.normalized_shape) == 1:
+            return layer_norm(x, self.weight, self.bias, self.eps)
+        return super().forward(x)

@@ -1,0 +1,104 @@
+"""Model-side kernels against fp32 PyTorch definitions of the same op."""
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from heavyball_b200 import ops
+from heavyball_b200.ops.nn import linear_cross_entropy
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("rows,vocab,padded", [(64, 1000, 1024), (33, 50257, 50304), (7, 8, 8), (5, 509, 512)])
+def test_cross_entropy_kernel_matches_fp32_definition(rows, vocab, padded):
+    torch.manual_seed(0)
+    logits = (torch.randn(rows, padded, device="cuda") * 3).to(torch.bfloat16)
+    targets = torch.randint(0, vocab, (rows,), device="cuda")
+    targets[rows // 2] = -100
+    ref_in = logits[:, :vocab].float().requires_grad_()
+    ref = F.cross_entropy(ref_in, targets, reduction="none", ignore_index=-100)
+    n_valid = (targets != -100).sum()
+    (ref.sum() / n_valid).backward()
+
+    scale = (1.0 / n_valid.float()).reshape(1)
+    work = logits.clone()
+    losses = ops.load().cross_entropy_(work, targets, scale, vocab, -100)
+    assert torch.allclose(losses, ref, atol=2e-5, rtol=1e-5)
+    assert losses[rows // 2] == 0
+    grad = work.float()
+    assert (grad[:, vocab:] == 0).all() and (grad[rows // 2] == 0).all()
+    # bf16 storage of the gradient: relative error 2^-9 per element
+    assert torch.allclose(grad[:, :vocab], ref_in.grad, atol=1e-7, rtol=1e-2)
+
+
+def test_linear_cross_entropy_gradients_match_autograd_of_plain_ops():
+    torch.manual_seed(1)
+    d, vocab, rows_w = 96, 1001, 1024
+    h = torch.randn(4, 20, d, device="cuda", requires_grad=True)
+    w = (torch.randn(rows_w, d, device="cuda") * 0.05).requires_grad_()
+    targets = torch.randint(0, vocab, (4, 20), device="cuda")
+    loss = linear_cross_entropy(h, w, targets, vocab)
+    loss.backward()
+
+    h2 = h.detach().clone().requires_grad_()
+    w2 = w.detach().clone().requires_grad_()
+    logits = (h2.to(torch.bfloat16) @ w2.to(torch.bfloat16).mT)[..., :vocab]
+    ref = F.cross_entropy(logits.float().reshape(-1, vocab), targets.reshape(-1))
+    ref.backward()
+    assert abs(loss.item() - ref.item()) < 1e-4
+    assert torch.allclose(h.grad, h2.grad, atol=2e-4, rtol=5e-2)
+    assert torch.allclose(w.grad, w2.grad, atol=2e-4, rtol=5e-2)
+    assert (w.grad[vocab:] == 0).all()
+
+
+def test_gpt_pads_its_vocabulary_and_trains():
+    from heavyball_b200.models import GPT, GPTConfig
+
+    torch.manual_seed(0)
+    model = GPT(GPTConfig(n_layer=2, n_head=2, d_model=64, vocab_size=1001, seq_len=32)).cuda()
+    assert model.wte.weight.shape[0] == 1024
+    x = torch.randint(0, 1001, (4, 32), device="cuda")
+    y = torch.randint(0, 1001, (4, 32), device="cuda")
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        loss = model(x, y)
+        assert model(x).shape == (4, 32, 1001)
+    loss.backward()
+    assert torch.isfinite(loss) and abs(loss.item() - 6.9) < 0.3
+    assert (model.wte.weight.grad[1001:] == 0).all()
+
+
+@pytest.mark.parametrize("shape", [(16, 1024, 768), (3, 5, 128), (1, 1, 1024), (2000, 384)])
+@pytest.mark.parametrize("bf16", [False, True])
+def test_layer_norm_kernels_match_fp32_definition(shape, bf16):
+    from heavyball_b200.ops.nn import layer_norm
+
+    torch.manual_seed(0)
+    d = shape[-1]
+    x = (torch.randn(*shape, device="cuda") * 2 + 0.5).requires_grad_()
+    w = (torch.rand(d, device="cuda") + 0.5).requires_grad_()
+    b = torch.randn(d, device="cuda").requires_grad_()
+    dy = torch.randn(*shape, device="cuda")
+    with torch.autocast("cuda", dtype=torch.bfloat16, enabled=bf16):
+        y = layer_norm(x, w, b, 1e-5)
+    assert y.dtype == (torch.bfloat16 if bf16 else torch.float32)
+    y.backward(dy.to(y.dtype))
+
+    x2, w2, b2 = (t.detach().clone().requires_grad_() for t in (x, w, b))
+    ref = F.layer_norm(x2, (d,), w2, b2, 1e-5)
+    ref.backward(dy.to(y.dtype).float())
+    tol = dict(atol=2e-2, rtol=2e-2) if bf16 else dict(atol=2e-5, rtol=1e-5)
+    assert torch.allclose(y.float(), ref, **tol)
+    assert torch.allclose(x.grad, x2.grad, atol=1e-4, rtol=1e-4)
+    rows = x.numel() // d
+    assert torch.allclose(w.grad, w2.grad, atol=1e-5 * rows**0.5 + 1e-4, rtol=1e-4)
+    assert torch.allclose(b.grad, b2.grad, atol=1e-5 * rows**0.5 + 1e-4, rtol=1e-4)
+
+
+def test_layer_norm_module_keeps_state_dict_and_falls_back():
+    from heavyball_b200.ops.nn import LayerNorm
+
+    ln = LayerNorm(100).cuda()  # row length not a multiple of 128: framework path
+    assert set(ln.state_dict()) == {"weight", "bias"}
+    x = torch.randn(4, 100, device="cuda")
+    assert torch.allclose(ln(x), F.layer_norm(x, (100,), ln.weight, ln.bias, ln.eps))

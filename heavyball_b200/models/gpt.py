@@ -47,7 +47,15 @@ class Block(nn.Module):
 
     def forward(self, x):
         B, T, D = x.shape
-        q, k, v = self.qkv(self.ln1(x)).view(B, T, 3, self.n_head, D // self.n_head).permute(2, 0, 3, 1, 4)
+        # One packed [3D, D] parameter (the shape the matrix optimizers see), three projections: each of q, k, v
+        # is then dense in [B, T, H, hd] order, so neither the attention output nor the three gradients coming
+        # back from the attention kernel need a strided copy / concatenation (about 0.3 ms per layer otherwise).
+        h = self.ln1(x)
+        w, b = self.qkv.weight, self.qkv.bias
+        q, k, v = (
+            F.linear(h, w[i * D : (i + 1) * D], b[i * D : (i + 1) * D]).view(B, T, self.n_head, D // self.n_head).transpose(1, 2)
+            for i in range(3)
+        )
         a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         x = x + self.proj(a.transpose(1, 2).reshape(B, T, D))
         return x + self.out(F.gelu(self.fc(self.ln2(x)), approximate="tanh"))

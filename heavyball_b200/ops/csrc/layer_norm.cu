@@ -154,22 +154,22 @@ __global__ void __launch_bounds__(kWarps * 32) ln_bwd_kernel(const GradT* __rest
   }
 }
 
-// dgamma / dbeta = column sums of the per-CTA partials; thread t sums column t of the [n, 2 * D] table.
-__global__ void ln_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dgamma, float* __restrict__ dbeta,
-                                 int n, int D) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= 2 * D) return;
-  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-  int i = 0;
-  for (; i + 3 < n; i += 4) {
-    a0 += partial[(long long)i * 2 * D + c];
-    a1 += partial[(long long)(i + 1) * 2 * D + c];
-    a2 += partial[(long long)(i + 2) * 2 * D + c];
-    a3 += partial[(long long)(i + 3) * 2 * D + c];
+// dgamma / dbeta = column sums of the per-CTA partials ([n, 2 * D] table).  A block of 32 x 8 threads owns 32
+// adjacent columns; the 8 thread rows stride over the n partials and are combined through shared memory.
+__global__ void __launch_bounds__(256) ln_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dgamma,
+                                                        float* __restrict__ dbeta, int n, int D) {
+  const int c = blockIdx.x * 32 + threadIdx.x;  // 2 * D is a multiple of 32
+  float a = 0.f;
+  for (int i = threadIdx.y; i < n; i += 8) a += partial[(long long)i * 2 * D + c];
+  __shared__ float red[8][33];
+  red[threadIdx.y][threadIdx.x] = a;
+  __syncthreads();
+  if (threadIdx.y == 0) {
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += red[j][threadIdx.x];
+    if (c < D) dgamma[c] = s; else dbeta[c - D] = s;
   }
-  for (; i < n; ++i) a0 += partial[(long long)i * 2 * D + c];
-  const float s = (a0 + a1) + (a2 + a3);
-  if (c < D) dgamma[c] = s; else dbeta[c - D] = s;
 }
 
 template <int VPL>
@@ -199,7 +199,7 @@ bool layer_norm_supported(int D) { return D > 0 && D % 128 == 0 && D / 128 <= 8;
 
 int layer_norm_partial_ctas(long long rows) {
   const long long want = (rows + kWarps - 1) / kWarps;
-  return (int)(want < 148 * 4 ? (want < 1 ? 1 : want) : 148 * 4);
+  return (int)(want < 148 * 2 ? (want < 1 ? 1 : want) : 148 * 2);
 }
 
 #define HB_LN_SWITCH(D, CALL)            \
@@ -237,7 +237,7 @@ cudaError_t launch_layer_norm_bwd(const void* dy, bool dy_bf16, const float* x, 
     err = run();
   }
   if (err != cudaSuccess) return err;
-  ln_reduce_kernel<<<(2 * D + 255) / 256, 256, 0, stream>>>(partial, dgamma, dbeta, n_cta, D);
+  ln_reduce_kernel<<<2 * D / 32, dim3(32, 8), 0, stream>>>(partial, dgamma, dbeta, n_cta, D);
   return cudaGetLastError();
 }
 

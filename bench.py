@@ -36,6 +36,7 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--trace-steps", action="store_true", help="also print every timed step's device time to stderr")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="gpt2-small", choices=sorted(CONFIGS))
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end phase")
@@ -44,54 +45,83 @@ def parse():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs.
+
+    nvidia-smi is started before the warm-up steps (its start-up initialises NVML on every GPU of the node and
+    stalls running kernels for up to a second, which must not land in the timed region); samples carry
+    timestamps and only those taken between ``begin()`` and ``stop()`` are summarised."""
 
     FIELDS = (
-        "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+        "timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
         "clocks_event_reasons.sw_power_cap"
     )
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self, device_index):
-        self.proc, self.index = None, device_index
+        self.proc, self.index, self.t_begin = None, device_index, None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
                  "-i", str(self.index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
             )  # fmt: skip
         except OSError:
             self.proc = None
+            return
+        import threading
+
+        self.lines = []
+        self.reader = threading.Thread(target=lambda: self.lines.extend(iter(self.proc.stdout.readline, "")), daemon=True)
+        self.reader.start()
+        deadline = time.time() + 5.0  # first sample printed = NVML start-up is over
+        while not self.lines and time.time() < deadline and self.proc.poll() is None:
+            time.sleep(0.02)
+
+    def begin(self):
+        self.t_begin = time.time()
+
+    @staticmethod
+    def _stamp(text):
+        import datetime
+
+        try:
+            return datetime.datetime.strptime(text, "%Y/%m/%d %H:%M:%S.%f").timestamp()
+        except ValueError:
+            return None
 
     def stop(self):
+        t_end = time.time()
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.12)  # let the sample that covers the end of the region be written
         self.proc.terminate()
         try:
-            out, _ = self.proc.communicate(timeout=5)
+            self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-            out, _ = self.proc.communicate()
-        clocks, maxes, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
+            self.proc.wait()
+        self.reader.join(timeout=2)
+        rows = []
+        for line in list(self.lines):
             parts = [x.strip() for x in line.split(",")]
-            if len(parts) < 8:
+            if len(parts) < 9:
                 continue
             try:
-                clocks.append(float(parts[1]))
-                maxes.append(float(parts[2]))
+                rows.append((self._stamp(parts[0]), float(parts[2]), float(parts[3]), parts[5:9]))
             except ValueError:
                 continue
-            for name, val in zip(names, parts[4:8]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        clocks.sort()
+        t0 = self.t_begin if self.t_begin is not None else 0.0
+        inside = [r for r in rows if r[0] is not None and t0 <= r[0] <= t_end + 0.1]
+        if not inside:  # region shorter than the sampling period: take the samples nearest to it
+            inside = [r for r in rows if r[0] is None or r[0] >= t0 - 0.25][:3] or rows[-3:]
+        clocks = sorted(r[1] for r in inside)
+        reasons = {name for r in inside for name, val in zip(self.NAMES, r[3]) if val.lower().startswith("active")}
         return {
             "sm_mhz": clocks[len(clocks) // 2] if clocks else None,
-            "sm_max_mhz": max(maxes) if maxes else None,
+            "sm_max_mhz": max((r[2] for r in inside), default=None),
             "samples": len(clocks),
             "reasons": sorted(reasons),
         }
@@ -195,25 +225,33 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     for i in range(args.warmup):
         train_step(dev_tokens[i % n_host])
     barrier()
 
     # ---- phase 1: device-timed, inputs already on the GPU
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     if launches is not None:
         launches.reset()
     opt_ms = []
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    sampler.begin()
     start.record()
     last = None
+    marks = []
     for i in range(args.steps):
         last = train_step(dev_tokens[i % n_host])
+        if args.trace_steps:
+            marks.append(torch.cuda.Event(enable_timing=True))
+            marks[-1].record()
     stop.record()
     barrier()
+    if marks:
+        per_step = [a.elapsed_time(b) for a, b in zip([start] + marks[:-1], marks)]
+        print(f"rank {rank} step ms: " + " ".join(f"{t:.1f}" for t in per_step), file=sys.stderr)
     n_launch = launches.count if launches is not None else None
     clocks = sampler.stop() if rank == 0 else None
     step_ms = max_over_ranks(start.elapsed_time(stop) / args.steps)

@@ -24,7 +24,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _SRC = os.path.join(_HERE, "csrc")
 _BUILD = os.path.join(_HERE, "_build")
 _NAME = "hb200_ops"
-_SOURCES = ["bindings.cpp", "cross_entropy.cu", "fused_chain.cu", "layer_norm.cu", "ns_gemm.cu", "noalloc_adamw.cu", "peer_sync.cu"]
+_SOURCES = ["bindings.cpp", "cross_entropy.cu", "fused_chain.cu", "layer_norm.cu", "ns_gemm.cu", "noalloc_adamw.cu", "peer_sync.cu", "tf32_gemm.cu"]
 _lock = threading.Lock()
 _ext = None
 _load_error: Optional[BaseException] = None
@@ -251,3 +251,28 @@ def newton_schulz(G: torch.Tensor, coeffs, out_scale: float = 1.0) -> Optional[t
     mats = list(G.reshape(-1, R, C).unbind(0))
     res = newton_schulz_batched(mats, coeffs, out_scale=out_scale)
     return res.reshape(G.shape).to(G.dtype)
+
+
+# ---------------------------------------------------------------------------------------- fp32 matmul on tensor cores
+
+
+def matmul_supported(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """True when :func:`matmul3` applies: fp32 CUDA matrices on sm_100a, large enough for 128 x 128 tiles to pay."""
+    return (
+        a.is_cuda and b.is_cuda and a.dtype == torch.float32 and b.dtype == torch.float32 and a.ndim >= 2 and b.ndim >= 2
+        and min(a.shape[-1], a.shape[-2], b.shape[-1], b.shape[-2]) >= 128 and available()
+    )  # fmt: skip
+
+
+def matmul3(a: torch.Tensor, b: torch.Tensor, trans_a: bool = False, trans_b: bool = False, alpha: float = 1.0) -> torch.Tensor:
+    """``alpha * op(a) @ op(b)`` for fp32 matrices (optionally batched, equal leading shapes) on the tf32 tensor
+    cores with the 3-term split (relative error about 2^-21; plain tf32 gives 2^-11, fp32 SIMT 2^-24)."""
+    lead = a.shape[:-2]
+    if b.shape[:-2] != lead:
+        lead = torch.broadcast_shapes(a.shape[:-2], b.shape[:-2])
+        a, b = a.expand(*lead, *a.shape[-2:]), b.expand(*lead, *b.shape[-2:])
+    a3 = a.reshape(-1, *a.shape[-2:]).contiguous()
+    b3 = b.reshape(-1, *b.shape[-2:]).contiguous()
+    out = load().tf32x3_matmul(a3, b3, trans_a, trans_b, alpha, _status(a.device))
+    launch_counter.count += 3
+    return out.reshape(*lead, *out.shape[-2:])

@@ -12,6 +12,7 @@
 #include "layer_norm.h"
 #include "ns_gemm.h"
 #include "peer_sync.h"
+#include "tf32_gemm.h"
 
 namespace py = pybind11;
 using OptT = std::optional<at::Tensor>;
@@ -205,6 +206,31 @@ at::Tensor cross_entropy_(at::Tensor& logits, const at::Tensor& targets, const a
   return loss;
 }
 
+// op(a) @ op(b) for batched fp32 matrices on the split-tf32 tensor-core path.  a: [batch, R, C]; ta = 0 uses a as
+// [M, K], ta = 1 as [K, M]; likewise b is [K, N] for tb = 0 and [N, K] for tb = 1.  Returns [batch, M, N].
+at::Tensor tf32x3_matmul(const at::Tensor& a, const at::Tensor& b, bool ta, bool tb, double alpha, const at::Tensor& status) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == at::kFloat && b.scalar_type() == at::kFloat &&
+                  a.dim() == 3 && b.dim() == 3 && a.is_contiguous() && b.is_contiguous() && a.size(0) == b.size(0),
+              "tf32x3_matmul: contiguous fp32 [batch, rows, cols] CUDA tensors");
+  const int64_t batch = a.size(0);
+  const int64_t M = ta ? a.size(2) : a.size(1), K = ta ? a.size(1) : a.size(2);
+  const int64_t N = tb ? b.size(1) : b.size(2), Kb = tb ? b.size(2) : b.size(1);
+  TORCH_CHECK(K == Kb, "tf32x3_matmul: inner dimensions differ");
+  c10::cuda::CUDAGuard guard(a.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int64_t kp = hb::tf32_split_kp(K), ldc = (N + 3) / 4 * 4;
+  at::Tensor a3 = at::empty({batch, M, 3 * kp}, a.options()), b3 = at::empty({batch, N, 3 * kp}, a.options());
+  at::Tensor c = at::empty({batch, M, ldc}, a.options());
+  check(hb::launch_tf32_split(a.data_ptr<float>(), a.size(2), a.size(1) * a.size(2), (int)a.size(1), (int)a.size(2),
+                              (int)batch, ta ? 1 : 0, 0, a3.data_ptr<float>(), stream), "tf32 split A");
+  // B as the K-major [N, K] operand: b given as [K, N] must be transposed, b given as [N, K] is used as it is
+  check(hb::launch_tf32_split(b.data_ptr<float>(), b.size(2), b.size(1) * b.size(2), (int)b.size(1), (int)b.size(2),
+                              (int)batch, tb ? 0 : 1, 1, b3.data_ptr<float>(), stream), "tf32 split B");
+  check(hb::launch_tf32_gemm(a3.data_ptr<float>(), b3.data_ptr<float>(), (int)M, (int)N, (int)K, (int)batch, (float)alpha,
+                             c.data_ptr<float>(), ldc, M * ldc, status.data_ptr<int>(), stream), "tf32 gemm");
+  return ldc == N ? c : c.narrow(2, 0, N);
+}
+
 // LayerNorm over the last dimension of a contiguous fp32 tensor.  Returns (y, mean, rstd); y is bf16 when asked.
 std::vector<at::Tensor> layer_norm_fwd(const at::Tensor& x, const at::Tensor& gamma, const at::Tensor& beta, double eps,
                                        bool out_bf16) {
@@ -244,6 +270,7 @@ std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("tf32x3_matmul", &tf32x3_matmul);
   m.def("layer_norm_fwd", &layer_norm_fwd);
   m.def("layer_norm_bwd", &layer_norm_bwd);
   m.def("layer_norm_supported", &hb::layer_norm_supported);

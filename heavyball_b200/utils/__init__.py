@@ -8,6 +8,9 @@ switches, which are read at call time:
 * ``default_division_backend`` / ``atan2_scale`` — guarded division flavour
 * ``dither_steps`` — number of uniform draws summed for stochastic rounding
 * ``fast_qr`` — on CUDA, orthogonalise eigenbasis refreshes with batched panel-wise Cholesky QR instead of Householder QR
+* ``graph_qr`` — replay that QR from a CUDA graph per shape (about 800 small launches otherwise)
+* ``tensor_core_matmul`` — on sm_100a, fp32 matrix products of SOAP / PSGD with all dimensions >= 128 use the
+  3-term split-tf32 tensor-core kernel (relative error about 2^-21) instead of fp32 SIMT library GEMMs
 * ``compile_mode`` / ``dynamic`` / ``compile_mode_recommended_to_none`` — accepted for source
   compatibility; there is no tracing compiler here, fused execution is done by the sm_100a kernels
   in ``heavyball_b200.ops``.
@@ -24,6 +27,8 @@ default_division_backend = "eps_clamp"
 atan2_scale = 16.0
 dither_steps = 1
 fast_qr = True  # CUDA: eigenbasis refreshes use batched panel-wise Cholesky QR (Householder QR when that fails, and on CPU)
+graph_qr = True  # replay the panel-wise QR of a given shape from a CUDA graph (it is launch-bound)
+tensor_core_matmul = True  # CUDA: large fp32 products of the preconditioners run on the split-tf32 tcgen05 kernel
 tiny_bf16 = torch.finfo(torch.bfloat16).tiny
 
 from .core import *  # noqa: E402,F401,F403

@@ -449,3 +449,23 @@ def apply_flat_update(params: List[Tensor], update: Tensor):
 def apply_flat_add(params: List[Tensor], update: Tensor, alpha):
     for p, seg in _segments(params, update):
         stochastic_add_([p], [seg], alpha)
+
+
+# ---------------------------------------------------------------------------------------- tensor-core products
+
+
+def _tc_matmul(a: Tensor, b: Tensor, ta: bool = False, tb: bool = False):
+    """``op(a) @ op(b)`` on the split-tf32 tensor-core kernel when it applies (fp32 CUDA matrices on sm_100a with
+    every dimension >= 128 and ``utils.tensor_core_matmul`` on), else ``None``."""
+    if not (a.is_cuda and getattr(_settings(), "tensor_core_matmul", True)):
+        return None
+    from .. import ops
+
+    if not ops.matmul_supported(a, b):
+        return None
+    return ops.matmul3(a, b, ta, tb)
+
+
+def _mm(a: Tensor, b: Tensor, ta: bool = False, tb: bool = False) -> Tensor:
+    out = _tc_matmul(a, b, ta, tb)
+    return out if out is not None else (a.mT if ta else a) @ (b.mT if tb else b)

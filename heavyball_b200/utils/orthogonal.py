@@ -141,7 +141,7 @@ _QR_PANEL = 32
 _QR_PASSES = 3
 
 
-def _panel_cholesky_qr(x: Tensor):
+def _panel_cholesky_qr(x: Tensor, defer_check: bool = False):
     """Orthonormal basis of the columns of ``x`` (``... x n x k``, ``n >= k``), equal to the Q factor of
     Householder QR up to the sign of each column, built from batched GEMM / POTRF / TRSM only.
 
@@ -175,15 +175,57 @@ def _panel_cholesky_qr(x: Tensor):
             w = torch.linalg.solve_triangular(chol.mT, w, upper=True, left=False)
         q[..., j : j + _QR_PANEL] = w
     bad += (~torch.isfinite(q)).any()
+    if defer_check:  # caller reads the flag (used under CUDA graph capture, where the host cannot)
+        return q.reshape(*batch, n, k), bad
     if int(bad):
         return None
     return q.reshape(*batch, n, k)
 
 
+_qr_graphs = {}  # (device, shape) -> [calls seen, (graph, input, output, failure flag) | None | False]
+_QR_GRAPH_LIMIT = 16
+
+
+def _panel_qr_replayed(x: Tensor):
+    """:func:`_panel_cholesky_qr` through a CUDA graph per (device, shape): an eigenbasis refresh of a
+    1024-wide factor is about 800 small launches, and the host, not the GPU, sets its duration.  The first call
+    for a shape runs eagerly (library handles and workspaces get created outside capture), the second is
+    captured, later ones copy the input into the captured buffer and replay.  If capture is not possible the
+    shape stays on the eager path."""
+    key = (x.device, tuple(x.shape))
+    slot = _qr_graphs.get(key)
+    if slot is None:
+        if len(_qr_graphs) >= _QR_GRAPH_LIMIT:
+            return _panel_cholesky_qr(x)
+        slot = _qr_graphs[key] = [0, None]
+    slot[0] += 1
+    if slot[1] is False or slot[0] == 1 or torch.cuda.is_current_stream_capturing():
+        return _panel_cholesky_qr(x)
+    if slot[1] is None:
+        try:
+            static_in = x.clone()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_out, static_bad = _panel_cholesky_qr(static_in, defer_check=True)
+            slot[1] = (graph, static_in, static_out, static_bad)
+        except Exception as err:  # noqa: BLE001 - any capture failure means "do not graph this shape"
+            slot[1] = False
+            import warnings
+
+            warnings.warn(f"CUDA graph capture of the refresh QR failed ({type(err).__name__}); running it eagerly")
+            return _panel_cholesky_qr(x)
+    graph, static_in, static_out, static_bad = slot[1]
+    static_in.copy_(x)
+    graph.replay()
+    if int(static_bad):
+        return None
+    return static_out.clone()
+
+
 def _qr_basis(x: Tensor) -> Tensor:
     x32 = promote(x)
     if x32.is_cuda and _settings().fast_qr and x32.shape[-2] >= x32.shape[-1] >= 2 * _QR_PANEL:
-        q = _panel_cholesky_qr(x32)
+        q = _panel_qr_replayed(x32.contiguous()) if _settings().graph_qr else _panel_cholesky_qr(x32)
         if q is not None:
             return q
     return torch.linalg.qr(x32).Q

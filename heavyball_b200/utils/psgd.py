@@ -39,6 +39,7 @@ from .core import (
     warn_once,
 )
 from . import core as _core
+from .core import _mm, _tc_matmul
 from .orthogonal import inplace_orthogonal_
 from .soap import compiled_einsum, einsum_base
 
@@ -403,9 +404,9 @@ def _kron_apply(g: Tensor, factors, twice: bool) -> Tensor:
             moved = out.movedim(dim, -1)
             lead = moved.shape
             flat = moved.reshape(lead[0], -1, lead[-1])
-            flat = flat @ q.mT
+            flat = _mm(flat, q, False, True)
             if twice:
-                flat = flat @ q
+                flat = _mm(flat, q)
             out = flat.reshape(*lead[:-1], flat.shape[-1]).movedim(-1, dim)
         else:
             scale = q * q if twice else q
@@ -475,6 +476,16 @@ def psgd_calc_A_and_conjB(G: Tensor, Q, conjB: Optional[Tensor]):
     return A, conjB
 
 
+def _outer(expr: str, x: Tensor, mode: int) -> Tensor:
+    """Per-mode second moment ``x_(mode) x_(mode)^T`` (fp32); matrices take the tensor-core product."""
+    if x.ndim == 3:
+        x32 = promote(x)
+        out = _tc_matmul(x32, x32, mode == 1, mode == 0)
+        if out is not None:
+            return out
+    return promote(compiled_einsum(expr, x, x))
+
+
 def _update_lb(ell: Tensor, lb_state: Tensor, beta) -> Tensor:
     ell, old = promote(ell), promote(lb_state)
     ell = ell.maximum(old + (ell - old) * (1 - beta))
@@ -490,16 +501,16 @@ def psgd_update_precond(G, precond_lr, oq, store_triu_as_line, beta2, V, running
     exprs = calcG_expr(ndim_tuple(Q), G.ndim)
     A, conjB = psgd_calc_A_and_conjB(G, Q, V)
     del V
-    for oq_i, q, expr, lb in zip(oq, Q, exprs, running_lower_bound):
-        t1 = promote(compiled_einsum(expr, A, A))
-        t2 = promote(compiled_einsum(expr, conjB, conjB))
+    for mode, (oq_i, q, expr, lb) in enumerate(zip(oq, Q, exprs, running_lower_bound)):
+        t1 = _outer(expr, A, mode)
+        t2 = _outer(expr, conjB, mode)
         if q.ndim < 3:
             total = t1 + t2
             ell = _update_lb(total if q.ndim == 1 else total.amax(dim=-1), lb, lower_bount_beta)
             step = promote(q) * (t1 - t2)
         else:
             ell = _update_lb(max_eigenvalue_spd(t1 + t2, power_iter=power_iter), lb, lower_bount_beta)
-            step = (t1 - t2).triu() @ promote(q)
+            step = _mm((t1 - t2).triu(), promote(q))
             if store_triu_as_line:
                 step = triu_to_line([step])[0][1]
         target = oq_i[1] if isinstance(oq_i, tuple) else oq_i

@@ -21,6 +21,7 @@ import torch
 from torch import Tensor
 
 from .core import copy_stochastic_, promote, stochastic_lerp_
+from .core import _mm, _tc_matmul
 from .orthogonal import _qr_basis, inplace_orthogonal_
 
 einsum_base = string.ascii_lowercase
@@ -165,7 +166,13 @@ def update_ggt(grad, GG, max_precond_dim, precondition_1d, beta):
         return
     for idx, m in enumerate(GG):
         if isinstance(m, Tensor):
-            stochastic_lerp_(m, compiled_einsum(_mode_outer_expr(grad.dim() - 1, idx), grad, grad), 1 - beta)
+            outer = None
+            if grad.dim() == 3:  # (slot, rows, cols): G G^T / G^T G as one symmetric product
+                g32 = promote(grad)
+                outer = _tc_matmul(g32, g32, idx == 1, idx == 0)
+            if outer is None:
+                outer = compiled_einsum(_mode_outer_expr(grad.dim() - 1, idx), grad, grad)
+            stochastic_lerp_(m, outer, 1 - beta)
 
 
 def _kl_eigvals(q: Tensor, m: Tensor) -> Tensor:
@@ -236,6 +243,21 @@ def project(grad, Q, back: bool):
     factors = [f"...{(c + c.upper())[::-1 if back else 1]}" for q, c in zip(Q, modes) if q is not None]
     if not factors:
         return grad
+    if grad.dim() == 3 and grad.is_cuda:
+        res = promote(grad)
+        ok = True
+        for idx, q in enumerate(Q):
+            if q is None:
+                continue
+            q32 = promote(q)
+            # into the basis: Q_l^T G, G Q_r; out of it: Q_l G, G Q_r^T
+            nxt = _tc_matmul(q32, res, not back, False) if idx == 0 else _tc_matmul(res, q32, False, back)
+            if nxt is None:
+                ok = False
+                break
+            res = nxt
+        if ok:
+            return res.to(grad.dtype)
     joined = ",".join(factors)
     out = "".join(c.upper() if c.upper() in joined else c for c in modes)
     res = compiled_einsum(f"...{modes},{joined}->...{out}", promote(grad), *[promote(q) for q in Q if q is not None])
@@ -283,6 +305,18 @@ def _rotate_states(old_qs, new_qs, states):
     expr = _basis_change_expr(old_qs, new_qs, states[0].dim() - 1)
     if expr is None:
         return
+    if states[0].dim() == 3 and states[0].is_cuda:
+        # matrices: S' = R_l S R_r^T with R = Q_new^T Q_old per side, as tensor-core products
+        rots = [None if qo is None else _tc_matmul(promote(qn), promote(qo), True, False) for qo, qn in zip(old_qs, new_qs)]
+        if all(r is not None or qo is None for r, qo in zip(rots, old_qs)):
+            for s in states:
+                out = promote(s)
+                if rots[0] is not None:
+                    out = _mm(rots[0], out)
+                if len(rots) > 1 and rots[1] is not None:
+                    out = _mm(out, rots[1], False, True)
+                copy_stochastic_(s, out)
+            return
     old = [promote(q) for q in old_qs if q is not None]
     new = [promote(q) for q in new_qs if q is not None]
     for s in states:
@@ -314,13 +348,13 @@ def get_orthogonal_matrix_QR(GG, Q, *exp_avg, exp_avg_sq=None, heavy: bool = Fal
             continue
         m = promote(m.data)
         if heavy:
-            basis = inplace_orthogonal_(m @ promote(q.data), precise)
+            basis = inplace_orthogonal_(_mm(m, promote(q.data)), precise)
             ray = compiled_einsum("...ij,...ij->...j", basis, m @ basis)
             order = torch.argsort(ray, descending=True).unsqueeze(-2).expand_as(basis)
             new_qs.append(basis.gather(-1, order))
             continue
         q_old = promote(q.data)
-        power = m @ q_old
+        power = _mm(m, q_old)
         ray = compiled_einsum("...ij,...ij->...j", q_old, power)
         order = torch.argsort(ray, descending=True).unsqueeze(-2).expand_as(power)
         power.scatter_(-1, order, inplace_orthogonal_(power.gather(-1, order), precise))

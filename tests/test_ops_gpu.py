@@ -201,3 +201,47 @@ def test_graft_smoke():
     import __graft_entry__ as entry
 
     entry.smoke()
+
+
+@pytest.mark.parametrize("shape", [(1, 128, 128, 128), (3, 256, 384, 512), (2, 200, 130, 150), (1, 1024, 1024, 1024)])
+@pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (False, True), (True, True)])
+def test_split_tf32_matmul_is_close_to_fp32(shape, ta, tb):
+    """3-term tf32 product on tcgen05: error about 2^-21 relative to |a||b|, far below a single tf32 pass."""
+    batch, m, n, k = shape
+    torch.manual_seed(0)
+    a = torch.randn(batch, *((k, m) if ta else (m, k)), device="cuda")
+    b = torch.randn(batch, *((n, k) if tb else (k, n)), device="cuda")
+    a = a * torch.logspace(-3, 3, a.shape[-1], device="cuda")  # wide dynamic range along one axis
+    got = ops.matmul3(a, b, ta, tb, alpha=0.5)
+    ops.check_status()
+    a64, b64 = a.double(), b.double()
+    ref = 0.5 * ((a64.mT if ta else a64) @ (b64.mT if tb else b64))
+    bound = 0.5 * ((a64.mT if ta else a64).abs() @ (b64.mT if tb else b64).abs())
+    err = ((got.double() - ref).abs() / bound).max().item()
+    assert got.shape == ref.shape and got.dtype == torch.float32
+    assert err < 2e-6, err
+    fp32_err = ((0.5 * ((a.mT if ta else a) @ (b.mT if tb else b))).double() - ref).abs().div(bound).max().item()
+    assert err < max(50 * fp32_err, 2e-6)
+
+
+def test_peer_wait_gives_up_after_its_budget_and_reports_the_missing_rank():
+    """A flag that nothing sets: the wait returns after its clock budget with the absent rank in the status
+    word, and the context keeps working."""
+    import time
+
+    ext = ops.load()
+    flags = torch.zeros(2 * ext.MAX_WORLD, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    flags[0] = 1  # rank 0 has arrived at epoch 1, rank 1 never does
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    ext.peer_wait(flags, 0, 2, 1, 0.2, status)
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    assert status.item() == 2 + 1
+    assert 0.1 < waited < 2.0
+    status.zero_()
+    flags[1] = 1
+    ext.peer_wait(flags, 0, 2, 1, 0.2, status)
+    assert status.item() == 0
+    assert torch.ones(4, device="cuda").sum().item() == 4.0

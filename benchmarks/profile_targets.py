@@ -3,6 +3,9 @@
     python benchmarks/profile_targets.py opt_step_gpt2   # 3 optimizer steps, GPT-2-small parameter shapes
     python benchmarks/profile_targets.py ns_small        # Newton-Schulz on 8 x (1024 x 4096) bf16-sized work
     python benchmarks/profile_targets.py adam_small      # fused AdamW over 64M fp32 parameters (768 MB state+params)
+    python benchmarks/profile_targets.py ce_small        # cross-entropy fwd+bwd kernel, 4096 x 50304 bf16 logits (412 MB)
+    python benchmarks/profile_targets.py ln_small        # LayerNorm fwd + bwd kernels, 16384 x 768 fp32 (50 MB) x 4 tensors
+    python benchmarks/profile_targets.py tf32_small      # split-tf32 GEMM, 4 x (2048 x 2048 x 2048)
 
 Each case holds well under a few GB on the device and launches only a handful of kernels.
 """
@@ -70,5 +73,78 @@ def adam_small():
     torch.cuda.profiler.stop()
 
 
+def _timed(fn, reps=5):
+    """Median CUDA-event time of ``fn`` in microseconds, with a 256 MB L2 flush before each repetition."""
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    times = []
+    for _ in range(reps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3)
+    return sorted(times)[len(times) // 2]
+
+
+def ce_small():
+    rows, vocab, padded = 4096, 50257, 50304
+    logits = (torch.randn(rows, padded, device="cuda") * 2).to(torch.bfloat16)
+    targets = torch.randint(0, vocab, (rows,), device="cuda")
+    scale = torch.full((1,), 1.0 / rows, device="cuda")
+    ext = ops.load()
+    work = logits.clone()
+    us = _timed(lambda: ext.cross_entropy_(work, targets, scale, vocab, -100))
+    gb = 2 * rows * padded * 2 / 1e9
+    print(f"cross_entropy {rows}x{padded}: {us:.1f} us, {gb / us * 1e6:.0f} GB/s of algorithmic traffic (1 read + 1 write)")
+    work.copy_(logits)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    ext.cross_entropy_(work, targets, scale, vocab, -100)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+
+
+def ln_small():
+    rows, d = 16384, 768
+    x = torch.randn(rows, d, device="cuda")
+    w, b = torch.rand(d, device="cuda") + 0.5, torch.randn(d, device="cuda")
+    dy = torch.randn(rows, d, device="cuda").to(torch.bfloat16)
+    ext = ops.load()
+    y, mean, rstd = ext.layer_norm_fwd(x, w, b, 1e-5, True)
+    us_f = _timed(lambda: ext.layer_norm_fwd(x, w, b, 1e-5, True))
+    us_b = _timed(lambda: ext.layer_norm_bwd(dy, x, w, mean, rstd))
+    print(f"layer_norm fwd {rows}x{d}: {us_f:.1f} us, {(rows * d * 6) / us_f / 1e3:.0f} GB/s (fp32 in, bf16 out)")
+    print(f"layer_norm bwd {rows}x{d}: {us_b:.1f} us, {(rows * d * 10) / us_b / 1e3:.0f} GB/s (bf16 dy + fp32 x in, fp32 dx out)")
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    ext.layer_norm_fwd(x, w, b, 1e-5, True)
+    ext.layer_norm_bwd(dy, x, w, mean, rstd)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+
+
+def tf32_small():
+    a = torch.randn(4, 2048, 2048, device="cuda")
+    b = torch.randn(4, 2048, 2048, device="cuda")
+    out = ops.matmul3(a, b)
+    us = _timed(lambda: ops.matmul3(a, b))
+    us_ref = _timed(lambda: torch.matmul(a, b))
+    flops = 2 * 4 * 2048**3
+    print(f"matmul3 4x2048^3: {us:.1f} us incl. both split passes = {flops / us / 1e6:.1f} useful TFLOP/s "
+          f"({3 * flops / us / 1e6:.1f} tf32 TFLOP/s issued); torch fp32 matmul {us_ref:.1f} us = {flops / us_ref / 1e6:.1f} TFLOP/s")
+    err = (out.double() - a.double() @ b.double()).abs().max().item()
+    ref_err = (torch.matmul(a, b).double() - a.double() @ b.double()).abs().max().item()
+    print(f"max abs error vs fp64: ours {err:.3e}, torch fp32 {ref_err:.3e}")
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    ops.matmul3(a, b)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    ops.check_status()
+
+
 if __name__ == "__main__":
-    {"opt_step_gpt2": opt_step_gpt2, "ns_small": ns_small, "adam_small": adam_small}[sys.argv[1]]()
+    {"opt_step_gpt2": opt_step_gpt2, "ns_small": ns_small, "adam_small": adam_small, "ce_small": ce_small,
+     "ln_small": ln_small, "tf32_small": tf32_small}[sys.argv[1]]()

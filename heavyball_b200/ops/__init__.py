@@ -266,7 +266,7 @@ def matmul_supported(a: torch.Tensor, b: torch.Tensor) -> bool:
 
 def matmul3(a: torch.Tensor, b: torch.Tensor, trans_a: bool = False, trans_b: bool = False, alpha: float = 1.0) -> torch.Tensor:
     """``alpha * op(a) @ op(b)`` for fp32 matrices (optionally batched, equal leading shapes) on the tf32 tensor
-    cores with the 3-term split (relative error about 2^-21; plain tf32 gives 2^-11, fp32 SIMT 2^-24)."""
+    cores with the 3-term split (measured error about 2^-18 of ``|a| @ |b|``; one tf32 pass gives 2^-11, fp32 SIMT 2^-21)."""
     lead = a.shape[:-2]
     if b.shape[:-2] != lead:
         lead = torch.broadcast_shapes(a.shape[:-2], b.shape[:-2])

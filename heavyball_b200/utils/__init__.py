@@ -10,7 +10,7 @@ switches, which are read at call time:
 * ``fast_qr`` — on CUDA, orthogonalise eigenbasis refreshes with batched panel-wise Cholesky QR instead of Householder QR
 * ``graph_qr`` — replay that QR from a CUDA graph per shape (about 800 small launches otherwise)
 * ``tensor_core_matmul`` — on sm_100a, fp32 matrix products of SOAP / PSGD with all dimensions >= 128 use the
-  3-term split-tf32 tensor-core kernel (relative error about 2^-21) instead of fp32 SIMT library GEMMs
+  3-term split-tf32 tensor-core kernel (error about 2^-18 of ``|a| @ |b|``) instead of fp32 SIMT library GEMMs
 * ``compile_mode`` / ``dynamic`` / ``compile_mode_recommended_to_none`` — accepted for source
   compatibility; there is no tracing compiler here, fused execution is done by the sm_100a kernels
   in ``heavyball_b200.ops``.

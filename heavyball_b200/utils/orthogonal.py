@@ -156,13 +156,14 @@ def _panel_cholesky_qr(x: Tensor, defer_check: bool = False):
     ``|Q^T Q - I|`` at fp32 rounding level for spectra spanning 20 decades with an arbitrary ``Q_old``.
 
     Returns ``None`` when a panel's Gram matrix is not positive definite or the result is not finite
-    (e.g. an all-zero input); the caller then uses Householder QR.  One host synchronisation, at the end."""
+    (e.g. an all-zero input); the caller then uses Householder QR.  One host synchronisation, at the end.
+    With ``defer_check`` nothing is read on the host: the result comes back with one failure count per matrix."""
     batch, (n, k) = x.shape[:-2], x.shape[-2:]
     a = x.reshape(-1, n, k)
     tiny = torch.finfo(a.dtype).tiny
     a = a / a.norm(dim=-2, keepdim=True).clamp_(min=tiny)
     q = torch.empty_like(a)
-    bad = torch.zeros((), dtype=torch.int32, device=a.device)
+    bad = torch.zeros(a.shape[0], dtype=torch.int32, device=a.device)
     for j in range(0, k, _QR_PANEL):
         w = a[..., j : j + _QR_PANEL]
         done = q[..., :j]
@@ -171,13 +172,13 @@ def _panel_cholesky_qr(x: Tensor, defer_check: bool = False):
                 w = torch.baddbmm(w, done, done.mT @ w, alpha=-1.0)
             w = w / w.norm(dim=-2, keepdim=True).clamp_(min=tiny)
             chol, info = torch.linalg.cholesky_ex(w.mT @ w)
-            bad += info.ne(0).sum()
+            bad += info.ne(0)
             w = torch.linalg.solve_triangular(chol.mT, w, upper=True, left=False)
         q[..., j : j + _QR_PANEL] = w
-    bad += (~torch.isfinite(q)).any()
-    if defer_check:  # caller reads the flag (used under CUDA graph capture, where the host cannot)
+    bad += (~torch.isfinite(q)).flatten(1).any(dim=1)
+    if defer_check:  # caller reads the flags (used under CUDA graph capture, where the host cannot)
         return q.reshape(*batch, n, k), bad
-    if int(bad):
+    if int(bad.sum()):
         return None
     return q.reshape(*batch, n, k)
 
@@ -186,12 +187,15 @@ _qr_graphs = {}  # (device, shape) -> [calls seen, (graph, input, output, failur
 _QR_GRAPH_LIMIT = 16
 
 
-def _panel_qr_replayed(x: Tensor):
+def _panel_qr_replayed(x: Tensor, fallback: Tensor = None):
     """:func:`_panel_cholesky_qr` through a CUDA graph per (device, shape): an eigenbasis refresh of a
     1024-wide factor is about 800 small launches, and the host, not the GPU, sets its duration.  The first call
     for a shape runs eagerly (library handles and workspaces get created outside capture), the second is
     captured, later ones copy the input into the captured buffer and replay.  If capture is not possible the
-    shape stays on the eager path."""
+    shape stays on the eager path.
+
+    ``fallback`` (same shape, orthonormal columns - the basis being refreshed) makes a replay free of host
+    synchronisation: a matrix whose factorisation failed keeps its ``fallback`` columns, chosen on the device."""
     key = (x.device, tuple(x.shape))
     slot = _qr_graphs.get(key)
     if slot is None:
@@ -217,15 +221,20 @@ def _panel_qr_replayed(x: Tensor):
     graph, static_in, static_out, static_bad = slot[1]
     static_in.copy_(x)
     graph.replay()
-    if int(static_bad):
+    if fallback is not None:
+        failed = static_bad.view(*x.shape[:-2], 1, 1) > 0
+        return torch.where(failed, fallback.to(static_out.dtype), static_out)
+    if int(static_bad.sum()):
         return None
     return static_out.clone()
 
 
-def _qr_basis(x: Tensor) -> Tensor:
+def _qr_basis(x: Tensor, fallback: Tensor = None) -> Tensor:
+    """Q factor of ``x``.  ``fallback``: orthonormal matrix to keep where the fast factorisation fails (see
+    :func:`_panel_qr_replayed`); without it a failure costs a host synchronisation and Householder QR."""
     x32 = promote(x)
     if x32.is_cuda and _settings().fast_qr and x32.shape[-2] >= x32.shape[-1] >= 2 * _QR_PANEL:
-        q = _panel_qr_replayed(x32.contiguous()) if _settings().graph_qr else _panel_cholesky_qr(x32)
+        q = _panel_qr_replayed(x32.contiguous(), fallback) if _settings().graph_qr else _panel_cholesky_qr(x32)
         if q is not None:
             return q
     return torch.linalg.qr(x32).Q

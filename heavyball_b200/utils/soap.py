@@ -357,7 +357,12 @@ def get_orthogonal_matrix_QR(GG, Q, *exp_avg, exp_avg_sq=None, heavy: bool = Fal
         power = _mm(m, q_old)
         ray = compiled_einsum("...ij,...ij->...j", q_old, power)
         order = torch.argsort(ray, descending=True).unsqueeze(-2).expand_as(power)
-        power.scatter_(-1, order, inplace_orthogonal_(power.gather(-1, order), precise))
+        if str(getattr(precise, "value", precise)) == "qr":
+            # the old basis in the new column order is what a factor keeps if its factorisation fails
+            basis = _qr_basis(power.gather(-1, order), fallback=q_old.gather(-1, order))
+        else:
+            basis = inplace_orthogonal_(power.gather(-1, order), precise)
+        power.scatter_(-1, order, basis)
         new_qs.append(power)
 
     if ref is not None:

@@ -8,7 +8,7 @@ switches, which are read at call time:
 * ``default_division_backend`` / ``atan2_scale`` — guarded division flavour
 * ``dither_steps`` — number of uniform draws summed for stochastic rounding
 * ``fast_qr`` — on CUDA, orthogonalise eigenbasis refreshes with batched panel-wise Cholesky QR instead of Householder QR
-* ``graph_qr`` — replay that QR from a CUDA graph per shape (about 800 small launches otherwise)
+* ``graph_qr`` — replay that QR from a CUDA graph per shape (several hundred small launches otherwise)
 * ``tensor_core_matmul`` — on sm_100a, fp32 matrix products of SOAP / PSGD with all dimensions >= 128 use the
   3-term split-tf32 tensor-core kernel (error about 2^-18 of ``|a| @ |b|``) instead of fp32 SIMT library GEMMs
 * ``compile_mode`` / ``dynamic`` / ``compile_mode_recommended_to_none`` — accepted for source

@@ -36,6 +36,7 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--no-clocks", action="store_true", help="do not run the nvidia-smi clock sampler (diagnostics)")
     ap.add_argument("--trace-steps", action="store_true", help="also print every timed step's device time to stderr")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="gpt2-small", choices=sorted(CONFIGS))
@@ -226,10 +227,16 @@ def main():
         return float(t.item())
 
     sampler = ClockSampler(local)
-    if rank == 0:
+    if rank == 0 and not args.no_clocks:
         sampler.start()
     for i in range(args.warmup):
         train_step(dev_tokens[i % n_host])
+    # Python's cyclic collector pauses one rank for milliseconds at unpredictable steps, and in data-parallel runs
+    # every rank then waits for it: collect now, keep it off while timing (both arms)
+    import gc
+
+    gc.collect()
+    gc.disable()
     barrier()
 
     # ---- phase 1: device-timed, inputs already on the GPU
@@ -253,7 +260,7 @@ def main():
         per_step = [a.elapsed_time(b) for a, b in zip([start] + marks[:-1], marks)]
         print(f"rank {rank} step ms: " + " ".join(f"{t:.1f}" for t in per_step), file=sys.stderr)
     n_launch = launches.count if launches is not None else None
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop() if (rank == 0 and not args.no_clocks) else None
     step_ms = max_over_ranks(start.elapsed_time(stop) / args.steps)
 
     # ---- optimizer step alone (same state, gradients from one backward), device-timed
@@ -292,6 +299,7 @@ def main():
             "d2h_bytes_per_step": 4,
         }
 
+    gc.enable()
     if args.impl == "ours":
         from heavyball_b200 import ops
 

@@ -1,12 +1,13 @@
 // Softmax cross-entropy over bf16 logits, forward and backward in one pass over HBM.
 //
-// One CTA owns one row.  Pass 1 streams the row with 16-byte loads and keeps a running (max, sum of
-// exponentials) per thread, merged across the CTA; pass 2 streams the same row again (it is still in L2: a row
-// of 50k bf16 logits is 100 KB) and overwrites it with the gradient of the mean loss,
-// (softmax - onehot) * scale[0], so the logits buffer becomes the dlogits buffer and no fp32 copy of the
-// logits ever exists.  Columns >= vocab are padding (the leading dimension is rounded up so that rows start
-// on 16-byte boundaries and the producing GEMM stays on its aligned path): they are skipped in pass 1 and
-// zeroed in pass 2.  Rows whose target equals ignore_index get zero loss and zero gradient.
+// One CTA owns one row and sweeps it three times with 16-byte accesses: the maximum (packed bf16 max, from
+// DRAM), the sum of exponentials, and the write of the gradient of the mean loss, (softmax - onehot) * scale[0];
+// the second and third sweep hit L2 (a row of 50k bf16 logits is 100 KB).  The logits buffer becomes the
+// dlogits buffer and no fp32 copy of the logits ever exists.  Columns >= vocab are padding (the leading
+// dimension is rounded up so that rows start on 16-byte boundaries and the producing GEMM stays on its aligned
+// path): they are skipped by the reductions and zeroed by the write.  Rows whose target equals ignore_index get
+// zero loss and zero gradient.  Separate sweeps keep the inner loops free of bounds checks and running-maximum
+// rescaling: the kernel is issue-bound (two ex2 per element), not DRAM-bound.
 //
 // DRAM traffic: one read and one write of the logits, against about eight of each for the chain
 // cast-to-fp32 / log_softmax / nll_loss / their backward kernels / cast-back that it replaces.
@@ -20,18 +21,6 @@ namespace {
 constexpr int kThreads = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 
-struct MaxSum {
-  float m, s;  // running maximum (natural units), sum of exp(x - m)
-};
-
-__device__ __forceinline__ MaxSum merge(MaxSum a, MaxSum b) {
-  const float m = fmaxf(a.m, b.m);
-  // exp2f(-inf) = 0 covers the empty state (m = -inf, s = 0) as long as the merged maximum is finite
-  const float sa = (a.m == -INFINITY) ? 0.f : a.s * exp2f((a.m - m) * kLog2e);
-  const float sb = (b.m == -INFINITY) ? 0.f : b.s * exp2f((b.m - m) * kLog2e);
-  return {m, sa + sb};
-}
-
 __device__ __forceinline__ void unpack8(const uint4& v, float (&x)[8]) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
@@ -42,6 +31,26 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&x)[8]) {
   }
 }
 
+// Sum (or maximum) over the CTA of one float per thread; every thread gets the result.  `scratch` holds kThreads / 32 floats.
+template <bool kMax>
+__device__ __forceinline__ float block_reduce(float v, float* scratch) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float o = __shfl_xor_sync(0xffffffffu, v, off);
+    v = kMax ? fmaxf(v, o) : v + o;
+  }
+  __syncthreads();  // scratch may still be read from a previous reduction
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = scratch[threadIdx.x & (kThreads / 32 - 1)];
+#pragma unroll
+  for (int off = kThreads / 64; off > 0; off >>= 1) {
+    const float o = __shfl_xor_sync(0xffffffffu, r, off);
+    r = kMax ? fmaxf(r, o) : r + o;
+  }
+  return r;
+}
+
 __global__ void __launch_bounds__(kThreads) ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits,
                                                               const long long* __restrict__ targets,
                                                               float* __restrict__ loss,
@@ -49,76 +58,80 @@ __global__ void __launch_bounds__(kThreads) ce_fwd_bwd_kernel(__nv_bfloat16* __r
                                                               long long ignore_index) {
   const long long row = blockIdx.x;
   __nv_bfloat16* x = logits + row * (long long)ld;
+  uint4* xv = reinterpret_cast<uint4*>(x);
   const long long target = targets[row];
   const int n_vec = ld >> 3;
-  const bool ignored = target == ignore_index || target < 0 || target >= vocab;
+  const int full_vec = vocab >> 3;  // vectors [0, full_vec) hold only real columns; at most one more is partly padding
+  __shared__ float scratch[kThreads / 32];
 
-  __shared__ MaxSum warp_part[kThreads / 32];
-  __shared__ MaxSum total;
-
-  MaxSum acc{-INFINITY, 0.f};
-  if (!ignored) {
-    for (int v = threadIdx.x; v < n_vec; v += kThreads) {
-      float f[8];
-      unpack8(reinterpret_cast<const uint4*>(x)[v], f);
-      const int base = v << 3;
-      float vmax = -INFINITY;
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        if (base + i < vocab) vmax = fmaxf(vmax, f[i]);
-      if (vmax == -INFINITY) continue;  // vector lies entirely in the padding
-      const float m = fmaxf(acc.m, vmax);
-      float s = (acc.m == -INFINITY) ? 0.f : acc.s * exp2f((acc.m - m) * kLog2e);
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        if (base + i < vocab) s += exp2f((f[i] - m) * kLog2e);
-      acc = {m, s};
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      MaxSum other{__shfl_xor_sync(0xffffffffu, acc.m, off), __shfl_xor_sync(0xffffffffu, acc.s, off)};
-      acc = merge(acc, other);
-    }
-    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = acc;
-    __syncthreads();
-    if (threadIdx.x < 32) {
-      MaxSum p = threadIdx.x < kThreads / 32 ? warp_part[threadIdx.x] : MaxSum{-INFINITY, 0.f};
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) {
-        MaxSum other{__shfl_xor_sync(0xffffffffu, p.m, off), __shfl_xor_sync(0xffffffffu, p.s, off)};
-        p = merge(p, other);
-      }
-      if (threadIdx.x == 0) total = p;
-    }
-    __syncthreads();
+  if (target == ignore_index || target < 0 || target >= vocab) {  // no loss, no gradient
+    if (threadIdx.x == 0) loss[row] = 0.f;
+    for (int v = threadIdx.x; v < n_vec; v += kThreads) xv[v] = make_uint4(0, 0, 0, 0);
+    return;
   }
 
-  const float row_max = ignored ? 0.f : total.m;
-  const float inv_sum = ignored ? 0.f : 1.f / total.s;
-  const float g = ignored ? 0.f : scale[0];
-  if (threadIdx.x == 0)
-    loss[row] = ignored ? 0.f : (logf(total.s) + row_max - __bfloat162float(x[target]));
-  __syncthreads();  // x[target] is read before any thread overwrites it
-
-  const int tvec = ignored ? -1 : (int)(target >> 3);
-  for (int v = threadIdx.x; v < n_vec; v += kThreads) {
-    uint4 out = make_uint4(0, 0, 0, 0);
-    if (!ignored) {
-      float f[8];
-      unpack8(reinterpret_cast<const uint4*>(x)[v], f);
-      const int base = v << 3;
-      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float p = (base + i < vocab) ? exp2f((f[i] - row_max) * kLog2e) * inv_sum : 0.f;
-        if (v == tvec && base + i == (int)target) p -= 1.f;
-        f[i] = p * g;
-      }
-#pragma unroll
-      for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-    }
-    reinterpret_cast<uint4*>(x)[v] = out;
+  // sweep 1 (from DRAM): row maximum, on packed bf16 pairs (max is exact in any precision)
+  __nv_bfloat162 m2 = __float2bfloat162_rn(-INFINITY);
+  for (int v = threadIdx.x; v < full_vec; v += kThreads) {
+    const uint4 q = xv[v];
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+    m2 = __hmax2(__hmax2(m2, h[0]), __hmax2(h[1], __hmax2(h[2], h[3])));
   }
+  float m = fmaxf(__low2float(m2), __high2float(m2));
+  if (threadIdx.x == 0 && (vocab & 7)) {  // the vector that straddles the end of the vocabulary
+    float f[8];
+    unpack8(xv[full_vec], f);
+    for (int i = 0; i < (vocab & 7); ++i) m = fmaxf(m, f[i]);
+  }
+  const float row_max = block_reduce<true>(m, scratch);
+  const float bias = -row_max * kLog2e;
+
+  // sweep 2 (from L2): sum of exponentials
+  float s = 0.f;
+  for (int v = threadIdx.x; v < full_vec; v += kThreads) {
+    float f[8];
+    unpack8(xv[v], f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += exp2f(fmaf(f[i], kLog2e, bias));
+  }
+  if (threadIdx.x == 0 && (vocab & 7)) {
+    float f[8];
+    unpack8(xv[full_vec], f);
+    for (int i = 0; i < (vocab & 7); ++i) s += exp2f(fmaf(f[i], kLog2e, bias));
+  }
+  const float total = block_reduce<false>(s, scratch);
+  const float g = scale[0];
+  const float coef = g / total;
+  const float x_target = __bfloat162float(x[target]);
+  __syncthreads();  // x[target] has been read by everyone before anyone overwrites the row
+  if (threadIdx.x == 0) loss[row] = logf(total) + row_max - x_target;
+
+  // sweep 3 (from L2): the row becomes softmax * g; the target entry is fixed up afterwards
+  for (int v = threadIdx.x; v < full_vec; v += kThreads) {
+    float f[8];
+    unpack8(xv[v], f);
+    uint4 out;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      h[i] = __floats2bfloat162_rn(exp2f(fmaf(f[2 * i], kLog2e, bias)) * coef, exp2f(fmaf(f[2 * i + 1], kLog2e, bias)) * coef);
+    xv[v] = out;
+  }
+  for (int v = full_vec + threadIdx.x; v < n_vec; v += kThreads) {  // padding (and the straddling vector)
+    float f[8];
+    unpack8(xv[v], f);
+    uint4 out;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = (v << 3) + 2 * i;
+      h[i] = __floats2bfloat162_rn(c < vocab ? exp2f(fmaf(f[2 * i], kLog2e, bias)) * coef : 0.f,
+                                   c + 1 < vocab ? exp2f(fmaf(f[2 * i + 1], kLog2e, bias)) * coef : 0.f);
+    }
+    xv[v] = out;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) x[target] = __float2bfloat16_rn(exp2f(fmaf(x_target, kLog2e, bias)) * coef - g);
 }
 
 }  // namespace

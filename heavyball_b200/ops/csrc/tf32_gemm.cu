@@ -149,36 +149,59 @@ __device__ __forceinline__ float tf32_hi(float x) {
 
 // One block moves a 64 x 64 tile of the source through shared memory and writes the three K segments of the
 // operand rows it covers.  k runs over the source columns (transpose = 0) or rows (transpose = 1); the range
-// [K, kp) of every segment is zero-filled.  Grid: (ceil(kp / 64), ceil(rows / 64), batch).
+// [K, kp) of every segment is zero-filled.  256 threads = 16 float4 lanes x 16 rows, four passes each way; global
+// accesses are 16 bytes wide (the source falls back to scalars when its rows are not 16-byte aligned).
+// Grid: (ceil(kp / 64), ceil(rows / 64), batch).
 __global__ void __launch_bounds__(256) tf32_split_kernel(const float* __restrict__ src, int64_t ld_src, int64_t stride_src,
                                                         int R, int C, int transpose, int role_b, float* __restrict__ dst,
                                                         int rows, int K, int kp) {
-  __shared__ float tile[64][65];
+  __shared__ float tile[64][65];  // [operand row][k]
   const float* s = src + (int64_t)blockIdx.z * stride_src;
   float* d = dst + (int64_t)blockIdx.z * rows * 3 * kp;
-  const int k0 = blockIdx.x * 64, r0 = blockIdx.y * 64;  // operand coordinates of the tile
-  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
-  // fill tile[operand row][k]; reads are coalesced along the source's contiguous dimension
-  for (int i = ty; i < 64; i += 4) {
-    if (!transpose) {
-      const int r = r0 + i, k = k0 + tx;
-      tile[i][tx] = (r < R && k < C) ? s[(int64_t)r * ld_src + k] : 0.f;
-    } else {
-      const int k = k0 + i, r = r0 + tx;  // source row = k, source column = operand row
-      tile[tx][i] = (k < R && r < C) ? s[(int64_t)k * ld_src + r] : 0.f;
+  const int k0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
+  const int lane4 = (threadIdx.x & 15) * 4, line = threadIdx.x >> 4;
+  const bool vec_ok = (ld_src & 3) == 0 && (stride_src & 3) == 0 && (((uintptr_t)src) & 15) == 0;
+  // source tile: `line` walks the source rows, `lane4` the (contiguous) source columns
+  const int src_row0 = transpose ? k0 : r0, src_col0 = transpose ? r0 : k0;
+#pragma unroll
+  for (int pass = 0; pass < 4; ++pass) {
+    const int lr = line + 16 * pass, sr = src_row0 + lr, sc = src_col0 + lane4;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (sr < R) {
+      const float* row = s + (int64_t)sr * ld_src;
+      if (vec_ok && sc + 3 < C) {
+        const float4 t = *reinterpret_cast<const float4*>(row + sc);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (sc + e < C) v[e] = row[sc + e];
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (transpose) tile[lane4 + e][lr] = v[e];
+      else tile[lr][lane4 + e] = v[e];
     }
   }
   __syncthreads();
-  for (int i = ty; i < 64; i += 4) {
-    const int r = r0 + i, k = k0 + tx;
-    if (r >= rows || k >= kp) continue;
-    const float x = tile[i][tx];
-    // lo is rounded to tf32 here (the tensor core would truncate it): halves the error of the two cross terms
-    const float hi = tf32_hi(x), lo = tf32_hi(x - hi);
+#pragma unroll
+  for (int pass = 0; pass < 4; ++pass) {
+    const int lr = line + 16 * pass, r = r0 + lr, k = k0 + lane4;
+    if (r >= rows || k >= kp) continue;  // kp is a multiple of 32, so a float4 never straddles it
+    float hi[4], lo[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float x = tile[lr][lane4 + e];
+      // lo is rounded to tf32 here (the tensor core would truncate it): halves the error of the two cross terms
+      hi[e] = tf32_hi(x);
+      lo[e] = tf32_hi(x - hi[e]);
+    }
+    const float4 h4 = make_float4(hi[0], hi[1], hi[2], hi[3]), l4 = make_float4(lo[0], lo[1], lo[2], lo[3]);
     float* row = d + (int64_t)r * 3 * kp + k;
-    row[0] = hi;
-    row[kp] = role_b ? lo : hi;
-    row[2 * kp] = role_b ? hi : lo;
+    *reinterpret_cast<float4*>(row) = h4;
+    *reinterpret_cast<float4*>(row + kp) = role_b ? l4 : h4;
+    *reinterpret_cast<float4*>(row + 2 * kp) = role_b ? h4 : l4;
   }
 }
 

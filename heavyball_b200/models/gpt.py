@@ -13,7 +13,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops.nn import LayerNorm, linear_cross_entropy
+from ..ops.nn import LayerNorm, Linear, linear, linear_cross_entropy
 
 
 @dataclass
@@ -39,11 +39,11 @@ class Block(nn.Module):
         d, ff = cfg.d_model, cfg.d_ff or 4 * cfg.d_model
         self.n_head = cfg.n_head
         self.ln1 = LayerNorm(d)
-        self.qkv = nn.Linear(d, 3 * d)
-        self.proj = nn.Linear(d, d)
+        self.qkv = Linear(d, 3 * d)
+        self.proj = Linear(d, d)
         self.ln2 = LayerNorm(d)
-        self.fc = nn.Linear(d, ff)
-        self.out = nn.Linear(ff, d)
+        self.fc = Linear(d, ff)
+        self.out = Linear(ff, d)
 
     def forward(self, x):
         B, T, D = x.shape
@@ -53,7 +53,7 @@ class Block(nn.Module):
         h = self.ln1(x)
         w, b = self.qkv.weight, self.qkv.bias
         q, k, v = (
-            F.linear(h, w[i * D : (i + 1) * D], b[i * D : (i + 1) * D]).view(B, T, self.n_head, D // self.n_head).transpose(1, 2)
+            linear(h, w[i * D : (i + 1) * D], b[i * D : (i + 1) * D]).view(B, T, self.n_head, D // self.n_head).transpose(1, 2)
             for i in range(3)
         )
         a = F.scaled_dot_product_attention(q, k, v, is_causal=True)

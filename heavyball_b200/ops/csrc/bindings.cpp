@@ -7,6 +7,7 @@
 #include <optional>
 #include <vector>
 
+#include "colsum.h"
 #include "cross_entropy.h"
 #include "fused_chain.h"
 #include "layer_norm.h"
@@ -231,6 +232,18 @@ at::Tensor tf32x3_matmul(const at::Tensor& a, const at::Tensor& b, bool ta, bool
   return ldc == N ? c : c.narrow(2, 0, N);
 }
 
+// fp32 column sums of a contiguous bf16 matrix [rows, cols] (cols % 8 == 0).
+at::Tensor colsum_bf16(const at::Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kBFloat16 && x.is_contiguous() &&
+                  x.size(1) % 8 == 0 && aligned16(x.data_ptr()), "colsum_bf16: contiguous bf16 [rows, cols], cols % 8 == 0");
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor out = at::empty({x.size(1)}, x.options().dtype(at::kFloat));
+  at::Tensor partial = at::empty({hb::colsum_splits(), x.size(1)}, out.options());
+  check(hb::launch_colsum_bf16(x.data_ptr(), x.size(0), (int)x.size(1), partial.data_ptr<float>(), out.data_ptr<float>(),
+                               at::cuda::getCurrentCUDAStream()), "colsum launch");
+  return out;
+}
+
 // LayerNorm over the last dimension of a contiguous fp32 tensor.  Returns (y, mean, rstd); y is bf16 when asked.
 std::vector<at::Tensor> layer_norm_fwd(const at::Tensor& x, const at::Tensor& gamma, const at::Tensor& beta, double eps,
                                        bool out_bf16) {
@@ -271,6 +284,7 @@ std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tf32x3_matmul", &tf32x3_matmul);
+  m.def("colsum_bf16", &colsum_bf16);
   m.def("layer_norm_fwd", &layer_norm_fwd);
   m.def("layer_norm_bwd", &layer_norm_bwd);
   m.def("layer_norm_supported", &hb::layer_norm_supported);

@@ -102,3 +102,39 @@ def test_layer_norm_module_keeps_state_dict_and_falls_back():
     assert set(ln.state_dict()) == {"weight", "bias"}
     x = torch.randn(4, 100, device="cuda")
     assert torch.allclose(ln(x), F.layer_norm(x, (100,), ln.weight, ln.bias, ln.eps))
+
+
+@pytest.mark.parametrize("rows,cols", [(16384, 768), (1000, 3072), (7, 8), (33, 200)])
+def test_column_sum_kernel_matches_fp32_sum(rows, cols):
+    torch.manual_seed(0)
+    x = torch.randn(rows, cols, device="cuda").to(torch.bfloat16)
+    got = ops.load().colsum_bf16(x)
+    ref = x.double().sum(0)
+    assert got.dtype == torch.float32 and got.shape == (cols,)
+    assert torch.allclose(got.double(), ref, atol=1e-3 * rows**0.5, rtol=1e-5)
+
+
+def test_linear_under_autocast_matches_framework_linear():
+    from heavyball_b200.ops.nn import linear
+
+    torch.manual_seed(0)
+    x = torch.randn(4, 96, 256, device="cuda", requires_grad=True)
+    w = (torch.randn(384, 256, device="cuda") * 0.05).requires_grad_()
+    b = torch.randn(384, device="cuda").requires_grad_()
+    dy = torch.randn(4, 96, 384, device="cuda")
+    x2, w2, b2 = (t.detach().clone().requires_grad_() for t in (x, w, b))
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = linear(x, w, b)
+        y2 = F.linear(x2, w2, b2)
+    assert y.dtype == torch.bfloat16 and torch.equal(y, y2)
+    y.backward(dy.to(y.dtype))
+    y2.backward(dy.to(y.dtype))
+    assert x.grad.dtype == torch.float32 and w.grad.dtype == torch.float32 and b.grad.dtype == torch.float32
+    assert torch.allclose(x.grad, x2.grad, atol=1e-2, rtol=1e-2)
+    assert torch.allclose(w.grad, w2.grad, atol=5e-2, rtol=1e-2)
+    # the kernel sums in fp32 and rounds once; the framework path rounds the bf16 result of its own fp32 sum
+    assert torch.allclose(b.grad, b2.grad, atol=0.15, rtol=1e-2)
+    exact = dy.to(torch.bfloat16).double().sum((0, 1))
+    assert (b.grad.double() - exact).abs().max() <= (b2.grad.double() - exact).abs().max() + 0.1
+    # outside autocast nothing changes
+    assert torch.equal(linear(x.detach(), w.detach(), b.detach()), F.linear(x.detach(), w.detach(), b.detach()))

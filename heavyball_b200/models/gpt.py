@@ -13,7 +13,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops.nn import LayerNorm, Linear, linear, linear_cross_entropy
+from ..ops.nn import CastCache, LayerNorm, Linear, _bf16_training, linear, linear_cross_entropy
 
 
 @dataclass
@@ -51,10 +51,11 @@ class Block(nn.Module):
         # is then dense in [B, T, H, hd] order, so neither the attention output nor the three gradients coming
         # back from the attention kernel need a strided copy / concatenation (about 0.3 ms per layer otherwise).
         h = self.ln1(x)
-        w, b = self.qkv.weight, self.qkv.bias
+        w, b, w16, b16 = self.qkv.weight, self.qkv.bias, self.qkv.w16, self.qkv.b16
         q, k, v = (
-            linear(h, w[i * D : (i + 1) * D], b[i * D : (i + 1) * D]).view(B, T, self.n_head, D // self.n_head).transpose(1, 2)
-            for i in range(3)
+            linear(h, w[sl], b[sl], None if w16 is None else w16[sl], None if b16 is None else b16[sl])
+            .view(B, T, self.n_head, D // self.n_head).transpose(1, 2)
+            for sl in (slice(i * D, (i + 1) * D) for i in range(3))
         )
         a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         x = x + self.proj(a.transpose(1, 2).reshape(B, T, D))
@@ -74,6 +75,7 @@ class GPT(nn.Module):
         if cfg.tie_embeddings:
             self.head.weight = self.wte.weight
         self.apply(self._init)
+        self._casts = CastCache(self)
         with torch.no_grad():  # padding rows: never indexed, zero probability, zero gradient
             self.wte.weight[cfg.vocab_size :].zero_()
             self.head.weight[cfg.vocab_size :].zero_()
@@ -86,6 +88,7 @@ class GPT(nn.Module):
 
     def forward(self, idx, targets=None):
         B, T = idx.shape
+        self._casts.refresh(_bf16_training(self.wte.weight))
         x = self.wte(idx) + self.wpe(torch.arange(T, device=idx.device))
         for blk in self.blocks:
             x = blk(x)

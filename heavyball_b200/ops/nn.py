@@ -114,50 +114,89 @@ class LayerNorm(torch.nn.LayerNorm):
 
 
 class _LinearFn(torch.autograd.Function):
-    """``x @ w^T + b`` whose backward takes the bias gradient from the column-sum kernel."""
+    """``x @ w^T + b`` computed from bf16 copies ``w16`` / ``b16`` of the fp32 parameters; gradients are routed
+    to the fp32 parameters, the bias gradient comes from the column-sum kernel."""
 
     @staticmethod
-    @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.bfloat16)
-    def forward(ctx, x, weight, bias):
-        ctx.save_for_backward(x, weight)
-        ctx.has_bias = bias is not None
-        return F.linear(x, weight, bias)
+    def forward(ctx, x, weight, bias, w16, b16):
+        x16 = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+        ctx.save_for_backward(x16, w16)
+        ctx.x_dtype = x.dtype
+        return F.linear(x16, w16, b16)
 
     @staticmethod
-    @torch.amp.custom_bwd(device_type="cuda")
     def backward(ctx, dy):
-        x, weight = ctx.saved_tensors
+        x16, w16 = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.dtype != torch.bfloat16:
+            dy2 = dy2.to(torch.bfloat16)
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
-            dx = (dy2 @ weight).reshape(x.shape)
+            dx = (dy2 @ w16).reshape(x16.shape).to(ctx.x_dtype)
         if ctx.needs_input_grad[1]:
-            dw = dy2.mT @ x.reshape(-1, x.shape[-1])
-        if ctx.has_bias and ctx.needs_input_grad[2]:
-            if dy2.dtype == torch.bfloat16 and dy2.shape[1] % 8 == 0 and dy2.data_ptr() % 16 == 0:
-                db = load().colsum_bf16(dy2).to(dy2.dtype)
+            dw = dy2.mT @ x16.reshape(-1, x16.shape[-1])
+        if ctx.needs_input_grad[2]:
+            if dy2.shape[1] % 8 == 0 and dy2.data_ptr() % 16 == 0:
+                db = load().colsum_bf16(dy2)
                 launch_counter.count += 2
             else:
-                db = dy2.sum(0)
-        return dx, dw, db
+                db = dy2.float().sum(0)
+        return dx, dw, db, None, None
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+def _bf16_training(x: torch.Tensor) -> bool:
+    return x.is_cuda and torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16 and available()
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, w16: torch.Tensor | None = None,
+           b16: torch.Tensor | None = None) -> torch.Tensor:  # fmt: skip
     """``F.linear`` for training under bf16 autocast on sm_100a: identical forward, but the bias gradient comes from
     a dedicated column-sum kernel (the framework's generic reduction runs at a third of memory bandwidth on the
-    ``[tokens, features]`` gradients of a transformer).  Elsewhere, and without a bias, it is ``F.linear``."""
-    if (
-        bias is not None and x.is_cuda and torch.is_autocast_enabled("cuda") and torch.is_grad_enabled()
-        and torch.get_autocast_dtype("cuda") == torch.bfloat16 and available()
-    ):  # fmt: skip
-        return _LinearFn.apply(x, weight, bias)
+    ``[tokens, features]`` gradients of a transformer).  ``w16`` / ``b16`` are bf16 copies of the parameters when
+    the caller keeps some (:class:`CastCache`); otherwise they are made here.  Elsewhere, and without a bias, it is
+    ``F.linear``."""
+    if bias is not None and _bf16_training(x):
+        if w16 is None:
+            w16, b16 = weight.detach().to(torch.bfloat16), bias.detach().to(torch.bfloat16)
+        return _LinearFn.apply(x, weight, bias, w16, b16)
     return F.linear(x, weight, bias)
 
 
 class Linear(torch.nn.Linear):
     """``torch.nn.Linear`` (same parameters and state dict) running :func:`linear`."""
 
+    w16 = b16 = None  # bf16 copies handed out by a CastCache, valid for the current forward pass
+
     def forward(self, x):
-        return linear(x, self.weight, self.bias)
+        return linear(x, self.weight, self.bias, self.w16, self.b16)
+
+
+class CastCache:
+    """bf16 copies of the parameters of a model's :class:`Linear` layers in one slab, made with one
+    multi-tensor copy per forward pass instead of one small cast kernel per parameter per use (about 300 launches
+    of ~3 us for a 12-layer transformer).  The copies are plain attributes of the layers (``w16`` / ``b16``): not
+    parameters, not buffers, absent from ``state_dict``."""
+
+    def __init__(self, model: torch.nn.Module):
+        self.layers = [m for m in model.modules() if isinstance(m, Linear) and m.bias is not None]
+
+    def refresh(self, active: bool) -> None:
+        if not active or not self.layers:
+            for m in self.layers:
+                m.w16 = m.b16 = None
+            return
+        params = [p for m in self.layers for p in (m.weight, m.bias)]
+        total = sum((p.numel() + 7) // 8 * 8 for p in params)
+        # a fresh slab every time: the previous one may be held by an autograd graph that has not run backward yet
+        # (the caching allocator hands the same memory back once that graph is gone)
+        slab = torch.empty(total, dtype=torch.bfloat16, device=params[0].device)
+        views, off = [], 0
+        for p in params:
+            views.append(slab[off : off + p.numel()].view(p.shape))
+            off += (p.numel() + 7) // 8 * 8  # 16-byte aligned starts
+        with torch.no_grad():
+            torch._foreach_copy_(views, params)
+        for i, m in enumerate(self.layers):
+            m.w16, m.b16 = views[2 * i], views[2 * i + 1]

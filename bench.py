@@ -36,6 +36,8 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--cuda-profiler", action="store_true",
+                    help="bracket the device-timed steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     ap.add_argument("--no-clocks", action="store_true", help="do not run the nvidia-smi clock sampler (diagnostics)")
     ap.add_argument("--trace-steps", action="store_true", help="also print every timed step's device time to stderr")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -246,6 +248,8 @@ def main():
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     sampler.begin()
+    if args.cuda_profiler:
+        torch.cuda.profiler.start()
     start.record()
     last = None
     marks = []
@@ -256,6 +260,8 @@ def main():
             marks[-1].record()
     stop.record()
     barrier()
+    if args.cuda_profiler:
+        torch.cuda.profiler.stop()
     if marks:
         per_step = [a.elapsed_time(b) for a, b in zip([start] + marks[:-1], marks)]
         print(f"rank {rank} step ms: " + " ".join(f"{t:.1f}" for t in per_step), file=sys.stderr)

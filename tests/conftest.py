@@ -14,9 +14,10 @@ def pytest_configure(config):
 
 
 def reference_path():
-    """Directory that makes ``import heavyball`` resolve to the unmodified reference, or None."""
-    for cand in (os.path.join(ROOT, "baseline", "_ref"), "/root/reference"):
-        if os.path.isdir(os.path.join(cand, "heavyball")):
+    """Directory that makes ``import heavyball`` resolve to the unmodified reference, or None: the in-tree
+    install under ``baseline/_ref``, else a checkout named by the ``HEAVYBALL_REFERENCE`` environment variable."""
+    for cand in (os.path.join(ROOT, "baseline", "_ref"), os.environ.get("HEAVYBALL_REFERENCE", "")):
+        if cand and os.path.isdir(os.path.join(cand, "heavyball")):
             return cand
     return None
 

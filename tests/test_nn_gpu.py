@@ -138,3 +138,29 @@ def test_linear_under_autocast_matches_framework_linear():
     assert (b.grad.double() - exact).abs().max() <= (b2.grad.double() - exact).abs().max() + 0.1
     # outside autocast nothing changes
     assert torch.equal(linear(x.detach(), w.detach(), b.detach()), F.linear(x.detach(), w.detach(), b.detach()))
+
+
+def test_cast_cache_follows_parameter_updates_made_by_the_kernels():
+    """The optimizer kernels write parameters through raw pointers (no autograd version bump): the bf16 copies
+    must still be current in the next forward pass."""
+    import heavyball_b200 as hb
+    from heavyball_b200.models import GPT, GPTConfig
+
+    torch.manual_seed(0)
+    model = GPT(GPTConfig(n_layer=1, n_head=2, d_model=128, vocab_size=512, seq_len=16)).cuda()
+    opt = hb.AdamW(model.parameters(), lr=1e-2)
+    x = torch.randint(0, 512, (2, 16), device="cuda")
+    for _ in range(2):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = model(x, x)
+        fc = model.blocks[0].fc
+        assert fc.w16 is not None and torch.equal(fc.w16, fc.weight.detach().to(torch.bfloat16))
+        assert torch.equal(fc.b16, fc.bias.detach().to(torch.bfloat16))
+        before = fc.weight.detach().clone()
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        assert not torch.equal(before, fc.weight.detach())
+    assert not any("16" in k for k in model.state_dict())
+    model(x)  # outside autocast the copies are dropped and F.linear runs
+    assert model.blocks[0].fc.w16 is None

@@ -4,6 +4,7 @@ KV heads).  They exist to exercise the optimizers on the shapes named by the ben
 attention core is ``torch.nn.functional.scaled_dot_product_attention``."""
 
 from .gpt import GPT, GPTConfig, gpt2_small, gpt_350m
+from .graphs import graph_forward_backward
 from .llama import Llama, LlamaConfig, llama_1p3b, llama3_8b
 
 
@@ -21,5 +22,5 @@ def split_param_groups(model):
 
 __all__ = [
     "GPT", "GPTConfig", "gpt2_small", "gpt_350m", "Llama", "LlamaConfig", "llama_1p3b", "llama3_8b",
-    "split_param_groups",
+    "split_param_groups", "graph_forward_backward",
 ]  # fmt: skip

@@ -199,7 +199,8 @@ bool layer_norm_supported(int D) { return D > 0 && D % 128 == 0 && D / 128 <= 8;
 
 int layer_norm_partial_ctas(long long rows) {
   const long long want = (rows + kWarps - 1) / kWarps;
-  return (int)(want < 148 * 2 ? (want < 1 ? 1 : want) : 148 * 2);
+  // 149 registers x 128 threads: three CTAs fit on an SM
+  return (int)(want < 148 * 3 ? (want < 1 ? 1 : want) : 148 * 3);
 }
 
 #define HB_LN_SWITCH(D, CALL)            \

@@ -164,3 +164,31 @@ def test_cast_cache_follows_parameter_updates_made_by_the_kernels():
     assert not any("16" in k for k in model.state_dict())
     model(x)  # outside autocast the copies are dropped and F.linear runs
     assert model.blocks[0].fc.w16 is None
+
+
+def test_graphed_forward_backward_matches_eager_launches():
+    import copy
+
+    from heavyball_b200.models import GPT, GPTConfig, graph_forward_backward
+
+    torch.manual_seed(0)
+    eager = GPT(GPTConfig(n_layer=2, n_head=2, d_model=128, vocab_size=1001, seq_len=32)).cuda()
+    graphed = copy.deepcopy(eager)
+    xs = [torch.randint(0, 1001, (4, 33), device="cuda") for _ in range(3)]
+    graph_forward_backward(graphed, (xs[0][:, :-1], xs[0][:, 1:]))
+    for x in xs:
+        losses = []
+        for model in (eager, graphed):
+            model.zero_grad(set_to_none=True)
+            with torch.autocast("cuda", dtype=torch.bfloat16, cache_enabled=False):
+                loss = model(x[:, :-1], x[:, 1:])
+            loss.backward()
+            losses.append(loss.detach().float())
+        assert torch.allclose(losses[0], losses[1], atol=1e-5)
+        for (name, p), q in zip(eager.named_parameters(), graphed.parameters()):
+            assert p.grad is not None and q.grad is not None, name
+            assert torch.allclose(p.grad, q.grad, atol=1e-4, rtol=1e-3), name
+        with torch.no_grad():  # move both models the same way, through raw parameter writes as an optimizer would
+            for p, q in zip(eager.parameters(), graphed.parameters()):
+                p.sub_(0.1 * p.grad)
+                q.sub_(0.1 * q.grad)

@@ -1,16 +1,21 @@
-"""Model-side fused ops used by ``heavyball_b200.models``: the output head's projection + softmax
-cross-entropy with the loss kernel writing the logits' gradient in place.
+"""Model-side ops used by ``heavyball_b200.models`` for bf16-autocast training on sm_100a.  Each has the
+framework op it replaces as its fallback (CPU, other dtypes, unsupported shapes).
 
-The forward pass computes ``logits = h @ W^T`` once in bf16 (library GEMM), then one kernel
-(``csrc/cross_entropy.cu``) reads each row twice (the second read hits L2), returns the per-row loss and
-overwrites the logits with ``(softmax - onehot) / n_valid``.  The backward pass is two GEMMs on that
-buffer.  Compared with ``F.cross_entropy(logits.float(), targets)`` under autocast this removes the fp32
-copy of the logits, ``log_softmax`` and its backward, and the cast back: about 26 GB of HBM traffic per
-step for 16 x 1024 tokens and a 50k vocabulary, against 3.3 GB here.
-
-``W`` may have more rows than the vocabulary (rows rounded up to a multiple of 64 keep the GEMMs on their
-aligned tensor-core kernels: a 50 257-row head runs on a legacy unaligned path about 9x slower); the
-extra columns get zero probability and zero gradient.
+``linear_cross_entropy``
+    The output head's projection + softmax cross-entropy.  ``logits = h @ W^T`` is computed once in bf16
+    (library GEMM); one kernel (``csrc/cross_entropy.cu``) sweeps each row three times (the last two from L2),
+    returns the per-row loss and overwrites the logits with ``(softmax - onehot) / n_valid``; backward is two
+    GEMMs on that buffer.  Against ``F.cross_entropy(logits.float(), targets)`` this removes the fp32 copy of
+    the logits, ``log_softmax``, its backward and the cast back: about 26 GB of HBM traffic per step for
+    16 x 1024 tokens and a 50k vocabulary, against 3.3 GB.  ``W`` may have more rows than the vocabulary (a
+    row count that is a multiple of 64 keeps the GEMMs on their aligned tensor-core kernels: a 50 257-row head
+    runs on a legacy unaligned path about 9x slower); the extra columns get zero probability and zero gradient.
+``layer_norm`` / ``LayerNorm``
+    One kernel each way (``csrc/layer_norm.cu``); under autocast the output is written, and the incoming
+    gradient read, in bf16 directly.
+``linear`` / ``Linear`` / ``CastCache``
+    ``F.linear`` whose bias gradient comes from a column-sum kernel (``csrc/colsum.cu``) and whose bf16 weights
+    come from one multi-tensor cast per forward pass.
 """
 
 from __future__ import annotations

@@ -282,6 +282,7 @@ def main():
             marks.append(torch.cuda.Event(enable_timing=True))
             marks[-1].record()
     stop.record()
+    last = last.detach().clone()  # under CUDA graphs the returned loss is a static buffer that later replays overwrite
     barrier()
     if args.cuda_profiler:
         torch.cuda.profiler.stop()

@@ -223,10 +223,11 @@ def main():
 
     launches_per_step = None
     if args.impl == "ours":
-        # one eager step: creates the optimizer state and counts this repository's kernel launches per step (inside
+        # two eager steps: create the optimizer state, then count this repository's kernel launches per step (inside
         # CUDA graphs the same kernels run, but the Python-side counter only sees them at capture time)
+        train_step(dev_tokens[0])  # first step: state initialisation takes its own path
         launches.reset()
-        train_step(dev_tokens[0])
+        train_step(dev_tokens[1 % n_host])
         launches_per_step = launches.count
         if args.graphs != "off":
             try:

@@ -18,8 +18,12 @@ def graph_forward_backward(model: torch.nn.Module, example_inputs: tuple, autoca
 
     ``example_inputs``: tensors shaped like every later call's arguments.  Call the result under
     ``torch.autocast("cuda", dtype=autocast_dtype, cache_enabled=False)`` - capture runs under the same context,
-    and the autocast weight cache must stay off because cached casts would not be replayed."""
+    and the autocast weight cache must stay off because cached casts would not be replayed.  The value returned
+    by a call (the loss) is a static buffer that the next call overwrites: copy it if it must outlive the step."""
     if not all(isinstance(t, torch.Tensor) and t.is_cuda for t in example_inputs):
         raise ValueError("graph capture needs CUDA tensors as example inputs")
+    # the capture keeps its sample arguments as the graphs' static input buffers: give it private copies, so that
+    # later calls never write into the caller's tensors (nor into views that overlap each other)
+    static_inputs = tuple(t.detach().clone() for t in example_inputs)
     with torch.autocast("cuda", dtype=autocast_dtype, cache_enabled=False):
-        return torch.cuda.make_graphed_callables(model, tuple(example_inputs), num_warmup_iters=warmup)
+        return torch.cuda.make_graphed_callables(model, static_inputs, num_warmup_iters=warmup)

@@ -13,6 +13,7 @@
 #include "layer_norm.h"
 #include "ns_gemm.h"
 #include "peer_sync.h"
+#include "skinny.h"
 #include "tf32_gemm.h"
 
 namespace py = pybind11;
@@ -232,6 +233,35 @@ at::Tensor tf32x3_matmul(const at::Tensor& a, const at::Tensor& b, bool ta, bool
   return ldc == N ? c : c.narrow(2, 0, N);
 }
 
+// Partial products X^T W over the long dimension: x = first `m` columns of the contiguous [batch, n, k] tensor `base`,
+// w: contiguous [batch, n, p], p <= 32.  Returns [splits, batch, m, p]; sum over dim 0 for the product.
+at::Tensor tall_t_mul(const at::Tensor& base, int64_t m, const at::Tensor& w) {
+  TORCH_CHECK(base.is_cuda() && w.is_cuda() && base.scalar_type() == at::kFloat && w.scalar_type() == at::kFloat &&
+                  base.dim() == 3 && w.dim() == 3 && base.is_contiguous() && w.is_contiguous() &&
+                  base.size(0) == w.size(0) && base.size(1) == w.size(1) && w.size(2) <= 32 && m >= 0 && m <= base.size(2),
+              "tall_t_mul: contiguous fp32 [batch, n, k] and [batch, n, p <= 32]");
+  c10::cuda::CUDAGuard guard(base.device());
+  const int64_t batch = base.size(0), n = base.size(1), k = base.size(2), p = w.size(2);
+  at::Tensor c = at::empty({hb::tall_splits((int)n), batch, m, p}, base.options());
+  check(hb::launch_tall_t_mul(base.data_ptr<float>(), k, n * k, w.data_ptr<float>(), p, n * p, (int)batch, (int)n, (int)m,
+                              (int)p, c.data_ptr<float>(), at::cuda::getCurrentCUDAStream()), "tall_t_mul launch");
+  return c;
+}
+
+// w -= base[:, :, :m] @ sum(c, 0), in place.
+void tall_update_(const at::Tensor& base, int64_t m, const at::Tensor& c, at::Tensor& w) {
+  TORCH_CHECK(base.is_cuda() && base.scalar_type() == at::kFloat && base.dim() == 3 && base.is_contiguous() &&
+                  w.scalar_type() == at::kFloat && w.dim() == 3 && w.is_contiguous() && c.is_contiguous() &&
+                  c.scalar_type() == at::kFloat && c.dim() == 4 && c.size(0) == hb::tall_splits((int)base.size(1)) &&
+                  c.size(1) == base.size(0) && c.size(2) == m && c.size(3) == w.size(2) && w.size(2) <= 32 &&
+                  w.size(0) == base.size(0) && w.size(1) == base.size(1) && m <= base.size(2),
+              "tall_update_: shapes do not match tall_t_mul's");
+  c10::cuda::CUDAGuard guard(base.device());
+  const int64_t batch = base.size(0), n = base.size(1), k = base.size(2), p = w.size(2);
+  check(hb::launch_tall_update(base.data_ptr<float>(), k, n * k, c.data_ptr<float>(), w.data_ptr<float>(), p, n * p,
+                               (int)batch, (int)n, (int)m, (int)p, at::cuda::getCurrentCUDAStream()), "tall_update launch");
+}
+
 // fp32 column sums of a contiguous bf16 matrix [rows, cols] (cols % 8 == 0).
 at::Tensor colsum_bf16(const at::Tensor& x) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kBFloat16 && x.is_contiguous() &&
@@ -285,6 +315,8 @@ std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tf32x3_matmul", &tf32x3_matmul);
   m.def("colsum_bf16", &colsum_bf16);
+  m.def("tall_t_mul", &tall_t_mul);
+  m.def("tall_update_", &tall_update_);
   m.def("layer_norm_fwd", &layer_norm_fwd);
   m.def("layer_norm_bwd", &layer_norm_bwd);
   m.def("layer_norm_supported", &hb::layer_norm_supported);

@@ -1,0 +1,18 @@
+// Tall-and-skinny fp32 products for block Gram-Schmidt panels (see skinny.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+namespace hb {
+
+// number of partial products tall_t_mul writes for a contraction length n
+int tall_splits(int n);
+
+// C[s][b] = partial X[b]^T W[b] over the s-th part of the n rows; C: [tall_splits(n), batch, m, p] fp32, p <= 32.
+cudaError_t launch_tall_t_mul(const float* X, long long ldx, long long strideX, const float* W, long long ldw,
+                              long long strideW, int batch, int n, int m, int p, float* C, cudaStream_t stream);
+
+// W[b] -= X[b] * sum_s C[s][b], in place.
+cudaError_t launch_tall_update(const float* X, long long ldx, long long strideX, const float* C, float* W, long long ldw,
+                               long long strideW, int batch, int n, int m, int p, cudaStream_t stream);
+
+}  // namespace hb

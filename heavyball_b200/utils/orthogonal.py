@@ -169,15 +169,21 @@ def _panel_cholesky_qr(x: Tensor, defer_check: bool = False):
     a = a / a.norm(dim=-2, keepdim=True).clamp_(min=tiny)
     q = torch.empty_like(a)
     bad = torch.zeros(a.shape[0], dtype=torch.int32, device=a.device)
+    ext = _skinny_kernels(a)
     for j in range(0, k, _QR_PANEL):
         w = a[..., j : j + _QR_PANEL]
+        w = w.contiguous() if ext is not None else w
         done = q[..., :j]
         for _ in range(_QR_PASSES):
-            if j:
+            if ext is not None and not w.is_contiguous():  # the triangular solve may hand back a column-major panel
+                w = w.contiguous()
+            if j and ext is not None:  # w -= done (done^T w), both products split over the long dimension
+                ext.tall_update_(q, j, ext.tall_t_mul(q, j, w), w)
+            elif j:
                 w = torch.baddbmm(w, done, done.mT @ w, alpha=-1.0)
             # column scales come from the Gram diagonal (no separate reduction over the long dimension):
             # chol(D G D) with D = diag(G)^-1/2 is the factor of the unit-column panel w D
-            gram = w.mT @ w
+            gram = ext.tall_t_mul(w, w.shape[-1], w).sum(0) if ext is not None else w.mT @ w
             d = gram.diagonal(dim1=-2, dim2=-1).clamp(min=tiny).rsqrt()
             chol, info = torch.linalg.cholesky_ex(gram * d.unsqueeze(-1) * d.unsqueeze(-2))
             bad += info.ne(0)
@@ -189,6 +195,15 @@ def _panel_cholesky_qr(x: Tensor, defer_check: bool = False):
     if int(bad.sum()):
         return None
     return q.reshape(*batch, n, k)
+
+
+def _skinny_kernels(a: Tensor):
+    """The extension when its tall-and-skinny product kernels apply (fp32 CUDA input on sm_100a), else ``None``."""
+    if not (a.is_cuda and a.dtype == torch.float32):
+        return None
+    from .. import ops
+
+    return ops.load() if ops.available() else None
 
 
 _qr_graphs = {}  # (device, shape) -> [calls seen, (graph, input, output, failure flag) | None | False]

@@ -94,3 +94,20 @@ def test_psgd_kron_steps_with_tensor_core_products_match_library_products():
     for x, y in zip(a, b):
         assert torch.isfinite(x).all()
         assert (x - y).abs().max().item() < 1e-3 * y.abs().max().item()
+
+
+@pytest.mark.parametrize("n,k,m,p", [(1024, 1024, 512, 32), (1000, 300, 7, 32), (130, 64, 64, 32), (4096, 256, 224, 20)])
+def test_tall_skinny_products_match_matmul(n, k, m, p):
+    ext = hb.ops.load()
+    torch.manual_seed(0)
+    base = torch.randn(3, n, k, device="cuda")
+    w = torch.randn(3, n, p, device="cuda")
+    parts = ext.tall_t_mul(base, m, w)
+    ref = base[..., :m].double().mT @ w.double()
+    assert parts.shape[1:] == (3, m, p)
+    assert torch.allclose(parts.sum(0).double(), ref, atol=1e-3, rtol=1e-4)
+    expected = w.double() - base[..., :m].double() @ ref
+    ext.tall_update_(base, m, parts, w)
+    assert torch.allclose(w.double(), expected, atol=2e-2, rtol=1e-4)  # entries are O(sqrt(n m)); fp32 accumulation
+    rel = (w.double() - expected).norm() / expected.norm()
+    assert rel < 1e-5

@@ -4,6 +4,10 @@ matrices by ``merge_dims`` before the Kronecker factors are built)."""
 import torch
 import torch.nn as nn
 
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # run from a checkout
 import heavyball_b200 as hb
 
 if __name__ == "__main__":

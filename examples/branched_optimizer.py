@@ -6,6 +6,10 @@
 import torch
 import torch.nn as nn
 
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # run from a checkout
 import heavyball_b200.chainable as C
 
 

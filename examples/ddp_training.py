@@ -13,6 +13,10 @@ import os
 import torch
 import torch.distributed as dist
 
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # run from a checkout
 import heavyball_b200 as hb
 from heavyball_b200.models import GPT, GPTConfig, split_param_groups
 from heavyball_b200.parallel import ddp

@@ -8,6 +8,10 @@ fp32 trajectory closely; plain ``storage_dtype="bfloat16"`` is cheaper (2 bytes)
 import torch
 import torch.nn as nn
 
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # run from a checkout
 import heavyball_b200 as hb
 
 

@@ -11,6 +11,10 @@ import time
 
 import torch
 
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # run from a checkout
 import heavyball_b200 as hb
 from heavyball_b200.models import GPT, GPTConfig, graph_forward_backward, split_param_groups
 

@@ -7,6 +7,10 @@ while keeping the indices - and therefore the checkpoint keys - of the existing 
 import torch
 import torch.nn as nn
 
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # run from a checkout
 import heavyball_b200 as hb
 
 if __name__ == "__main__":

@@ -248,20 +248,6 @@ at::Tensor tall_t_mul(const at::Tensor& base, int64_t m, const at::Tensor& w) {
   return c;
 }
 
-// w -= base[:, :, :m] @ sum(c, 0), in place.
-void tall_update_(const at::Tensor& base, int64_t m, const at::Tensor& c, at::Tensor& w) {
-  TORCH_CHECK(base.is_cuda() && base.scalar_type() == at::kFloat && base.dim() == 3 && base.is_contiguous() &&
-                  w.scalar_type() == at::kFloat && w.dim() == 3 && w.is_contiguous() && c.is_contiguous() &&
-                  c.scalar_type() == at::kFloat && c.dim() == 4 && c.size(0) == hb::tall_splits((int)base.size(1)) &&
-                  c.size(1) == base.size(0) && c.size(2) == m && c.size(3) == w.size(2) && w.size(2) <= 32 &&
-                  w.size(0) == base.size(0) && w.size(1) == base.size(1) && m <= base.size(2),
-              "tall_update_: shapes do not match tall_t_mul's");
-  c10::cuda::CUDAGuard guard(base.device());
-  const int64_t batch = base.size(0), n = base.size(1), k = base.size(2), p = w.size(2);
-  check(hb::launch_tall_update(base.data_ptr<float>(), k, n * k, c.data_ptr<float>(), w.data_ptr<float>(), p, n * p,
-                               (int)batch, (int)n, (int)m, (int)p, at::cuda::getCurrentCUDAStream()), "tall_update launch");
-}
-
 // fp32 column sums of a contiguous bf16 matrix [rows, cols] (cols % 8 == 0).
 at::Tensor colsum_bf16(const at::Tensor& x) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kBFloat16 && x.is_contiguous() &&
@@ -316,7 +302,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tf32x3_matmul", &tf32x3_matmul);
   m.def("colsum_bf16", &colsum_bf16);
   m.def("tall_t_mul", &tall_t_mul);
-  m.def("tall_update_", &tall_update_);
   m.def("layer_norm_fwd", &layer_norm_fwd);
   m.def("layer_norm_bwd", &layer_norm_bwd);
   m.def("layer_norm_supported", &hb::layer_norm_supported);

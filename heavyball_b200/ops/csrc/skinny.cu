@@ -1,14 +1,14 @@
-// Two fp32 kernels for block Gram-Schmidt with a narrow panel (the eigenbasis-refresh QR):
+// fp32 product over a long dimension for block Gram-Schmidt with a narrow panel (the eigenbasis-refresh QR):
 //
 //   tall_t_mul : C[b] = X[b]^T W[b]     X: [n, m] (leading dimension ldx), W: [n, p], p <= 32, contraction over the
 //                                       long dimension n.  The library's GEMM for this shape is a 32x32x16 SIMT
 //                                       kernel that walks n serially (18 us whatever m is); here n is split over
-//                                       CTAs and the kSplit partial products are kept apart (deterministic).
-//   tall_update: W[b] <- W[b] - X[b] (sum_s C_s[b])   the matching rank-m update, rows of W in parallel; it also
-//                                       adds up the partial products of tall_t_mul on the fly.
+//                                       CTAs and the partial products are kept apart (deterministic), to be summed
+//                                       by the caller.
 //
-// Both stage 32-wide tiles in shared memory and use plain FMAs: the products are tiny (at most 2 * 1024 * 1024 * 32
-// flops per matrix) and latency, not throughput, is what the panel loop pays for.
+// 32-wide tiles staged in shared memory, plain FMAs: the products are tiny (at most 2 * 1024 * 1024 * 32 flops per
+// matrix) and latency, not throughput, is what the panel loop pays for.  The matching rank-m update W -= X C has
+// plenty of row parallelism and stays a library GEMM (a version written here the same way was slower).
 #include "skinny.h"
 
 namespace hb {
@@ -53,47 +53,6 @@ __global__ void __launch_bounds__(256) tall_t_mul_kernel(const float* __restrict
   }
 }
 
-// grid: (ceil(n / 64), batch); block 256 = 32 (column of W) x 8 (row groups); each thread owns 8 rows
-__global__ void __launch_bounds__(256) tall_update_kernel(const float* __restrict__ X, long long ldx, long long strideX,
-                                                         const float* __restrict__ C, int splits, int batch,
-                                                         float* __restrict__ W, long long ldw, long long strideW,
-                                                         int n, int m, int p) {
-  __shared__ float xs[64][33];
-  __shared__ float cs[32][33];
-  const int b = blockIdx.y, r0 = blockIdx.x * 64;
-  const float* x = X + (long long)b * strideX;
-  float* w = W + (long long)b * strideW;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // rows r0 + ty + 8 i, column tx
-  for (int k0 = 0; k0 < m; k0 += 32) {
-    for (int i = ty; i < 64; i += 8) {
-      const int r = r0 + i;
-      xs[i][tx] = (r < n && k0 + tx < m) ? x[(long long)r * ldx + k0 + tx] : 0.f;
-    }
-    for (int i = ty; i < 32; i += 8) {
-      float s = 0.f;
-      if (k0 + i < m && tx < p)
-        for (int sp = 0; sp < splits; ++sp) s += C[(((long long)sp * batch + b) * m + k0 + i) * p + tx];
-      cs[i][tx] = s;
-    }
-    __syncthreads();
-#pragma unroll 8
-    for (int k = 0; k < 32; ++k) {
-      const float cv = cs[k][tx];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = fmaf(xs[ty + 8 * i][k], cv, acc[i]);
-    }
-    __syncthreads();
-  }
-  if (tx < p) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int r = r0 + ty + 8 * i;
-      if (r < n) w[(long long)r * ldw + tx] -= acc[i];
-    }
-  }
-}
-
 }  // namespace
 
 int tall_splits(int n) {
@@ -107,14 +66,6 @@ cudaError_t launch_tall_t_mul(const float* X, long long ldx, long long strideX, 
   const int splits = tall_splits(n);
   dim3 grid((m + 31) / 32, splits, batch);
   tall_t_mul_kernel<<<grid, 256, 0, stream>>>(X, ldx, strideX, W, ldw, strideW, n, m, p, C, splits);
-  return cudaGetLastError();
-}
-
-cudaError_t launch_tall_update(const float* X, long long ldx, long long strideX, const float* C, float* W, long long ldw,
-                               long long strideW, int batch, int n, int m, int p, cudaStream_t stream) {
-  if (batch == 0 || m == 0 || p == 0 || n == 0) return cudaSuccess;
-  dim3 grid((n + 63) / 64, batch);
-  tall_update_kernel<<<grid, 256, 0, stream>>>(X, ldx, strideX, C, tall_splits(n), batch, W, ldw, strideW, n, m, p);
   return cudaGetLastError();
 }
 

@@ -11,8 +11,4 @@ int tall_splits(int n);
 cudaError_t launch_tall_t_mul(const float* X, long long ldx, long long strideX, const float* W, long long ldw,
                               long long strideW, int batch, int n, int m, int p, float* C, cudaStream_t stream);
 
-// W[b] -= X[b] * sum_s C[s][b], in place.
-cudaError_t launch_tall_update(const float* X, long long ldx, long long strideX, const float* C, float* W, long long ldw,
-                               long long strideW, int batch, int n, int m, int p, cudaStream_t stream);
-
 }  // namespace hb

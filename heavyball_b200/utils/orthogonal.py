@@ -177,10 +177,9 @@ def _panel_cholesky_qr(x: Tensor, defer_check: bool = False):
         for _ in range(_QR_PASSES):
             if ext is not None and not w.is_contiguous():  # the triangular solve may hand back a column-major panel
                 w = w.contiguous()
-            if j and ext is not None:  # w -= done (done^T w), both products split over the long dimension
-                ext.tall_update_(q, j, ext.tall_t_mul(q, j, w), w)
-            elif j:
-                w = torch.baddbmm(w, done, done.mT @ w, alpha=-1.0)
+            if j:  # w -= done (done^T w); the inner product runs over the long dimension
+                coef = ext.tall_t_mul(q, j, w).sum(0) if ext is not None else done.mT @ w
+                w = torch.baddbmm(w, done, coef, alpha=-1.0)
             # column scales come from the Gram diagonal (no separate reduction over the long dimension):
             # chol(D G D) with D = diag(G)^-1/2 is the factor of the unit-column panel w D
             gram = ext.tall_t_mul(w, w.shape[-1], w).sum(0) if ext is not None else w.mT @ w

@@ -106,8 +106,3 @@ def test_tall_skinny_products_match_matmul(n, k, m, p):
     ref = base[..., :m].double().mT @ w.double()
     assert parts.shape[1:] == (3, m, p)
     assert torch.allclose(parts.sum(0).double(), ref, atol=1e-3, rtol=1e-4)
-    expected = w.double() - base[..., :m].double() @ ref
-    ext.tall_update_(base, m, parts, w)
-    assert torch.allclose(w.double(), expected, atol=2e-2, rtol=1e-4)  # entries are O(sqrt(n m)); fp32 accumulation
-    rel = (w.double() - expected).norm() / expected.norm()
-    assert rel < 1e-5

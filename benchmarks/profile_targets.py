@@ -6,6 +6,7 @@
     python benchmarks/profile_targets.py ce_small        # cross-entropy fwd+bwd kernel, 4096 x 50304 bf16 logits (412 MB)
     python benchmarks/profile_targets.py ln_small        # LayerNorm fwd + bwd kernels, 16384 x 768 fp32 (50 MB) x 4 tensors
     python benchmarks/profile_targets.py tf32_small      # split-tf32 GEMM, 4 x (2048 x 2048 x 2048)
+    python benchmarks/profile_targets.py qr_small        # panel-wise Cholesky QR of 8 x (1024 x 1024), eager launches
 
 Each case holds well under a few GB on the device and launches only a handful of kernels.
 """
@@ -145,6 +146,25 @@ def tf32_small():
     ops.check_status()
 
 
+def qr_small():
+    from heavyball_b200.utils.orthogonal import _panel_cholesky_qr
+
+    torch.manual_seed(0)
+    basis = torch.linalg.qr(torch.randn(8, 1024, 1024, device="cuda")).Q
+    gg = (basis * torch.logspace(0, -6, 1024, device="cuda")) @ basis.mT
+    power = gg @ torch.linalg.qr(basis + 1e-3 * torch.randn_like(basis)).Q
+    q = _panel_cholesky_qr(power)
+    us = _timed(lambda: _panel_cholesky_qr(power), reps=3)
+    err = (q.mT @ q - torch.eye(1024, device="cuda")).abs().max().item()
+    us_ref = _timed(lambda: torch.linalg.qr(power), reps=3)
+    print(f"panel QR 8x1024x1024: {us:.0f} us eager launches (library Householder QR {us_ref:.0f} us), |Q^T Q - I| = {err:.1e}")
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    _panel_cholesky_qr(power)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+
+
 if __name__ == "__main__":
-    {"opt_step_gpt2": opt_step_gpt2, "ns_small": ns_small, "adam_small": adam_small, "ce_small": ce_small,
+    {"qr_small": qr_small, "opt_step_gpt2": opt_step_gpt2, "ns_small": ns_small, "adam_small": adam_small, "ce_small": ce_small,
      "ln_small": ln_small, "tf32_small": tf32_small}[sys.argv[1]]()

@@ -6,66 +6,134 @@
 //                                       CTAs and the partial products are kept apart (deterministic), to be summed
 //                                       by the caller.
 //
-// 32-wide tiles staged in shared memory, plain FMAs: the products are tiny (at most 2 * 1024 * 1024 * 32 flops per
+// Tiles staged in shared memory, 8 x 4 register tiles, plain FMAs: the products are tiny (at most 2 * 1024 * 1024 * 32 flops per
 // matrix) and latency, not throughput, is what the panel loop pays for.  The matching rank-m update W -= X C has
 // plenty of row parallelism and stays a library GEMM (a version written here the same way was slower).
 #include "skinny.h"
 
+#include <stdint.h>
+
 namespace hb {
 namespace {
 
-constexpr int kRowsPerCta = 128;  // rows of the long dimension per CTA in tall_t_mul
+constexpr int kTileM = 128;   // columns of X (rows of the result) per CTA
+constexpr int kTileR = 64;    // rows of the long dimension staged at a time
+constexpr int kMaxSplits = 16;
 
-// grid: (ceil(m / 32), splits, batch); block: 256 threads = 32 (column of W) x 8 (row groups of X^T)
-__global__ void __launch_bounds__(256) tall_t_mul_kernel(const float* __restrict__ X, long long ldx, long long strideX,
+// grid: (ceil(m / 128), splits, batch); block: 128 threads = 16 (groups of 8 result rows) x 8 (groups of 4 columns).
+// Each thread keeps an 8 x 4 register tile: per staged row it reads 8 + 4 values from shared memory (three 16-byte
+// loads) for 32 FMAs.  A first version with one value per load and four FMAs was issue-bound at 20 us per call.
+template <bool kVec>
+__global__ void __launch_bounds__(128) tall_t_mul_kernel(const float* __restrict__ X, long long ldx, long long strideX,
                                                         const float* __restrict__ W, long long ldw, long long strideW,
                                                         int n, int m, int p, float* __restrict__ C, int splits) {
-  __shared__ float xs[kRowsPerCta][33];
-  __shared__ float ws[kRowsPerCta][33];
-  const int b = blockIdx.z, split = blockIdx.y, m0 = blockIdx.x * 32;
+  __shared__ __align__(16) float xs[kTileR][kTileM];
+  __shared__ __align__(16) float ws[kTileR][32];
+  const int b = blockIdx.z, split = blockIdx.y, m0 = blockIdx.x * kTileM;
   const float* x = X + (long long)b * strideX;
   const float* w = W + (long long)b * strideW;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // ty in 0..7
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};                    // outputs (m0 + ty + 8 i, tx)
+  const int t = threadIdx.x, tm = t >> 3, tp = t & 7;
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
   const int rows_per_split = (n + splits - 1) / splits;
   const int r_begin = split * rows_per_split, r_end = min(n, r_begin + rows_per_split);
-  for (int r0 = r_begin; r0 < r_end; r0 += kRowsPerCta) {
-    for (int i = ty; i < kRowsPerCta; i += 8) {
-      const int r = r0 + i;
-      const bool in = r < r_end;
-      xs[i][tx] = (in && m0 + tx < m) ? x[(long long)r * ldx + m0 + tx] : 0.f;
-      ws[i][tx] = (in && tx < p) ? w[(long long)r * ldw + tx] : 0.f;
+  for (int r0 = r_begin; r0 < r_end; r0 += kTileR) {
+    // stage X[r0 .. r0+63][m0 .. m0+127] and W[r0 .. r0+63][0 .. 31]; loads are issued before any is consumed
+    if (kVec) {
+      float4 xv[16], wv[4];
+#pragma unroll
+      for (int it = 0; it < 16; ++it) {  // 64 rows x 32 float4 per row, 128 threads
+        const int idx = t + 128 * it, rr = idx >> 5, c4 = (idx & 31) * 4;
+        const int r = r0 + rr, c = m0 + c4;
+        xv[it] = (r < r_end && c < m) ? *reinterpret_cast<const float4*>(x + (long long)r * ldx + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c + 3 >= m && c < m) {  // tail of the m range: mask the lanes past it
+          if (c + 1 >= m) xv[it].y = 0.f;
+          if (c + 2 >= m) xv[it].z = 0.f;
+          xv[it].w = 0.f;
+        }
+      }
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {  // 64 rows x 8 float4 per row
+        const int idx = t + 128 * it, rr = idx >> 3, c4 = (idx & 7) * 4;
+        const int r = r0 + rr;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < r_end && c4 < p) {
+          const float* src = w + (long long)r * ldw + c4;
+          v.x = src[0];
+          if (c4 + 1 < p) v.y = src[1];
+          if (c4 + 2 < p) v.z = src[2];
+          if (c4 + 3 < p) v.w = src[3];
+        }
+        wv[it] = v;
+      }
+#pragma unroll
+      for (int it = 0; it < 16; ++it) {
+        const int idx = t + 128 * it;
+        *reinterpret_cast<float4*>(&xs[idx >> 5][(idx & 31) * 4]) = xv[it];
+      }
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const int idx = t + 128 * it;
+        *reinterpret_cast<float4*>(&ws[idx >> 3][(idx & 7) * 4]) = wv[it];
+      }
+    } else {
+      for (int idx = t; idx < kTileR * kTileM; idx += 128) {
+        const int rr = idx >> 7, c = idx & 127, r = r0 + rr;
+        xs[rr][c] = (r < r_end && m0 + c < m) ? x[(long long)r * ldx + m0 + c] : 0.f;
+      }
+      for (int idx = t; idx < kTileR * 32; idx += 128) {
+        const int rr = idx >> 5, c = idx & 31, r = r0 + rr;
+        ws[rr][c] = (r < r_end && c < p) ? w[(long long)r * ldw + c] : 0.f;
+      }
     }
     __syncthreads();
-#pragma unroll 8
-    for (int i = 0; i < kRowsPerCta; ++i) {
-      const float wv = ws[i][tx];
+#pragma unroll 4
+    for (int rr = 0; rr < kTileR; ++rr) {
+      const float4 a0 = *reinterpret_cast<const float4*>(&xs[rr][tm * 8]);
+      const float4 a1 = *reinterpret_cast<const float4*>(&xs[rr][tm * 8 + 4]);
+      const float4 bv = *reinterpret_cast<const float4*>(&ws[rr][tp * 4]);
+      const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float bw[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
-      for (int k = 0; k < 4; ++k) acc[k] = fmaf(xs[i][ty + 8 * k], wv, acc[k]);
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bw[j], acc[i][j]);
     }
     __syncthreads();
   }
   float* c = C + ((long long)split * gridDim.z + b) * m * p;
 #pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const int row = m0 + ty + 8 * k;
-    if (row < m && tx < p) c[(long long)row * p + tx] = acc[k];
+  for (int i = 0; i < 8; ++i) {
+    const int row = m0 + tm * 8 + i;
+    if (row >= m) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int col = tp * 4 + j;
+      if (col < p) c[(long long)row * p + col] = acc[i][j];
+    }
   }
 }
 
 }  // namespace
 
-int tall_splits(int n) {
-  const int s = (n + 2 * kRowsPerCta - 1) / (2 * kRowsPerCta);
-  return s < 1 ? 1 : (s > 16 ? 16 : s);
+int tall_splits(int n) {  // two staged tiles of rows per CTA, up to 16 splits
+  const int s = (n + 2 * kTileR - 1) / (2 * kTileR);
+  return s < 1 ? 1 : (s > kMaxSplits ? kMaxSplits : s);
 }
 
 cudaError_t launch_tall_t_mul(const float* X, long long ldx, long long strideX, const float* W, long long ldw,
                               long long strideW, int batch, int n, int m, int p, float* C, cudaStream_t stream) {
   if (batch == 0 || m == 0 || p == 0) return cudaSuccess;
   const int splits = tall_splits(n);
-  dim3 grid((m + 31) / 32, splits, batch);
-  tall_t_mul_kernel<<<grid, 256, 0, stream>>>(X, ldx, strideX, W, ldw, strideW, n, m, p, C, splits);
+  dim3 grid((m + kTileM - 1) / kTileM, splits, batch);
+  const bool vec = (ldx % 4 == 0) && (strideX % 4 == 0) && ((reinterpret_cast<uintptr_t>(X) & 15) == 0);
+  if (vec)
+    tall_t_mul_kernel<true><<<grid, 128, 0, stream>>>(X, ldx, strideX, W, ldw, strideW, n, m, p, C, splits);
+  else
+    tall_t_mul_kernel<false><<<grid, 128, 0, stream>>>(X, ldx, strideX, W, ldw, strideW, n, m, p, C, splits);
   return cudaGetLastError();
 }
 

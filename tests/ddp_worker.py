@@ -1,8 +1,10 @@
 """Worker for the multi-GPU data-parallel test (launched by ``torch.distributed.run``).
 
-Trains a small GPT for a few steps on rank-specific data twice: with the peer-memory scheme and with
+Trains a small GPT for a few steps on rank-specific data: with the peer-memory scheme and with
 ``DistributedDataParallel`` + replicated optimizer.  Checks that (a) replicas are bit-identical under the
-peer scheme, (b) both schemes agree to rounding noise, (c) no bounded wait expired.
+peer scheme, (b) both schemes agree to rounding noise, (c) no bounded wait expired, (d) under bf16 autocast the
+peer scheme gives the same parameters whether forward and backward are launched kernel by kernel or replayed
+from CUDA graphs.
 """
 
 import os
@@ -13,11 +15,11 @@ import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import heavyball_b200 as hb  # noqa: E402
-from heavyball_b200.models import GPT, GPTConfig, split_param_groups  # noqa: E402
+from heavyball_b200.models import GPT, GPTConfig, graph_forward_backward, split_param_groups  # noqa: E402
 from heavyball_b200.parallel import ddp  # noqa: E402
 
 
-def run(mode, steps, rank, world, device):
+def run(mode, steps, rank, world, device, autocast=False, graphs=False):
     torch.manual_seed(0)
     model = GPT(GPTConfig(n_layer=2, n_head=4, d_model=256, vocab_size=512, seq_len=64)).to(device)
     mats, rest = split_param_groups(model)
@@ -27,14 +29,18 @@ def run(mode, steps, rank, world, device):
     ])
     wrapped = ddp.wrap(model, opt, mode=mode)
     gen = torch.Generator().manual_seed(100 + rank)
+    if graphs:
+        example = torch.randint(0, 512, (4, 65)).to(device)
+        graph_forward_backward(model, (example[:, :-1], example[:, 1:]))
     losses = []
     for _ in range(steps):
         tokens = torch.randint(0, 512, (4, 65), generator=gen).to(device)
-        loss = wrapped(tokens[:, :-1], tokens[:, 1:])
+        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=autocast, cache_enabled=False):
+            loss = wrapped(tokens[:, :-1], tokens[:, 1:])
         loss.backward()
         opt.step()
         opt.zero_grad()
-        losses.append(loss.detach())
+        losses.append(loss.detach().clone())
     if hasattr(wrapped, "peer"):
         wrapped.peer.check()
     hb.ops.check_status()
@@ -51,6 +57,9 @@ def main():
     steps = 4
     peer_flat, peer_loss = run("peer", steps, rank, world, device)
     nccl_flat, nccl_loss = run("nccl", steps, rank, world, device)
+    amp_flat, amp_loss = run("peer", steps, rank, world, device, autocast=True)
+    graph_flat, graph_loss = run("peer", steps, rank, world, device, autocast=True, graphs=True)
+    graph_rms = ((amp_flat - graph_flat).square().mean().sqrt() / amp_flat.square().mean().sqrt()).item()
 
     gathered = [torch.empty_like(peer_flat) for _ in range(world)]
     dist.all_gather(gathered, peer_flat)
@@ -60,8 +69,9 @@ def main():
     rms = ((peer_flat - nccl_flat).square().mean().sqrt() / nccl_flat.square().mean().sqrt()).item()
     if rank == 0:
         print(f"RESULT identical={identical} max_abs_diff={diff:.3e} max_abs={scale:.3e} rel_rms={rms:.3e} "
-              f"loss_peer={peer_loss.tolist()} loss_nccl={nccl_loss.tolist()}")
-    ok = identical and rms < 2e-2
+              f"loss_peer={peer_loss.tolist()} loss_nccl={nccl_loss.tolist()} graph_rel_rms={graph_rms:.3e} "
+              f"loss_amp={amp_loss.tolist()} loss_graph={graph_loss.tolist()}")
+    ok = identical and rms < 2e-2 and graph_rms < 2e-2
     dist.barrier()
     dist.destroy_process_group()
     sys.exit(0 if ok else 1)

@@ -260,31 +260,44 @@ at::Tensor colsum_bf16(const at::Tensor& x) {
   return out;
 }
 
-// LayerNorm over the last dimension of a contiguous fp32 tensor.  Returns (y, mean, rstd); y is bf16 when asked.
-std::vector<at::Tensor> layer_norm_fwd(const at::Tensor& x, const at::Tensor& gamma, const at::Tensor& beta, double eps,
-                                       bool out_bf16) {
+// LayerNorm over the last dimension of a contiguous fp32 tensor.  With `res` (same shape, bf16 or fp32) the normalised
+// tensor is x + res, which is returned as a fourth tensor.  Returns (y, mean, rstd[, x + res]); y is bf16 when asked.
+std::vector<at::Tensor> layer_norm_fwd(const at::Tensor& x, const OptT& res, const at::Tensor& gamma, const at::Tensor& beta,
+                                       double eps, bool out_bf16) {
   const int64_t D = x.size(-1);
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.is_contiguous(), "x: contiguous fp32 CUDA tensor");
   TORCH_CHECK(hb::layer_norm_supported((int)D), "row length must be a multiple of 128, at most 1024");
   TORCH_CHECK(gamma.scalar_type() == at::kFloat && beta.scalar_type() == at::kFloat && gamma.numel() == D &&
                   beta.numel() == D && gamma.is_contiguous() && beta.is_contiguous(), "gamma / beta: fp32 [D]");
+  const bool has_res = res.has_value() && res->defined();
+  if (has_res)
+    TORCH_CHECK(res->is_cuda() && res->is_contiguous() && res->numel() == x.numel() &&
+                    (res->scalar_type() == at::kFloat || res->scalar_type() == at::kBFloat16), "res: contiguous fp32 / bf16 like x");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t rows = x.numel() / D;
   at::Tensor y = at::empty(x.sizes(), x.options().dtype(out_bf16 ? at::kBFloat16 : at::kFloat));
   at::Tensor mean = at::empty({rows}, x.options()), rstd = at::empty({rows}, x.options());
-  check(hb::launch_layer_norm_fwd(x.data_ptr<float>(), gamma.data_ptr<float>(), beta.data_ptr<float>(), y.data_ptr(),
-                                  out_bf16, mean.data_ptr<float>(), rstd.data_ptr<float>(), rows, (int)D, (float)eps,
+  at::Tensor xsum = has_res ? at::empty_like(x) : at::Tensor();
+  check(hb::launch_layer_norm_fwd(x.data_ptr<float>(), has_res ? res->data_ptr() : nullptr,
+                                  has_res && res->scalar_type() == at::kBFloat16, has_res ? xsum.data_ptr<float>() : nullptr,
+                                  gamma.data_ptr<float>(), beta.data_ptr<float>(), y.data_ptr(), out_bf16,
+                                  mean.data_ptr<float>(), rstd.data_ptr<float>(), rows, (int)D, (float)eps,
                                   at::cuda::getCurrentCUDAStream()), "layer_norm_fwd launch");
+  if (has_res) return {y, mean, rstd, xsum};
   return {y, mean, rstd};
 }
 
-// Returns (dx, dgamma, dbeta) for dy in fp32 or bf16.
+// Returns (dx, dgamma, dbeta) for dy in fp32 or bf16; `dres` (fp32, optional) is added to dx.
 std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& gamma,
-                                       const at::Tensor& mean, const at::Tensor& rstd) {
+                                       const at::Tensor& mean, const at::Tensor& rstd, const OptT& dres) {
   const int64_t D = x.size(-1);
   TORCH_CHECK(dy.is_cuda() && dy.is_contiguous() && dy.numel() == x.numel() &&
                   (dy.scalar_type() == at::kFloat || dy.scalar_type() == at::kBFloat16), "dy: contiguous fp32 / bf16");
   TORCH_CHECK(x.scalar_type() == at::kFloat && x.is_contiguous() && hb::layer_norm_supported((int)D), "x: contiguous fp32");
+  const bool has_dres = dres.has_value() && dres->defined();
+  if (has_dres)
+    TORCH_CHECK(dres->is_cuda() && dres->is_contiguous() && dres->scalar_type() == at::kFloat && dres->numel() == x.numel(),
+                "dres: contiguous fp32 like x");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t rows = x.numel() / D;
   const int n_cta = hb::layer_norm_partial_ctas(rows);
@@ -292,9 +305,9 @@ std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x
   at::Tensor partial = at::empty({n_cta, 2 * D}, x.options());
   check(hb::launch_layer_norm_bwd(dy.data_ptr(), dy.scalar_type() == at::kBFloat16, x.data_ptr<float>(),
                                   gamma.data_ptr<float>(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
-                                  dx.data_ptr<float>(), dgamma.data_ptr<float>(), dbeta.data_ptr<float>(),
-                                  partial.data_ptr<float>(), n_cta, rows, (int)D, at::cuda::getCurrentCUDAStream()),
-        "layer_norm_bwd launch");
+                                  has_dres ? dres->data_ptr<float>() : nullptr, dx.data_ptr<float>(),
+                                  dgamma.data_ptr<float>(), dbeta.data_ptr<float>(), partial.data_ptr<float>(), n_cta, rows,
+                                  (int)D, at::cuda::getCurrentCUDAStream()), "layer_norm_bwd launch");
   return {dx, dgamma, dbeta};
 }
 

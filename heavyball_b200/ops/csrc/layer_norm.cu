@@ -51,8 +51,12 @@ __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v
   *reinterpret_cast<uint2*>(p) = raw;
 }
 
+// With `res` the kernel normalises s = x + res (res in bf16 or fp32) and also writes s to `xsum`: the residual add
+// of a transformer block rides along instead of being a separate pass over the stream.
 template <int VPL, typename OutT>
-__global__ void __launch_bounds__(kWarps * 32) ln_fwd_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+__global__ void __launch_bounds__(kWarps * 32) ln_fwd_kernel(const float* __restrict__ x, const void* __restrict__ res,
+                                                            int res_bf16, float* __restrict__ xsum,
+                                                            const float* __restrict__ gamma,
                                                             const float* __restrict__ beta, OutT* __restrict__ y,
                                                             float* __restrict__ mean, float* __restrict__ rstd,
                                                             long long rows, float eps) {
@@ -65,7 +69,14 @@ __global__ void __launch_bounds__(kWarps * 32) ln_fwd_kernel(const float* __rest
   float s = 0.f;
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
-    v[i] = load4<float>(xr + i * 128 + lane * 4);
+    const int c = i * 128 + lane * 4;
+    v[i] = load4<float>(xr + c);
+    if (res != nullptr) {
+      const float4 r = res_bf16 ? load4<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(res) + row * D + c)
+                                : load4<float>(static_cast<const float*>(res) + row * D + c);
+      v[i] = make_float4(v[i].x + r.x, v[i].y + r.y, v[i].z + r.z, v[i].w + r.w);
+      store4<float>(xsum + row * D + c, v[i]);
+    }
     s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
   }
   const float mu = warp_sum(s) * (1.f / D);
@@ -95,7 +106,8 @@ __global__ void __launch_bounds__(kWarps * 32) ln_fwd_kernel(const float* __rest
 template <int VPL, typename GradT>
 __global__ void __launch_bounds__(kWarps * 32) ln_bwd_kernel(const GradT* __restrict__ dy, const float* __restrict__ x,
                                                             const float* __restrict__ gamma, const float* __restrict__ mean,
-                                                            const float* __restrict__ rstd, float* __restrict__ dx,
+                                                            const float* __restrict__ rstd,
+                                                            const float* __restrict__ dres, float* __restrict__ dx,
                                                             float* __restrict__ partial, long long rows) {
   constexpr int D = VPL * 128;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -127,8 +139,13 @@ __global__ void __launch_bounds__(kWarps * 32) ln_bwd_kernel(const GradT* __rest
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
       const int c = i * 128 + lane * 4;
-      store4<float>(dx + row * D + c, make_float4(rs * (g[i].x - s1 - xh[i].x * s2), rs * (g[i].y - s1 - xh[i].y * s2),
-                                                  rs * (g[i].z - s1 - xh[i].z * s2), rs * (g[i].w - s1 - xh[i].w * s2)));
+      float4 o = make_float4(rs * (g[i].x - s1 - xh[i].x * s2), rs * (g[i].y - s1 - xh[i].y * s2),
+                             rs * (g[i].z - s1 - xh[i].z * s2), rs * (g[i].w - s1 - xh[i].w * s2));
+      if (dres != nullptr) {  // gradient arriving through the residual path: added here instead of by a separate kernel
+        const float4 r = load4<float>(dres + row * D + c);
+        o = make_float4(o.x + r.x, o.y + r.y, o.z + r.z, o.w + r.w);
+      }
+      store4<float>(dx + row * D + c, o);
     }
   }
   // combine the CTA's warps through shared memory, one column vector at a time
@@ -173,23 +190,24 @@ __global__ void __launch_bounds__(256) ln_reduce_kernel(const float* __restrict_
 }
 
 template <int VPL>
-cudaError_t fwd_dispatch(const float* x, const float* gamma, const float* beta, void* y, bool y_bf16, float* mean,
-                         float* rstd, long long rows, float eps, cudaStream_t stream) {
+cudaError_t fwd_dispatch(const float* x, const void* res, bool res_bf16, float* xsum, const float* gamma, const float* beta,
+                         void* y, bool y_bf16, float* mean, float* rstd, long long rows, float eps, cudaStream_t stream) {
   const unsigned grid = (unsigned)((rows + kWarps - 1) / kWarps);
   if (y_bf16)
-    ln_fwd_kernel<VPL, __nv_bfloat16><<<grid, kWarps * 32, 0, stream>>>(x, gamma, beta, static_cast<__nv_bfloat16*>(y), mean, rstd, rows, eps);
+    ln_fwd_kernel<VPL, __nv_bfloat16><<<grid, kWarps * 32, 0, stream>>>(x, res, res_bf16, xsum, gamma, beta, static_cast<__nv_bfloat16*>(y), mean, rstd, rows, eps);
   else
-    ln_fwd_kernel<VPL, float><<<grid, kWarps * 32, 0, stream>>>(x, gamma, beta, static_cast<float*>(y), mean, rstd, rows, eps);
+    ln_fwd_kernel<VPL, float><<<grid, kWarps * 32, 0, stream>>>(x, res, res_bf16, xsum, gamma, beta, static_cast<float*>(y), mean, rstd, rows, eps);
   return cudaGetLastError();
 }
 
 template <int VPL>
 cudaError_t bwd_dispatch(const void* dy, bool dy_bf16, const float* x, const float* gamma, const float* mean,
-                         const float* rstd, float* dx, float* partial, int n_cta, long long rows, cudaStream_t stream) {
+                         const float* rstd, const float* dres, float* dx, float* partial, int n_cta, long long rows,
+                         cudaStream_t stream) {
   if (dy_bf16)
-    ln_bwd_kernel<VPL, __nv_bfloat16><<<n_cta, kWarps * 32, 0, stream>>>(static_cast<const __nv_bfloat16*>(dy), x, gamma, mean, rstd, dx, partial, rows);
+    ln_bwd_kernel<VPL, __nv_bfloat16><<<n_cta, kWarps * 32, 0, stream>>>(static_cast<const __nv_bfloat16*>(dy), x, gamma, mean, rstd, dres, dx, partial, rows);
   else
-    ln_bwd_kernel<VPL, float><<<n_cta, kWarps * 32, 0, stream>>>(static_cast<const float*>(dy), x, gamma, mean, rstd, dx, partial, rows);
+    ln_bwd_kernel<VPL, float><<<n_cta, kWarps * 32, 0, stream>>>(static_cast<const float*>(dy), x, gamma, mean, rstd, dres, dx, partial, rows);
   return cudaGetLastError();
 }
 
@@ -216,22 +234,23 @@ int layer_norm_partial_ctas(long long rows) {
     default: return cudaErrorInvalidValue; \
   }
 
-cudaError_t launch_layer_norm_fwd(const float* x, const float* gamma, const float* beta, void* y, bool y_bf16, float* mean,
-                                  float* rstd, long long rows, int D, float eps, cudaStream_t stream) {
+cudaError_t launch_layer_norm_fwd(const float* x, const void* res, bool res_bf16, float* xsum, const float* gamma,
+                                  const float* beta, void* y, bool y_bf16, float* mean, float* rstd, long long rows, int D,
+                                  float eps, cudaStream_t stream) {
   if (rows == 0) return cudaSuccess;
-#define CALL(V) fwd_dispatch<V>(x, gamma, beta, y, y_bf16, mean, rstd, rows, eps, stream)
+#define CALL(V) fwd_dispatch<V>(x, res, res_bf16, xsum, gamma, beta, y, y_bf16, mean, rstd, rows, eps, stream)
   HB_LN_SWITCH(D, CALL)
 #undef CALL
 }
 
 cudaError_t launch_layer_norm_bwd(const void* dy, bool dy_bf16, const float* x, const float* gamma, const float* mean,
-                                  const float* rstd, float* dx, float* dgamma, float* dbeta, float* partial, int n_cta,
-                                  long long rows, int D, cudaStream_t stream) {
+                                  const float* rstd, const float* dres, float* dx, float* dgamma, float* dbeta,
+                                  float* partial, int n_cta, long long rows, int D, cudaStream_t stream) {
   if (rows == 0) return cudaSuccess;
   cudaError_t err;
   {
     auto run = [&]() -> cudaError_t {
-#define CALL(V) bwd_dispatch<V>(dy, dy_bf16, x, gamma, mean, rstd, dx, partial, n_cta, rows, stream)
+#define CALL(V) bwd_dispatch<V>(dy, dy_bf16, x, gamma, mean, rstd, dres, dx, partial, n_cta, rows, stream)
       HB_LN_SWITCH(D, CALL)
 #undef CALL
     };

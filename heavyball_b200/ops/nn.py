@@ -10,9 +10,10 @@ framework op it replaces as its fallback (CPU, other dtypes, unsupported shapes)
     16 x 1024 tokens and a 50k vocabulary, against 3.3 GB.  ``W`` may have more rows than the vocabulary (a
     row count that is a multiple of 64 keeps the GEMMs on their aligned tensor-core kernels: a 50 257-row head
     runs on a legacy unaligned path about 9x slower); the extra columns get zero probability and zero gradient.
-``layer_norm`` / ``LayerNorm``
+``layer_norm`` / ``add_layer_norm`` / ``LayerNorm``
     One kernel each way (``csrc/layer_norm.cu``); under autocast the output is written, and the incoming
-    gradient read, in bf16 directly.
+    gradient read, in bf16 directly.  ``add_layer_norm`` also performs the residual add that precedes the
+    normalisation (and, on the way back, the add of the gradient arriving on the residual stream).
 ``linear`` / ``Linear`` / ``CastCache``
     ``F.linear`` whose bias gradient comes from a column-sum kernel (``csrc/colsum.cu``) and whose bf16 weights
     come from one multi-tensor cast per forward pass.
@@ -77,7 +78,7 @@ def linear_cross_entropy(h: torch.Tensor, weight: torch.Tensor, targets: torch.T
 class _LayerNormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, eps, out_bf16):
-        y, mean, rstd = load().layer_norm_fwd(x, weight, bias, eps, out_bf16)
+        y, mean, rstd = load().layer_norm_fwd(x, None, weight, bias, eps, out_bf16)
         launch_counter.count += 1
         ctx.save_for_backward(x, weight, mean, rstd)
         return y
@@ -85,9 +86,32 @@ class _LayerNormFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x, weight, mean, rstd = ctx.saved_tensors
-        dx, dw, db = load().layer_norm_bwd(dy.contiguous(), x, weight, mean, rstd)
+        dx, dw, db = load().layer_norm_bwd(dy.contiguous(), x, weight, mean, rstd, None)
         launch_counter.count += 2
         return dx, dw, db, None, None
+
+
+class _AddLayerNormFn(torch.autograd.Function):
+    """``s = x + res``, ``y = LayerNorm(s)`` in one kernel; backward adds the gradient arriving at ``s`` to the
+    LayerNorm gradient in the same kernel that computes it."""
+
+    @staticmethod
+    def forward(ctx, x, res, weight, bias, eps, out_bf16):
+        y, mean, rstd, s = load().layer_norm_fwd(x, res, weight, bias, eps, out_bf16)
+        launch_counter.count += 1
+        ctx.save_for_backward(s, weight, mean, rstd)
+        ctx.res_dtype = res.dtype
+        return s, y
+
+    @staticmethod
+    def backward(ctx, ds, dy):
+        s, weight, mean, rstd = ctx.saved_tensors
+        if dy is None:  # the normalised output was not used
+            return ds, None if ds is None else ds.to(ctx.res_dtype), None, None, None, None
+        ds = None if ds is None else ds.contiguous()
+        dx, dw, db = load().layer_norm_bwd(dy.contiguous(), s, weight, mean, rstd, ds)
+        launch_counter.count += 2
+        return dx, dx.to(ctx.res_dtype), dw, db, None, None
 
 
 def _ln_kernel_applies(x: torch.Tensor, weight, bias) -> bool:
@@ -109,13 +133,29 @@ def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: f
     return F.layer_norm(x, (x.shape[-1],), weight, bias, eps)
 
 
-class LayerNorm(torch.nn.LayerNorm):
-    """``torch.nn.LayerNorm`` (same parameters and state dict) running :func:`layer_norm`."""
+def add_layer_norm(x: torch.Tensor, res, weight: torch.Tensor, bias: torch.Tensor, eps: float = 1e-5):
+    """``(x + res, LayerNorm(x + res))``: the residual add of a pre-norm transformer block fused into the
+    normalisation that follows it (one pass over the stream instead of two each way).  ``res=None`` gives
+    ``(x, LayerNorm(x))``."""
+    if res is None:
+        return x, layer_norm(x, weight, bias, eps)
+    if _ln_kernel_applies(x, weight, bias) and res.shape == x.shape and res.dtype in (torch.float32, torch.bfloat16):
+        out_bf16 = torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16
+        return _AddLayerNormFn.apply(x.contiguous(), res.contiguous(), weight, bias, eps, out_bf16)
+    s = x + res
+    return s, layer_norm(s, weight, bias, eps)
 
-    def forward(self, x):
-        if len(self.normalized_shape) == 1:
+
+class LayerNorm(torch.nn.LayerNorm):
+    """``torch.nn.LayerNorm`` (same parameters and state dict) running :func:`layer_norm`; ``forward(x, res)``
+    returns ``(x + res, LayerNorm(x + res))`` through :func:`add_layer_norm`."""
+
+    def forward(self, x, res=None):
+        if len(self.normalized_shape) != 1:
+            return super().forward(x if res is None else x + res)
+        if res is None:
             return layer_norm(x, self.weight, self.bias, self.eps)
-        return super().forward(x)
+        return add_layer_norm(x, res, self.weight, self.bias, self.eps)
 
 
 class _LinearFn(torch.autograd.Function):

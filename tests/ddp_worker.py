@@ -30,7 +30,8 @@ def run(mode, steps, rank, world, device, autocast=False, graphs=False):
     wrapped = ddp.wrap(model, opt, mode=mode)
     gen = torch.Generator().manual_seed(100 + rank)
     if graphs:
-        example = torch.randint(0, 512, (4, 65)).to(device)
+        example = torch.randint(0, 512, (4, 65), generator=torch.Generator().manual_seed(5)).to(device)  # own generator:
+        # the default one seeds the optimizer's stochastic rounding and must see the same draws in both runs
         graph_forward_backward(model, (example[:, :-1], example[:, 1:]))
     losses = []
     for _ in range(steps):

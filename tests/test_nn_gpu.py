@@ -192,3 +192,36 @@ def test_graphed_forward_backward_matches_eager_launches():
             for p, q in zip(eager.parameters(), graphed.parameters()):
                 p.sub_(0.1 * p.grad)
                 q.sub_(0.1 * q.grad)
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_add_layer_norm_matches_separate_add_and_norm(bf16):
+    from heavyball_b200.ops.nn import add_layer_norm
+
+    torch.manual_seed(0)
+    shape, d = (8, 96, 384), 384
+    x = torch.randn(*shape, device="cuda").requires_grad_()
+    res = torch.randn(*shape, device="cuda").to(torch.bfloat16 if bf16 else torch.float32).requires_grad_()
+    w = (torch.rand(d, device="cuda") + 0.5).requires_grad_()
+    b = torch.randn(d, device="cuda").requires_grad_()
+    ds, dy = torch.randn(*shape, device="cuda"), torch.randn(*shape, device="cuda")
+    with torch.autocast("cuda", dtype=torch.bfloat16, enabled=bf16):
+        s, y = add_layer_norm(x, res, w, b, 1e-5)
+    assert s.dtype == torch.float32 and y.dtype == (torch.bfloat16 if bf16 else torch.float32)
+    torch.autograd.backward([s, y], [ds, dy.to(y.dtype)])
+
+    x2, r2, w2, b2 = (t.detach().clone().requires_grad_() for t in (x, res, w, b))
+    s2 = x2 + r2.float()
+    y2 = F.layer_norm(s2, (d,), w2, b2, 1e-5)
+    torch.autograd.backward([s2, y2], [ds, dy.to(y.dtype).float()])
+    assert torch.allclose(s, s2, atol=1e-6)
+    assert torch.allclose(y.float(), y2, **(dict(atol=2e-2, rtol=2e-2) if bf16 else dict(atol=2e-5, rtol=1e-5)))
+    assert torch.allclose(x.grad, x2.grad, atol=1e-4, rtol=1e-4)
+    assert res.grad.dtype == res.dtype
+    assert torch.allclose(res.grad.float(), r2.grad.float(), atol=3e-2 if bf16 else 1e-4, rtol=2e-2 if bf16 else 1e-4)
+    assert torch.allclose(w.grad, w2.grad, atol=2e-3, rtol=1e-4) and torch.allclose(b.grad, b2.grad, atol=2e-3, rtol=1e-4)
+    # only the sum used downstream: the gradient passes straight through
+    x3 = x.detach().clone().requires_grad_()
+    s3, _ = add_layer_norm(x3, res.detach(), w.detach(), b.detach(), 1e-5)
+    s3.backward(ds)
+    assert torch.equal(x3.grad, ds)

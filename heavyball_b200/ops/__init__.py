@@ -9,6 +9,13 @@ Entry points
 ``fused_chain``      one multi-tensor pass: decode -> MARS -> moment rule -> caution -> decay -> write
 ``sumsq``            per-tensor sum of squares (segmented reduction)
 ``newton_schulz``    batched quintic Newton–Schulz / Polar-Express chain on tcgen05 tensor cores
+``matmul3``          fp32 matrix product on the tf32 tensor cores (3-term split), for SOAP / PSGD algebra
+``nn``               (sub-module) model-side ops: fused head + cross-entropy, LayerNorm (+ residual add), Linear with
+                     column-sum bias gradients, bf16 cast cache
+``noalloc``          (sub-module) ctypes access to the allocation-free AdamW entry point
+
+The extension also exports ``tall_t_mul`` (product over a long dimension for the eigenbasis-refresh QR) and the peer
+flag kernels used by ``heavyball_b200.parallel.ddp``.
 """
 
 from __future__ import annotations

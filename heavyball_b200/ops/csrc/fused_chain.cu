@@ -149,8 +149,14 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
       out.v[k] = r;
     }
 
-    if (P.n_state >= 1) store4(M.s0, M.s0e, P.dt_s, i, nv, vec_ok, s0, draw(P.dt_s, rng, ctr, ctr_hi, (uint32_t)t, 0u));
-    if (P.n_state >= 2) store4(M.s1, M.s1e, P.dt_s, i, nv, vec_ok, s1, draw(P.dt_s, rng, ctr, ctr_hi, (uint32_t)t, 1u));
+    // plain bf16 rounding consumes 16 random bits per element: the first two state tensors share one draw
+    // (low / high halves); ECC residuals need 32 bits and keep a draw each
+    const uint4 r0 = (P.n_state >= 1) ? draw(P.dt_s, rng, ctr, ctr_hi, (uint32_t)t, 0u) : make_uint4(0u, 0u, 0u, 0u);
+    if (P.n_state >= 1) store4(M.s0, M.s0e, P.dt_s, i, nv, vec_ok, s0, r0);
+    if (P.n_state >= 2)
+      store4(M.s1, M.s1e, P.dt_s, i, nv, vec_ok, s1,
+             P.dt_s == kBF16 ? make_uint4(r0.x >> 16, r0.y >> 16, r0.z >> 16, r0.w >> 16)
+                             : draw(P.dt_s, rng, ctr, ctr_hi, (uint32_t)t, 1u));
     if (P.n_state >= 3) store4(M.s2, M.s2e, P.dt_s, i, nv, vec_ok, s2, draw(P.dt_s, rng, ctr, ctr_hi, (uint32_t)t, 2u));
 
     if (kCountCaution) {  // phase one of caution: mask, count, park the masked update

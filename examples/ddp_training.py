@@ -26,6 +26,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--mode", default="peer", choices=["peer", "nccl"])
     ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--save", default=None, help="write a checkpoint (model + optimizer state) here at the end")
     args = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
@@ -51,6 +52,9 @@ def main():
             print(f"step {step:4d}  loss {loss.item():.4f}")
     if hasattr(net, "peer"):
         net.peer.check()
+        net.peer.consolidate_state()  # collective: optimizer state is partitioned across ranks until now
+    if dist.get_rank() == 0 and args.save:
+        torch.save({"model": model.state_dict(), "optimizer": opt.state_dict()}, args.save)
     dist.destroy_process_group()
 
 

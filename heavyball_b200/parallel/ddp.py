@@ -22,6 +22,10 @@ Synchronisation is two epoch-flag barriers per step in symmetric memory (``ops/c
 writing your parameters" after the last.  Waits are bounded; :meth:`PeerContext.check` raises if a peer
 never arrived.  Every parameter element has exactly one writer, so replicas stay bit-identical.
 
+Optimizer state is partitioned the same way (a rank only advances the state it owns).  Before saving a
+checkpoint call ``wrapped.peer.consolidate_state()`` on every rank: it completes the state everywhere, so that
+the ``state_dict`` of any one rank is the whole optimizer state.
+
 ``mode="nccl"`` (or a single process) falls back to ``DistributedDataParallel``.
 """
 
@@ -107,7 +111,9 @@ class PeerContext:
         # ---- which parameters are handled by peer kernels, which by the all-reduce fallback
         self.plans: Dict[int, dict] = {}
         self.fallback_ranges: List[Tuple[int, int]] = []
-        for opt in _inner_optimizers(optimizer):
+        self._optimizers = list(_inner_optimizers(optimizer))
+        self.consolidations = 0
+        for opt in self._optimizers:
             prog = lowering._program(opt) if hasattr(opt, "_lowered") else None
             supported = prog is not None and opt.__class__.__name__ != "ADOPT"
             for g in getattr(opt, "param_groups", []):
@@ -196,6 +202,47 @@ class PeerContext:
         self._barrier(1)
         self.G.zero_()
         self._attach_grads()
+
+    def consolidate_state(self):
+        """Makes the optimizer state complete on every rank.  Collective: call it on all ranks, e.g. before rank 0
+        saves ``optimizer.state_dict()``.
+
+        Under the peer scheme a rank only advances the state (moments, momentum buffers) of the elements or matrices
+        it owns; the rest of each state tensor stays as it was.  Here every rank keeps its owned pieces, zeroes the
+        others in a scratch copy and the copies are summed across ranks, so afterwards all ranks hold the same,
+        complete state (and a checkpoint written by one rank resumes correctly under any world size)."""
+        self.consolidations += 1
+        for opt in self._optimizers:
+            for group in getattr(opt, "param_groups", []):
+                plan = self.plans.get(id(group))
+                if plan is None:
+                    continue  # fallback groups are updated on every rank already
+                owned = {}
+                for i, rng in plan["sel"]:
+                    owned.setdefault(i, []).append(rng)
+                for i, p in enumerate(group["params"]):
+                    for t in self._state_tensors(opt, p):
+                        flat = t.view(-1)
+                        scratch = torch.zeros_like(flat)
+                        for rng in owned.get(i, []):
+                            a, b = (0, flat.numel()) if rng is None else rng
+                            scratch[a:b] = flat[a:b]
+                        dist.all_reduce(scratch, group=self.group)
+                        flat.copy_(scratch)
+
+    @staticmethod
+    def _state_tensors(opt, p):
+        """Per-element state of ``p`` (tensors shaped like the parameter), whatever the nesting of the state dict."""
+        found, stack = [], [opt.state.get(p, {})]
+        while stack:
+            node = stack.pop()
+            if isinstance(node, dict):
+                stack.extend(node.values())
+            elif isinstance(node, (list, tuple)):
+                stack.extend(node)
+            elif isinstance(node, torch.Tensor) and node.numel() == p.numel() and node.numel() > 1 and node.is_floating_point():
+                found.append(node)
+        return found
 
     def check(self):
         """Host-synchronising health check: raises if a bounded wait expired."""

@@ -4,7 +4,8 @@ Trains a small GPT for a few steps on rank-specific data: with the peer-memory s
 ``DistributedDataParallel`` + replicated optimizer.  Checks that (a) replicas are bit-identical under the
 peer scheme, (b) both schemes agree to rounding noise, (c) no bounded wait expired, (d) under bf16 autocast the
 peer scheme gives the same parameters whether forward and backward are launched kernel by kernel or replayed
-from CUDA graphs.
+from CUDA graphs, (e) after ``consolidate_state`` every rank holds the complete optimizer state, equal to the
+replicated run's.
 """
 
 import os
@@ -44,9 +45,15 @@ def run(mode, steps, rank, world, device, autocast=False, graphs=False):
         losses.append(loss.detach().clone())
     if hasattr(wrapped, "peer"):
         wrapped.peer.check()
+        wrapped.peer.consolidate_state()
     hb.ops.check_status()
     flat = torch.cat([p.detach().flatten().float() for p in model.parameters()])
-    return flat, torch.stack(losses)
+    state = []
+    for inner in opt.optimizers if hasattr(opt, "optimizers") else [opt]:
+        for p in model.parameters():
+            if p in inner.state:
+                state += [t.detach().flatten().float() for t in ddp.PeerContext._state_tensors(inner, p)]
+    return flat, torch.stack(losses), torch.cat(state)
 
 
 def main():
@@ -56,10 +63,15 @@ def main():
     device = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=device)
     steps = 4
-    peer_flat, peer_loss = run("peer", steps, rank, world, device)
-    nccl_flat, nccl_loss = run("nccl", steps, rank, world, device)
-    amp_flat, amp_loss = run("peer", steps, rank, world, device, autocast=True)
-    graph_flat, graph_loss = run("peer", steps, rank, world, device, autocast=True, graphs=True)
+    peer_flat, peer_loss, peer_state = run("peer", steps, rank, world, device)
+    nccl_flat, nccl_loss, nccl_state = run("nccl", steps, rank, world, device)
+    amp_flat, amp_loss, _ = run("peer", steps, rank, world, device, autocast=True)
+    graph_flat, graph_loss, _ = run("peer", steps, rank, world, device, autocast=True, graphs=True)
+    # after consolidation every rank holds the whole optimizer state, and it is the replicated run's state
+    states = [torch.empty_like(peer_state) for _ in range(world)]
+    dist.all_gather(states, peer_state)
+    state_identical = all(torch.equal(states[0], s) for s in states)
+    state_rms = ((peer_state - nccl_state).square().mean().sqrt() / nccl_state.square().mean().sqrt()).item()
     graph_rms = ((amp_flat - graph_flat).square().mean().sqrt() / amp_flat.square().mean().sqrt()).item()
 
     gathered = [torch.empty_like(peer_flat) for _ in range(world)]
@@ -71,8 +83,9 @@ def main():
     if rank == 0:
         print(f"RESULT identical={identical} max_abs_diff={diff:.3e} max_abs={scale:.3e} rel_rms={rms:.3e} "
               f"loss_peer={peer_loss.tolist()} loss_nccl={nccl_loss.tolist()} graph_rel_rms={graph_rms:.3e} "
-              f"loss_amp={amp_loss.tolist()} loss_graph={graph_loss.tolist()}")
-    ok = identical and rms < 2e-2 and graph_rms < 2e-2
+              f"loss_amp={amp_loss.tolist()} loss_graph={graph_loss.tolist()} state_identical={state_identical} "
+              f"state_rel_rms={state_rms:.3e}")
+    ok = identical and rms < 2e-2 and graph_rms < 2e-2 and state_identical and state_rms < 2e-2
     dist.barrier()
     dist.destroy_process_group()
     sys.exit(0 if ok else 1)

@@ -24,6 +24,7 @@ import json
 import os
 import statistics
 import sys
+import time
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
@@ -47,6 +48,7 @@ def main():
     ap.add_argument("--count", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--breakdown", action="store_true", help="time barrier / kernels / barrier separately (peer arm)")
     args = ap.parse_args()
 
     import torch
@@ -73,7 +75,7 @@ def main():
         wrapped = ddp.wrap(holder, opt, mode="peer") if mode == "peer" else None
         gen = torch.Generator(device=device).manual_seed(1 + rank)
         grads = [torch.randn(rows, cols, device=device, generator=gen) * 0.01 for _ in range(args.count)]
-        times = []
+        times, parts = [], []
         for i in range(args.warmup + args.steps):
             for p, g in zip(holder.ps, grads):
                 if p.grad is None:
@@ -84,6 +86,24 @@ def main():
             dist.barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
+            if mode == "peer" and args.breakdown:  # the three parts of a peer step, timed separately
+                ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                h0 = time.perf_counter()
+                wrapped.peer.begin_step()
+                ea.record()
+                h1 = time.perf_counter()
+                type(opt).step(opt)  # the class's own step: the instance attribute is the wrapped one
+                eb.record()
+                h2 = time.perf_counter()
+                wrapped.peer.end_step()
+                e1.record()
+                h3 = time.perf_counter()
+                torch.cuda.synchronize()
+                if i >= args.warmup:
+                    times.append(e0.elapsed_time(e1))
+                    parts.append((e0.elapsed_time(ea), ea.elapsed_time(eb), eb.elapsed_time(e1),
+                                  (h1 - h0) * 1e3, (h2 - h1) * 1e3, (h3 - h2) * 1e3))
+                continue
             if mode == "nccl":  # replicated baseline: average the gradients, every rank updates everything
                 flat = torch._utils._flatten_dense_tensors([p.grad for p in holder.ps])
                 dist.all_reduce(flat, op=dist.ReduceOp.AVG)
@@ -97,6 +117,10 @@ def main():
         if wrapped is not None and hasattr(wrapped, "peer"):
             wrapped.peer.check()
         hb.ops.check_status()
+        if parts and rank == 0:
+            med = [statistics.median(x) for x in zip(*parts)]
+            print(f"{name} rank 0 breakdown, device ms: begin barrier {med[0]:.3f}, kernels {med[1]:.3f}, end barrier + clear "
+                  f"{med[2]:.3f}; host enqueue ms: {med[3]:.3f}, {med[4]:.3f}, {med[5]:.3f}", flush=True)
         t = torch.tensor([statistics.median(times)], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())

@@ -52,10 +52,17 @@ cudaError_t launch_peer_signal(const PeerPtrs& flags, int slot, int rank, int wo
 
 cudaError_t launch_peer_wait(const int* my_flags, int slot, int world, int epoch, double timeout_s, int* status,
                              cudaStream_t stream) {
-  int dev = 0, khz = 0;
+  // the clock-rate attribute is a driver round trip of about a millisecond: ask once per device
+  static int khz_of[64] = {0};
+  int dev = 0;
   cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev);
-  const long long budget = (long long)(timeout_s * 1e3 * (double)(khz > 0 ? khz : 1500000));
+  int khz = (dev >= 0 && dev < 64) ? khz_of[dev] : 0;
+  if (khz == 0) {
+    cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev);
+    if (khz <= 0) khz = 1500000;
+    if (dev >= 0 && dev < 64) khz_of[dev] = khz;
+  }
+  const long long budget = (long long)(timeout_s * 1e3 * (double)khz);
   peer_wait_kernel<<<1, 32, 0, stream>>>(my_flags, slot, world, epoch, budget, status);
   return cudaGetLastError();
 }

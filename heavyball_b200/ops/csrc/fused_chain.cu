@@ -60,14 +60,26 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
     const int nv = (int)min((int64_t)4, M.numel - i);
     const uint32_t ctr = (uint32_t)(i >> 2), ctr_hi = (uint32_t)(i >> 34);
 
+    // local state first, then the gradient: with peers the gradient loads are NVLink round trips (about 2 us each),
+    // and everything issued before the first use of one of them overlaps with it
+    F4 s0 = load4(M.s0, M.s0e, P.dt_s, i, nv, vec_ok);
+    F4 s1 = load4(M.s1, M.s1e, P.dt_s, i, nv, vec_ok);
+    F4 s2 = load4(M.s2, M.s2e, P.dt_s, i, nv, vec_ok);
     F4 g;
     if (P.n_src > 0) {  // reduce the same element over every rank's gradient slab (peer loads over NVLink)
 #pragma unroll
       for (int k = 0; k < 4; ++k) g.v[k] = 0.f;
-      for (int r = 0; r < P.n_src; ++r) {
-        F4 part = load4((const char*)M.g + P.g_delta[r], nullptr, P.dt_g, i, nv, vec_ok);
+      for (int r0 = 0; r0 < P.n_src; r0 += 4) {  // four sources in flight at a time, summed in rank order
+        F4 part[4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) g.v[k] += part.v[k];
+        for (int j = 0; j < 4; ++j)
+          if (r0 + j < P.n_src) part[j] = load4((const char*)M.g + P.g_delta[r0 + j], nullptr, P.dt_g, i, nv, vec_ok);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (r0 + j < P.n_src) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) g.v[k] += part[j].v[k];
+          }
       }
 #pragma unroll
       for (int k = 0; k < 4; ++k) g.v[k] *= P.g_scale;
@@ -75,9 +87,6 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
       g = load4(M.g, nullptr, P.dt_g, i, nv, vec_ok);
     }
     F4 u = P.u_is_input ? load4(M.u, nullptr, P.dt_u, i, nv, vec_ok) : g;
-    F4 s0 = load4(M.s0, M.s0e, P.dt_s, i, nv, vec_ok);
-    F4 s1 = load4(M.s1, M.s1e, P.dt_s, i, nv, vec_ok);
-    F4 s2 = load4(M.s2, M.s2e, P.dt_s, i, nv, vec_ok);
     F4 p = P.out_mode == kOutParam ? load4(M.p, M.pe, P.dt_p, i, nv, vec_ok) : F4{};
     F4 out;
 

@@ -5,8 +5,9 @@ with the NVLink bytes they move and the fraction of the link / HBM / tensor-core
         benchmarks/bench_peer_step.py --optimizer AdamW Muon
 
 Setup: ``--count`` parameters of shape ``--shape`` (fp32) wrapped by ``heavyball_b200.parallel.ddp.wrap(mode="peer")``;
-every rank writes random gradients into its gradient slab, then ``optimizer.step()`` is timed with CUDA events
-(barrier + synchronize before, median over ``--steps``, maximum over ranks).  One step = flag barrier, the fused
+every rank writes random gradients into its gradient slab, then ``--steps`` calls of ``optimizer.step()`` are enqueued
+back to back and timed with one pair of CUDA events (barrier + synchronize before; per-step time, maximum over ranks),
+so that the host's preparation of a step overlaps the device's execution of the previous one, as in a training loop.  One step = flag barrier, the fused
 kernels (each rank loads its share of the gradient from every rank's slab, updates, stores the new parameters into
 every rank's slab), flag barrier, clearing of the gradient slab.
 
@@ -75,52 +76,68 @@ def main():
         wrapped = ddp.wrap(holder, opt, mode="peer") if mode == "peer" else None
         gen = torch.Generator(device=device).manual_seed(1 + rank)
         grads = [torch.randn(rows, cols, device=device, generator=gen) * 0.01 for _ in range(args.count)]
-        times, parts = [], []
-        for i in range(args.warmup + args.steps):
+
+        def fill():
             for p, g in zip(holder.ps, grads):
                 if p.grad is None:
                     p.grad = g.clone()
                 else:
                     p.grad.copy_(g)
-            torch.cuda.synchronize()
-            dist.barrier()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            if mode == "peer" and args.breakdown:  # the three parts of a peer step, timed separately
-                ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                h0 = time.perf_counter()
-                wrapped.peer.begin_step()
-                ea.record()
-                h1 = time.perf_counter()
-                type(opt).step(opt)  # the class's own step: the instance attribute is the wrapped one
-                eb.record()
-                h2 = time.perf_counter()
-                wrapped.peer.end_step()
-                e1.record()
-                h3 = time.perf_counter()
-                torch.cuda.synchronize()
-                if i >= args.warmup:
-                    times.append(e0.elapsed_time(e1))
-                    parts.append((e0.elapsed_time(ea), ea.elapsed_time(eb), eb.elapsed_time(e1),
-                                  (h1 - h0) * 1e3, (h2 - h1) * 1e3, (h3 - h2) * 1e3))
-                continue
+
+        def one_step():
             if mode == "nccl":  # replicated baseline: average the gradients, every rank updates everything
                 flat = torch._utils._flatten_dense_tensors([p.grad for p in holder.ps])
                 dist.all_reduce(flat, op=dist.ReduceOp.AVG)
                 for p, g in zip(holder.ps, torch._utils._unflatten_dense_tensors(flat, [p.grad for p in holder.ps])):
                     p.grad.copy_(g)
             opt.step()
-            e1.record()
-            torch.cuda.synchronize()
-            if i >= args.warmup:
-                times.append(e0.elapsed_time(e1))
+
+        for _ in range(args.warmup):
+            fill()
+            one_step()
+        parts = []
+        if mode == "peer" and args.breakdown:  # the three parts of one isolated peer step, device and host side
+            for _ in range(5):
+                fill()
+                torch.cuda.synchronize()
+                dist.barrier()
+                ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+                ev[0].record()
+                h0 = time.perf_counter()
+                wrapped.peer.begin_step()
+                ev[1].record()
+                h1 = time.perf_counter()
+                type(opt).step(opt)  # the class's own step: the instance attribute is the wrapped one
+                ev[2].record()
+                h2 = time.perf_counter()
+                wrapped.peer.end_step()
+                ev[3].record()
+                h3 = time.perf_counter()
+                torch.cuda.synchronize()
+                parts.append((ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2]), ev[2].elapsed_time(ev[3]),
+                              (h1 - h0) * 1e3, (h2 - h1) * 1e3, (h3 - h2) * 1e3))
+        # steady state, as inside a training loop: steps are enqueued back to back, so the host's preparation of a
+        # step overlaps the device's execution of the previous one (the gradients are whatever the last step left:
+        # the traffic does not depend on their values)
+        if hasattr(opt, "consume_grad"):
+            opt.consume_grad = False  # gradients stay in place between the back-to-back steps
+        fill()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            one_step()
+        e1.record()
+        torch.cuda.synchronize()
+        times = [e0.elapsed_time(e1) / args.steps]
         if wrapped is not None and hasattr(wrapped, "peer"):
             wrapped.peer.check()
         hb.ops.check_status()
         if parts and rank == 0:
             med = [statistics.median(x) for x in zip(*parts)]
-            print(f"{name} rank 0 breakdown, device ms: begin barrier {med[0]:.3f}, kernels {med[1]:.3f}, end barrier + clear "
-                  f"{med[2]:.3f}; host enqueue ms: {med[3]:.3f}, {med[4]:.3f}, {med[5]:.3f}", flush=True)
+            print(f"{name} rank 0, one isolated step, device ms: begin barrier {med[0]:.3f}, kernels {med[1]:.3f}, end barrier + "
+                  f"clear {med[2]:.3f}; host enqueue ms: {med[3]:.3f}, {med[4]:.3f}, {med[5]:.3f}", flush=True)
         t = torch.tensor([statistics.median(times)], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())

@@ -113,6 +113,7 @@ class PeerContext:
         self.fallback_ranges: List[Tuple[int, int]] = []
         self._optimizers = list(_inner_optimizers(optimizer))
         self.consolidations = 0
+        self.stale_state = False  # True between an optimizer step and the next consolidate_state()
         for opt in self._optimizers:
             prog = lowering._program(opt) if hasattr(opt, "_lowered") else None
             supported = prog is not None and opt.__class__.__name__ != "ADOPT"
@@ -192,6 +193,7 @@ class PeerContext:
     def begin_step(self):
         """After backward: publish "my gradients are complete" and wait for every peer's."""
         self.epoch += 1
+        self.stale_state = True
         self._barrier(0)
         for off, n in self.fallback_ranges:
             dist.all_reduce(self.G[off : off + n], op=dist.ReduceOp.AVG, group=self.group)
@@ -212,6 +214,7 @@ class PeerContext:
         others in a scratch copy and the copies are summed across ranks, so afterwards all ranks hold the same,
         complete state (and a checkpoint written by one rank resumes correctly under any world size)."""
         self.consolidations += 1
+        self.stale_state = False
         for opt in self._optimizers:
             for group in getattr(opt, "param_groups", []):
                 plan = self.plans.get(id(group))
@@ -291,6 +294,19 @@ def wrap(model: torch.nn.Module, optimizer=None, mode: str = "peer", **kwargs):
 
         optimizer.step = step
         optimizer.zero_grad = lambda set_to_none=True: None  # the slab is cleared by end_step
+        real_state_dict = optimizer.state_dict
+
+        def state_dict(*a, **kw):
+            if ctx.stale_state:
+                import warnings
+
+                warnings.warn(
+                    "optimizer state is partitioned across ranks under peer data parallelism: call "
+                    "`model.peer.consolidate_state()` on every rank before `state_dict()`, or this checkpoint holds only "
+                    "the part this rank owns", stacklevel=2)
+            return real_state_dict(*a, **kw)
+
+        optimizer.state_dict = state_dict
         return _PeerModule(model, ctx)
     from torch.nn.parallel import DistributedDataParallel
 

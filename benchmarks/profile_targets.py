@@ -5,6 +5,7 @@
     python benchmarks/profile_targets.py adam_small      # fused AdamW over 64M fp32 parameters (768 MB state+params)
     python benchmarks/profile_targets.py ce_small        # cross-entropy fwd+bwd kernel, 4096 x 50304 bf16 logits (412 MB)
     python benchmarks/profile_targets.py ln_small        # LayerNorm fwd + bwd kernels, 16384 x 768 fp32 (50 MB) x 4 tensors
+    python benchmarks/profile_targets.py gelu_small      # GELU fwd, and bwd + bias gradient, 16384 x 3072 bf16 (100 MB per tensor)
     python benchmarks/profile_targets.py tf32_small      # split-tf32 GEMM, 4 x (2048 x 2048 x 2048)
     python benchmarks/profile_targets.py qr_small        # panel-wise Cholesky QR of 8 x (1024 x 1024), eager launches
 
@@ -113,15 +114,37 @@ def ln_small():
     w, b = torch.rand(d, device="cuda") + 0.5, torch.randn(d, device="cuda")
     dy = torch.randn(rows, d, device="cuda").to(torch.bfloat16)
     ext = ops.load()
-    y, mean, rstd = ext.layer_norm_fwd(x, w, b, 1e-5, True)
-    us_f = _timed(lambda: ext.layer_norm_fwd(x, w, b, 1e-5, True))
-    us_b = _timed(lambda: ext.layer_norm_bwd(dy, x, w, mean, rstd))
+    y, mean, rstd = ext.layer_norm_fwd(x, None, w, b, 1e-5, True)
+    us_f = _timed(lambda: ext.layer_norm_fwd(x, None, w, b, 1e-5, True))
+    us_b = _timed(lambda: ext.layer_norm_bwd(dy, x, w, mean, rstd, None))
     print(f"layer_norm fwd {rows}x{d}: {us_f:.1f} us, {(rows * d * 6) / us_f / 1e3:.0f} GB/s (fp32 in, bf16 out)")
     print(f"layer_norm bwd {rows}x{d}: {us_b:.1f} us, {(rows * d * 10) / us_b / 1e3:.0f} GB/s (bf16 dy + fp32 x in, fp32 dx out)")
     torch.cuda.synchronize()
     torch.cuda.profiler.start()
-    ext.layer_norm_fwd(x, w, b, 1e-5, True)
-    ext.layer_norm_bwd(dy, x, w, mean, rstd)
+    ext.layer_norm_fwd(x, None, w, b, 1e-5, True)
+    ext.layer_norm_bwd(dy, x, w, mean, rstd, None)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+
+
+def gelu_small():
+    rows, cols = 16384, 3072
+    u = (torch.randn(rows, cols, device="cuda") * 2).to(torch.bfloat16)
+    dy = torch.randn(rows, cols, device="cuda").to(torch.bfloat16)
+    ext = ops.load()
+    uf = u.clone().requires_grad_()
+    yf = torch.nn.functional.gelu(uf, approximate="tanh")
+    n = rows * cols
+    us_f = _timed(lambda: ext.gelu_fwd(u))
+    us_b = _timed(lambda: ext.gelu_bwd(dy, u))
+    us_ff = _timed(lambda: torch.nn.functional.gelu(u, approximate="tanh"))
+    us_fb = _timed(lambda: torch.autograd.grad(yf, uf, dy, retain_graph=True)) + _timed(lambda: ext.colsum_bf16(dy))
+    print(f"gelu fwd {rows}x{cols} bf16: {us_f:.1f} us, {n * 4 / us_f / 1e3:.0f} GB/s; framework kernel {us_ff:.1f} us")
+    print(f"gelu bwd + bias gradient: {us_b:.1f} us, {n * 6 / us_b / 1e3:.0f} GB/s; framework backward + column-sum kernel {us_fb:.1f} us")
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    ext.gelu_fwd(u)
+    ext.gelu_bwd(dy, u)
     torch.cuda.synchronize()
     torch.cuda.profiler.stop()
 
@@ -167,4 +190,4 @@ def qr_small():
 
 if __name__ == "__main__":
     {"qr_small": qr_small, "opt_step_gpt2": opt_step_gpt2, "ns_small": ns_small, "adam_small": adam_small, "ce_small": ce_small,
-     "ln_small": ln_small, "tf32_small": tf32_small}[sys.argv[1]]()
+     "ln_small": ln_small, "tf32_small": tf32_small, "gelu_small": gelu_small}[sys.argv[1]]()

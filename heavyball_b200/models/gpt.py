@@ -13,7 +13,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops.nn import CastCache, LayerNorm, Linear, _bf16_training, linear, linear_cross_entropy
+from ..ops.nn import CastCache, LayerNorm, Linear, _bf16_training, linear_cross_entropy, linear_gelu, split_linear
 
 
 @dataclass
@@ -53,19 +53,18 @@ class Block(nn.Module):
         # One packed [3D, D] parameter (the shape the matrix optimizers see), three projections: each of q, k, v
         # is then dense in [B, T, H, hd] order, so neither the attention output nor the three gradients coming
         # back from the attention kernel need a strided copy / concatenation (about 0.3 ms per layer otherwise).
+        # One autograd node for the three: input gradient accumulated inside the GEMMs, packed weight gradient.
         if pending is None:
             h = self.ln1(x)
         else:
             x, h = self.ln1(x, pending)
-        w, b, w16, b16 = self.qkv.weight, self.qkv.bias, self.qkv.w16, self.qkv.b16
         q, k, v = (
-            linear(h, w[sl], b[sl], None if w16 is None else w16[sl], None if b16 is None else b16[sl])
-            .view(B, T, self.n_head, D // self.n_head).transpose(1, 2)
-            for sl in (slice(i * D, (i + 1) * D) for i in range(3))
+            t.view(B, T, self.n_head, D // self.n_head).transpose(1, 2)
+            for t in split_linear(h, self.qkv.weight, self.qkv.bias, 3, self.qkv.w16, self.qkv.b16)
         )
         a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         x, h = self.ln2(x, self.proj(a.transpose(1, 2).reshape(B, T, D)))
-        return x, self.out(F.gelu(self.fc(h), approximate="tanh"))
+        return x, self.out(linear_gelu(h, self.fc.weight, self.fc.bias, self.fc.w16, self.fc.b16))
 
 
 class GPT(nn.Module):

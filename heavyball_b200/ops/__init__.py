@@ -31,7 +31,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _SRC = os.path.join(_HERE, "csrc")
 _BUILD = os.path.join(_HERE, "_build")
 _NAME = "hb200_ops"
-_SOURCES = ["bindings.cpp", "colsum.cu", "cross_entropy.cu", "fused_chain.cu", "layer_norm.cu", "ns_gemm.cu", "noalloc_adamw.cu", "peer_sync.cu", "skinny.cu", "tf32_gemm.cu"]
+_SOURCES = ["bindings.cpp", "colsum.cu", "cross_entropy.cu", "fused_chain.cu", "gelu.cu", "layer_norm.cu", "ns_gemm.cu", "noalloc_adamw.cu", "peer_sync.cu", "skinny.cu", "tf32_gemm.cu"]
 _lock = threading.Lock()
 _ext = None
 _load_error: Optional[BaseException] = None

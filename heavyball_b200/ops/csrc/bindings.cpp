@@ -10,6 +10,7 @@
 #include "colsum.h"
 #include "cross_entropy.h"
 #include "fused_chain.h"
+#include "gelu.h"
 #include "layer_norm.h"
 #include "ns_gemm.h"
 #include "peer_sync.h"
@@ -260,6 +261,34 @@ at::Tensor colsum_bf16(const at::Tensor& x) {
   return out;
 }
 
+// y = gelu_tanh(u) for a contiguous bf16 tensor whose element count is a multiple of 8.
+at::Tensor gelu_fwd(const at::Tensor& u) {
+  TORCH_CHECK(u.is_cuda() && u.scalar_type() == at::kBFloat16 && u.is_contiguous() && u.numel() % 8 == 0 &&
+                  aligned16(u.data_ptr()), "gelu_fwd: contiguous bf16, numel % 8 == 0");
+  c10::cuda::CUDAGuard guard(u.device());
+  at::Tensor y = at::empty_like(u);
+  check(hb::launch_gelu_fwd(u.data_ptr(), y.data_ptr(), u.numel(), at::cuda::getCurrentCUDAStream()), "gelu_fwd launch");
+  return y;
+}
+
+// (du, dbias) = (dy * gelu_tanh'(u), column sums of that product in fp32) for contiguous bf16 [rows, cols], cols % 8 == 0.
+std::vector<at::Tensor> gelu_bwd(const at::Tensor& dy, const at::Tensor& u) {
+  TORCH_CHECK(u.is_cuda() && u.dim() == 2 && u.scalar_type() == at::kBFloat16 && u.is_contiguous() && u.size(1) % 8 == 0 &&
+                  aligned16(u.data_ptr()), "gelu_bwd: u contiguous bf16 [rows, cols], cols % 8 == 0");
+  TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == at::kBFloat16 && dy.is_contiguous() && dy.sizes() == u.sizes() &&
+                  dy.device() == u.device() && aligned16(dy.data_ptr()), "gelu_bwd: dy like u");
+  c10::cuda::CUDAGuard guard(u.device());
+  const int64_t rows = u.size(0), cols = u.size(1);
+  at::Tensor du = at::empty_like(u);
+  at::Tensor dbias = at::zeros({cols}, u.options().dtype(at::kFloat));
+  if (rows > 0 && cols > 0) {
+    at::Tensor partial = at::empty({hb::gelu_bwd_splits(rows, (int)cols), cols}, dbias.options());
+    check(hb::launch_gelu_bwd(dy.data_ptr(), u.data_ptr(), du.data_ptr(), rows, (int)cols, partial.data_ptr<float>(),
+                              dbias.data_ptr<float>(), at::cuda::getCurrentCUDAStream()), "gelu_bwd launch");
+  }
+  return {du, dbias};
+}
+
 // LayerNorm over the last dimension of a contiguous fp32 tensor.  With `res` (same shape, bf16 or fp32) the normalised
 // tensor is x + res, which is returned as a fourth tensor.  Returns (y, mean, rstd[, x + res]); y is bf16 when asked.
 std::vector<at::Tensor> layer_norm_fwd(const at::Tensor& x, const OptT& res, const at::Tensor& gamma, const at::Tensor& beta,
@@ -314,6 +343,8 @@ std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tf32x3_matmul", &tf32x3_matmul);
   m.def("colsum_bf16", &colsum_bf16);
+  m.def("gelu_fwd", &gelu_fwd);
+  m.def("gelu_bwd", &gelu_bwd);
   m.def("tall_t_mul", &tall_t_mul);
   m.def("layer_norm_fwd", &layer_norm_fwd);
   m.def("layer_norm_bwd", &layer_norm_bwd);

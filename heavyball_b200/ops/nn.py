@@ -15,8 +15,14 @@ framework op it replaces as its fallback (CPU, other dtypes, unsupported shapes)
     gradient read, in bf16 directly.  ``add_layer_norm`` also performs the residual add that precedes the
     normalisation (and, on the way back, the add of the gradient arriving on the residual stream).
 ``linear`` / ``Linear`` / ``CastCache``
-    ``F.linear`` whose bias gradient comes from a column-sum kernel (``csrc/colsum.cu``) and whose bf16 weights
-    come from one multi-tensor cast per forward pass.
+    ``F.linear`` whose bias gradient comes from a column-sum kernel (``csrc/colsum.cu``), whose weight gradient
+    leaves its GEMM in fp32, and whose bf16 weights come from one multi-tensor cast per forward pass.
+``split_linear``
+    The packed q / k / v projection as one autograd node: three dense outputs, input gradient accumulated inside
+    the GEMMs, one packed weight / bias gradient.
+``linear_gelu``
+    Linear layer followed by tanh-GELU (``csrc/gelu.cu``): the activation's backward kernel also sums the bias
+    gradient.
 """
 
 from __future__ import annotations
@@ -158,9 +164,35 @@ class LayerNorm(torch.nn.LayerNorm):
         return add_layer_norm(x, res, self.weight, self.bias, self.eps)
 
 
+def _weight_grad(dy2: torch.Tensor, x2: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``dy2^T @ x2`` for bf16 operands, written in fp32 (the parameter's dtype) by the GEMM itself instead of in
+    bf16 followed by a cast kernel; ``out`` may be a row slice of a packed gradient."""
+    if dy2.is_cuda:
+        if out is None:
+            return torch.mm(dy2.mT, x2, out_dtype=torch.float32)
+        return torch.mm(dy2.mT, x2, out_dtype=torch.float32, out=out)
+    dw = (dy2.mT @ x2).float()  # the fp32-output GEMM exists on CUDA only
+    return dw if out is None else out.copy_(dw)
+
+
+def _bias_grad(dy2: torch.Tensor) -> torch.Tensor:
+    if dy2.is_cuda and dy2.shape[1] % 8 == 0 and dy2.data_ptr() % 16 == 0:
+        launch_counter.count += 2
+        return load().colsum_bf16(dy2)
+    return dy2.float().sum(0)
+
+
+def _as_bf16_rows(dy: torch.Tensor) -> torch.Tensor:
+    dy2 = dy.reshape(-1, dy.shape[-1])
+    if dy2.dtype != torch.bfloat16:
+        dy2 = dy2.to(torch.bfloat16)
+    return dy2 if dy2.is_contiguous() else dy2.contiguous()
+
+
 class _LinearFn(torch.autograd.Function):
     """``x @ w^T + b`` computed from bf16 copies ``w16`` / ``b16`` of the fp32 parameters; gradients are routed
-    to the fp32 parameters, the bias gradient comes from the column-sum kernel."""
+    to the fp32 parameters (the weight gradient leaves its GEMM in fp32), the bias gradient comes from the
+    column-sum kernel."""
 
     @staticmethod
     def forward(ctx, x, weight, bias, w16, b16):
@@ -172,23 +204,93 @@ class _LinearFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x16, w16 = ctx.saved_tensors
-        dy2 = dy.reshape(-1, dy.shape[-1])
-        if dy2.dtype != torch.bfloat16:
-            dy2 = dy2.to(torch.bfloat16)
-        if not dy2.is_contiguous():
-            dy2 = dy2.contiguous()
+        dy2 = _as_bf16_rows(dy)
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
             dx = (dy2 @ w16).reshape(x16.shape).to(ctx.x_dtype)
         if ctx.needs_input_grad[1]:
-            dw = dy2.mT @ x16.reshape(-1, x16.shape[-1])
+            dw = _weight_grad(dy2, x16.reshape(-1, x16.shape[-1]))
         if ctx.needs_input_grad[2]:
-            if dy2.shape[1] % 8 == 0 and dy2.data_ptr() % 16 == 0:
-                db = load().colsum_bf16(dy2)
-                launch_counter.count += 2
-            else:
-                db = dy2.float().sum(0)
+            db = _bias_grad(dy2)
         return dx, dw, db, None, None
+
+
+class _SplitLinearFn(torch.autograd.Function):
+    """``n`` projections of the same input by equal row blocks of one packed weight, each into its own dense
+    output (packed q / k / v).  Backward accumulates the input gradient inside the GEMMs (``beta = 1``) and writes
+    each block of the weight and bias gradients into its rows of one packed gradient; taking the row blocks as
+    views instead costs, per block, a zero-filled full-size gradient plus an add, and an add per extra input
+    gradient."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, w16, b16, n):
+        x16 = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+        ctx.save_for_backward(x16, w16)
+        ctx.x_dtype, ctx.n = x.dtype, n
+        rows = w16.shape[0] // n
+        return tuple(F.linear(x16, w16[i * rows : (i + 1) * rows], b16[i * rows : (i + 1) * rows]) for i in range(n))
+
+    @staticmethod
+    def backward(ctx, *dys):
+        x16, w16 = ctx.saved_tensors
+        n, rows = ctx.n, w16.shape[0] // ctx.n
+        x2 = x16.reshape(-1, x16.shape[-1])
+        parts = [None if dy is None else _as_bf16_rows(dy) for dy in dys]
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            for i, dy2 in enumerate(parts):
+                if dy2 is None:
+                    continue
+                blk = w16[i * rows : (i + 1) * rows]
+                dx = dy2 @ blk if dx is None else dx.addmm_(dy2, blk)
+            if dx is not None:
+                dx = dx.reshape(x16.shape).to(ctx.x_dtype)
+        if ctx.needs_input_grad[1]:
+            dw = torch.empty(w16.shape, dtype=torch.float32, device=w16.device)
+            for i, dy2 in enumerate(parts):
+                if dy2 is None:
+                    dw[i * rows : (i + 1) * rows].zero_()
+                else:
+                    _weight_grad(dy2, x2, out=dw[i * rows : (i + 1) * rows])
+        if ctx.needs_input_grad[2]:
+            zero = None
+            cols = []
+            for dy2 in parts:
+                if dy2 is None:
+                    zero = torch.zeros(rows, dtype=torch.float32, device=w16.device) if zero is None else zero
+                    cols.append(zero)
+                else:
+                    cols.append(_bias_grad(dy2))
+            db = torch.cat(cols)
+        return dx, dw, db, None, None, None
+
+
+class _LinearGeluFn(torch.autograd.Function):
+    """``gelu_tanh(x @ w^T + b)`` for the first half of a transformer MLP.  Forward: the library GEMM (bias in its
+    epilogue) and one activation kernel; backward: one kernel gives the gradient at the GEMM output and, from the
+    same pass, the bias gradient, then the two gradient GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, w16, b16):
+        x16 = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+        u = F.linear(x16, w16, b16)
+        y = load().gelu_fwd(u)
+        launch_counter.count += 1
+        ctx.save_for_backward(x16, w16, u)
+        ctx.x_dtype = x.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x16, w16, u = ctx.saved_tensors
+        du, db = load().gelu_bwd(_as_bf16_rows(dy), u.reshape(-1, u.shape[-1]))
+        launch_counter.count += 2
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = (du @ w16).reshape(x16.shape).to(ctx.x_dtype)
+        if ctx.needs_input_grad[1]:
+            dw = _weight_grad(du, x16.reshape(-1, x16.shape[-1]))
+        return dx, dw, db if ctx.needs_input_grad[2] else None, None, None
 
 
 def _bf16_training(x: torch.Tensor) -> bool:
@@ -207,6 +309,31 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
             w16, b16 = weight.detach().to(torch.bfloat16), bias.detach().to(torch.bfloat16)
         return _LinearFn.apply(x, weight, bias, w16, b16)
     return F.linear(x, weight, bias)
+
+
+def linear_gelu(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, w16: torch.Tensor | None = None,
+                b16: torch.Tensor | None = None) -> torch.Tensor:  # fmt: skip
+    """``F.gelu(F.linear(x, weight, bias), approximate="tanh")``.  Under bf16 autocast on sm_100a, with an output
+    width that is a multiple of 8, the activation and its backward run in this package's kernels and the backward
+    kernel also produces the bias gradient (see :class:`_LinearGeluFn`); elsewhere it is the two framework calls."""
+    if bias is not None and weight.shape[0] % 8 == 0 and _bf16_training(x):
+        if w16 is None:
+            w16, b16 = weight.detach().to(torch.bfloat16), bias.detach().to(torch.bfloat16)
+        return _LinearGeluFn.apply(x, weight, bias, w16, b16)
+    return F.gelu(linear(x, weight, bias, w16, b16), approximate="tanh")
+
+
+def split_linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, n: int, w16: torch.Tensor | None = None,
+                 b16: torch.Tensor | None = None) -> tuple:  # fmt: skip
+    """``n`` outputs ``x @ weight[i]^T + bias[i]`` for the ``n`` equal row blocks of a packed projection (q, k, v),
+    each dense.  Under bf16 autocast on sm_100a one autograd node covers all of them (see :class:`_SplitLinearFn`);
+    elsewhere it is ``n`` calls of ``F.linear`` on row slices."""
+    rows = weight.shape[0] // n
+    if _bf16_training(x):
+        if w16 is None:
+            w16, b16 = weight.detach().to(torch.bfloat16), bias.detach().to(torch.bfloat16)
+        return _SplitLinearFn.apply(x, weight, bias, w16, b16, n)
+    return tuple(F.linear(x, weight[i * rows : (i + 1) * rows], bias[i * rows : (i + 1) * rows]) for i in range(n))
 
 
 class Linear(torch.nn.Linear):

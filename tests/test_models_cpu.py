@@ -10,7 +10,7 @@ import torch.nn.functional as F
 import heavyball_b200 as hb
 from heavyball_b200.models import GPT, GPTConfig, Llama, LlamaConfig, split_param_groups
 from heavyball_b200.models.gpt import padded_vocab
-from heavyball_b200.ops.nn import add_layer_norm, layer_norm, linear, linear_cross_entropy
+from heavyball_b200.ops.nn import add_layer_norm, layer_norm, linear, linear_cross_entropy, linear_gelu
 
 
 def test_padded_vocab():
@@ -45,6 +45,7 @@ def test_fallback_ops_are_the_framework_ops():
     assert s0 is x and torch.equal(y0, F.layer_norm(x, (128,), w, b, 1e-5))
     lw, lb = torch.randn(32, 128), torch.randn(32)
     assert torch.equal(linear(x, lw, lb), F.linear(x, lw, lb))
+    assert torch.equal(linear_gelu(x, lw, lb), F.gelu(F.linear(x, lw, lb), approximate="tanh"))
     t = torch.randint(0, 30, (4, 10))
     t[0, 0] = -100
     ref = F.cross_entropy(F.linear(x, lw)[..., :30].reshape(-1, 30), t.reshape(-1), ignore_index=-100)
@@ -81,3 +82,26 @@ def test_gpt_causality():
     b[0, -1] = (b[0, -1] + 1) % 50
     la, lb = model(a), model(b)
     assert torch.allclose(la[:, :-1], lb[:, :-1], atol=1e-6) and not torch.allclose(la[:, -1], lb[:, -1])
+
+
+def test_split_linear_node_matches_autograd_of_the_packed_projection():
+    """The single autograd node behind the packed q / k / v projection, driven directly (on CPU the public entry
+    point takes the plain path): gradients equal those of one ``F.linear`` on the same bf16 operands."""
+    from heavyball_b200.ops.nn import _SplitLinearFn, split_linear
+
+    torch.manual_seed(0)
+    x = torch.randn(4, 10, 32).to(torch.bfloat16).requires_grad_()
+    w = torch.randn(96, 32, requires_grad=True)
+    b = torch.randn(96, requires_grad=True)
+    w16, b16 = w.detach().to(torch.bfloat16), b.detach().to(torch.bfloat16)
+    outs = _SplitLinearFn.apply(x, w, b, w16, b16, 3)
+    dys = [torch.randn_like(o) for o in outs]
+    torch.autograd.backward(outs, dys)
+    x2, w2, b2 = x.detach().float().requires_grad_(), w16.float().requires_grad_(), b16.float().requires_grad_()
+    F.linear(x2, w2, b2).backward(torch.cat(dys, -1).float())
+    assert w.grad.dtype == torch.float32 and b.grad.dtype == torch.float32 and x.grad.dtype == torch.bfloat16
+    assert torch.allclose(w.grad, w2.grad, atol=0.1, rtol=2e-2)
+    assert torch.allclose(b.grad, b2.grad, atol=1e-4)
+    assert torch.allclose(x.grad.float(), x2.grad, atol=0.2, rtol=2e-2)
+    plain = split_linear(x.detach().float(), w.detach(), b.detach(), 3)
+    assert torch.allclose(torch.cat(plain, -1), F.linear(x.detach().float(), w.detach(), b.detach()), atol=1e-5)

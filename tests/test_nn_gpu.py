@@ -140,6 +140,92 @@ def test_linear_under_autocast_matches_framework_linear():
     assert torch.equal(linear(x.detach(), w.detach(), b.detach()), F.linear(x.detach(), w.detach(), b.detach()))
 
 
+def test_split_linear_matches_fp32_definition_of_the_packed_projection():
+    from heavyball_b200.ops.nn import split_linear
+
+    torch.manual_seed(0)
+    d, n = 256, 3
+    x = torch.randn(4, 96, d, device="cuda").to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(n * d, d, device="cuda") * 0.05).requires_grad_()
+    b = torch.randn(n * d, device="cuda").requires_grad_()
+    dys = [torch.randn(4, 96, d, device="cuda").to(torch.bfloat16) for _ in range(n)]
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        outs = split_linear(x, w, b, n)
+    assert len(outs) == n and all(o.is_contiguous() and o.dtype == torch.bfloat16 for o in outs)
+    torch.autograd.backward(outs, dys)
+    assert w.grad.dtype == torch.float32 and w.grad.shape == w.shape and b.grad.shape == b.shape
+
+    # fp32 definition on the same bf16-rounded operands
+    x2 = x.detach().float().requires_grad_()
+    w2 = w.detach().to(torch.bfloat16).float().requires_grad_()
+    b2 = b.detach().to(torch.bfloat16).float().requires_grad_()
+    ref = F.linear(x2, w2, b2)
+    ref.backward(torch.cat(dys, -1).float())
+    for o, r in zip(outs, ref.split(d, -1)):
+        assert torch.allclose(o.float(), r, atol=2e-2, rtol=1e-2)
+    assert torch.allclose(w.grad, w2.grad, atol=1e-3, rtol=1e-4)  # fp32 straight out of the GEMM
+    assert torch.allclose(b.grad, b2.grad, atol=1e-3, rtol=1e-4)
+    assert torch.allclose(x.grad.float(), x2.grad, atol=3e-2, rtol=2e-2)  # bf16 accumulation across the three GEMMs
+
+    # one output unused: its rows of the packed gradients are zero
+    w.grad = b.grad = x.grad = None
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        outs = split_linear(x, w, b, n)
+    (outs[0].float() * dys[0].float()).sum().backward()
+    assert torch.allclose(w.grad[:d], w2.grad[:d], atol=1e-3, rtol=1e-4)
+    assert (w.grad[d:] == 0).all() and (b.grad[d:] == 0).all()
+    # outside autocast: plain slices
+    plain = split_linear(x.detach().float(), w.detach(), b.detach(), n)
+    assert torch.allclose(torch.cat(plain, -1), F.linear(x.detach().float(), w.detach(), b.detach()), atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("rows,cols", [(16384, 3072), (1000, 3072), (37, 8), (5, 264), (1, 512)])
+def test_gelu_kernels_match_fp32_definition(rows, cols):
+    torch.manual_seed(0)
+    u = (torch.randn(rows, cols, device="cuda") * 3).to(torch.bfloat16)
+    u[0, :8] = torch.tensor([0.0, -0.0, 30.0, -30.0, 200.0, -200.0, 1e-3, -1e-3], device="cuda").to(torch.bfloat16)
+    dy = torch.randn(rows, cols, device="cuda").to(torch.bfloat16)
+    ext = ops.load()
+    y = ext.gelu_fwd(u)
+    du, db = ext.gelu_bwd(dy, u)
+    ops.check_status()
+
+    uf = u.float().requires_grad_()
+    ref = F.gelu(uf, approximate="tanh")
+    ref.backward(dy.float())
+    assert y.dtype == torch.bfloat16 and du.dtype == torch.bfloat16 and db.dtype == torch.float32
+    # one rounding to bf16 (at most 2^-8 relative) on top of fp32 arithmetic
+    assert torch.allclose(y.float(), ref.detach(), atol=1e-6, rtol=2.0**-7)
+    assert torch.allclose(du.float(), uf.grad, atol=1e-6, rtol=2.0**-7)
+    exact = uf.grad.double().sum(0)
+    scale = uf.grad.double().abs().sum(0).clamp_min(1e-30)
+    assert ((db.double() - exact).abs() / scale).max() < 1e-5  # fp32 sums of unrounded products
+
+
+def test_linear_gelu_matches_the_two_framework_calls():
+    from heavyball_b200.ops.nn import linear_gelu
+
+    torch.manual_seed(0)
+    x = torch.randn(4, 96, 256, device="cuda").to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(1024, 256, device="cuda") * 0.05).requires_grad_()
+    b = torch.randn(1024, device="cuda").requires_grad_()
+    dy = torch.randn(4, 96, 1024, device="cuda").to(torch.bfloat16)
+    x2, w2, b2 = (t.detach().clone().requires_grad_() for t in (x, w, b))
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = linear_gelu(x, w, b)
+        y2 = F.gelu(F.linear(x2, w2, b2), approximate="tanh")
+    assert y.dtype == torch.bfloat16 and torch.allclose(y.float(), y2.float(), atol=1e-6, rtol=2.0**-7)
+    y.backward(dy)
+    y2.backward(dy)
+    assert w.grad.dtype == torch.float32 and b.grad.dtype == torch.float32
+    assert torch.allclose(x.grad.float(), x2.grad.float(), atol=2e-2, rtol=2e-2)
+    assert torch.allclose(w.grad, w2.grad, atol=5e-2, rtol=1e-2)
+    assert torch.allclose(b.grad, b2.grad, atol=0.15, rtol=1e-2)
+    # outside autocast: the framework calls
+    xd, wd, bd = x.detach().float(), w.detach(), b.detach()
+    assert torch.equal(linear_gelu(xd, wd, bd), F.gelu(F.linear(xd, wd, bd), approximate="tanh"))
+
+
 def test_cast_cache_follows_parameter_updates_made_by_the_kernels():
     """The optimizer kernels write parameters through raw pointers (no autograd version bump): the bf16 copies
     must still be current in the next forward pass."""

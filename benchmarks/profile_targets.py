@@ -113,16 +113,17 @@ def ln_small():
     x = torch.randn(rows, d, device="cuda")
     w, b = torch.rand(d, device="cuda") + 0.5, torch.randn(d, device="cuda")
     dy = torch.randn(rows, d, device="cuda").to(torch.bfloat16)
+    dres = torch.randn(rows, d, device="cuda")  # gradient arriving on the residual stream
     ext = ops.load()
     y, mean, rstd = ext.layer_norm_fwd(x, None, w, b, 1e-5, True)
     us_f = _timed(lambda: ext.layer_norm_fwd(x, None, w, b, 1e-5, True))
-    us_b = _timed(lambda: ext.layer_norm_bwd(dy, x, w, mean, rstd, None))
+    us_b = _timed(lambda: ext.layer_norm_bwd(dy, x, w, mean, rstd, dres, True))
     print(f"layer_norm fwd {rows}x{d}: {us_f:.1f} us, {(rows * d * 6) / us_f / 1e3:.0f} GB/s (fp32 in, bf16 out)")
-    print(f"layer_norm bwd {rows}x{d}: {us_b:.1f} us, {(rows * d * 10) / us_b / 1e3:.0f} GB/s (bf16 dy + fp32 x in, fp32 dx out)")
+    print(f"layer_norm bwd {rows}x{d}: {us_b:.1f} us, {(rows * d * 16) / us_b / 1e3:.0f} GB/s (bf16 dy + fp32 x + fp32 residual-stream gradient in, fp32 + bf16 dx out)")
     torch.cuda.synchronize()
     torch.cuda.profiler.start()
     ext.layer_norm_fwd(x, None, w, b, 1e-5, True)
-    ext.layer_norm_bwd(dy, x, w, mean, rstd, None)
+    ext.layer_norm_bwd(dy, x, w, mean, rstd, dres, True)
     torch.cuda.synchronize()
     torch.cuda.profiler.stop()
 

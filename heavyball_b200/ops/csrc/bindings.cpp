@@ -280,7 +280,7 @@ std::vector<at::Tensor> gelu_bwd(const at::Tensor& dy, const at::Tensor& u) {
   c10::cuda::CUDAGuard guard(u.device());
   const int64_t rows = u.size(0), cols = u.size(1);
   at::Tensor du = at::empty_like(u);
-  at::Tensor dbias = at::zeros({cols}, u.options().dtype(at::kFloat));
+  at::Tensor dbias = rows > 0 ? at::empty({cols}, u.options().dtype(at::kFloat)) : at::zeros({cols}, u.options().dtype(at::kFloat));
   if (rows > 0 && cols > 0) {
     at::Tensor partial = at::empty({hb::gelu_bwd_splits(rows, (int)cols), cols}, dbias.options());
     check(hb::launch_gelu_bwd(dy.data_ptr(), u.data_ptr(), du.data_ptr(), rows, (int)cols, partial.data_ptr<float>(),
@@ -316,9 +316,9 @@ std::vector<at::Tensor> layer_norm_fwd(const at::Tensor& x, const OptT& res, con
   return {y, mean, rstd};
 }
 
-// Returns (dx, dgamma, dbeta) for dy in fp32 or bf16; `dres` (fp32, optional) is added to dx.
+// Returns (dx, dgamma, dbeta[, bf16 copy of dx]) for dy in fp32 or bf16; `dres` (fp32, optional) is added to dx.
 std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& gamma,
-                                       const at::Tensor& mean, const at::Tensor& rstd, const OptT& dres) {
+                                       const at::Tensor& mean, const at::Tensor& rstd, const OptT& dres, bool dx_bf16) {
   const int64_t D = x.size(-1);
   TORCH_CHECK(dy.is_cuda() && dy.is_contiguous() && dy.numel() == x.numel() &&
                   (dy.scalar_type() == at::kFloat || dy.scalar_type() == at::kBFloat16), "dy: contiguous fp32 / bf16");
@@ -332,11 +332,13 @@ std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x
   const int n_cta = hb::layer_norm_partial_ctas(rows);
   at::Tensor dx = at::empty_like(x), dgamma = at::empty_like(gamma), dbeta = at::empty_like(gamma);
   at::Tensor partial = at::empty({n_cta, 2 * D}, x.options());
+  at::Tensor dx16 = dx_bf16 ? at::empty(x.sizes(), x.options().dtype(at::kBFloat16)) : at::Tensor();
   check(hb::launch_layer_norm_bwd(dy.data_ptr(), dy.scalar_type() == at::kBFloat16, x.data_ptr<float>(),
                                   gamma.data_ptr<float>(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
                                   has_dres ? dres->data_ptr<float>() : nullptr, dx.data_ptr<float>(),
-                                  dgamma.data_ptr<float>(), dbeta.data_ptr<float>(), partial.data_ptr<float>(), n_cta, rows,
+                                  dx_bf16 ? dx16.data_ptr() : nullptr, dgamma.data_ptr<float>(), dbeta.data_ptr<float>(), partial.data_ptr<float>(), n_cta, rows,
                                   (int)D, at::cuda::getCurrentCUDAStream()), "layer_norm_bwd launch");
+  if (dx_bf16) return {dx, dgamma, dbeta, dx16};
   return {dx, dgamma, dbeta};
 }
 

@@ -5,7 +5,9 @@
 // Backward: du = dy * gelu'(u), and in the same pass the column sums of du, i.e. the bias gradient of the linear
 // layer that produced u.  Computed separately that is a second full read of du (100 MB for 16384 x 3072) by a
 // column-sum kernel.  A CTA owns a strip of 256 columns (one warp reads 512 contiguous bytes of a row) and 1/splits
-// of the rows; its 8 warps take every 8th row, four rows in flight per warp.  Column sums are kept in fp32 registers
+// of the rows; its 8 warps take every 8th row, two rows in flight per warp.  The kernel issues about 30 instructions
+// per element (fp32 exp and reciprocal included), so it needs occupancy more than loads in flight: with four rows
+// in flight (80 registers, three CTAs per SM) the issue slots were 67 % busy and DRAM 49 %.  Column sums are kept in fp32 registers
 // (from the values before they are rounded to bf16), combined across the 8 warps through shared memory and written
 // to partial[split][c]; a second kernel adds the splits (deterministic: no atomics).
 //
@@ -23,8 +25,9 @@ constexpr float kK0 = 0.7978845608028654f;  // sqrt(2 / pi)
 constexpr float kK1 = 0.044715f;
 constexpr int kStrip = 256;     // columns per CTA in the backward kernel
 constexpr int kRowLanes = 8;    // warps per CTA, one row each per step
-constexpr int kInFlight = 4;    // rows (backward) or vectors (forward) loaded before any is consumed
-constexpr int kResident = 3;    // backward CTAs per SM the launch bounds ask for
+constexpr int kInFlight = 4;    // vectors per thread the forward kernel loads before any is consumed
+constexpr int kBwdRows = 2;     // rows per warp the backward kernel loads (dy and u) before any is consumed
+constexpr int kResident = 4;    // backward CTAs per SM the launch bounds ask for (63 registers per thread)
 constexpr int kSMs = 148;
 constexpr int kMaxSplits = 64;
 
@@ -81,10 +84,10 @@ __global__ void __launch_bounds__(256, kResident)
   const long long r_end = r_begin + per < rows ? r_begin + per : rows;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   if (c0 < cols) {  // cols is a multiple of 8: a vector is inside or outside as a whole
-    for (long long r = r_begin + lane_r; r < r_end; r += kRowLanes * kInFlight) {
-      uint4 g[kInFlight], a[kInFlight];
+    for (long long r = r_begin + lane_r; r < r_end; r += kRowLanes * kBwdRows) {
+      uint4 g[kBwdRows], a[kBwdRows];
 #pragma unroll
-      for (int i = 0; i < kInFlight; ++i) {
+      for (int i = 0; i < kBwdRows; ++i) {
         const long long rr = r + (long long)i * kRowLanes;
         if (rr < r_end) {
           g[i] = *reinterpret_cast<const uint4*>(dy + rr * cols + c0);
@@ -92,7 +95,7 @@ __global__ void __launch_bounds__(256, kResident)
         }
       }
 #pragma unroll
-      for (int i = 0; i < kInFlight; ++i) {
+      for (int i = 0; i < kBwdRows; ++i) {
         const long long rr = r + (long long)i * kRowLanes;
         if (rr >= r_end) continue;
         const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&g[i]);
@@ -145,7 +148,7 @@ int gelu_bwd_splits(long long rows, int cols) {
   // one full wave of resident CTAs over the strips; every split has at least one step of rows
   const int strips = (cols + kStrip - 1) / kStrip;
   long long s = (kSMs * kResident) / strips;
-  const long long by_rows = (rows + kRowLanes * kInFlight - 1) / (kRowLanes * kInFlight);
+  const long long by_rows = (rows + kRowLanes * kBwdRows - 1) / (kRowLanes * kBwdRows);
   if (s > by_rows) s = by_rows;
   if (s > kMaxSplits) s = kMaxSplits;
   return s < 1 ? 1 : (int)s;

@@ -15,8 +15,9 @@ cudaError_t launch_layer_norm_fwd(const float* x, const void* res, bool res_bf16
                                   float eps, cudaStream_t stream);
 
 // x is the normalised tensor (x + res when a residual was given).  dres (optional, fp32): added to dx.
+// dx_bf16 (optional): receives a bf16 copy of dx.
 cudaError_t launch_layer_norm_bwd(const void* dy, bool dy_bf16, const float* x, const float* gamma, const float* mean,
-                                  const float* rstd, const float* dres, float* dx, float* dgamma, float* dbeta,
-                                  float* partial, int n_cta, long long rows, int D, cudaStream_t stream);
+                                  const float* rstd, const float* dres, float* dx, void* dx_bf16, float* dgamma,
+                                  float* dbeta, float* partial, int n_cta, long long rows, int D, cudaStream_t stream);
 
 }  // namespace hb

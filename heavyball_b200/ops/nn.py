@@ -92,7 +92,7 @@ class _LayerNormFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x, weight, mean, rstd = ctx.saved_tensors
-        dx, dw, db = load().layer_norm_bwd(dy.contiguous(), x, weight, mean, rstd, None)
+        dx, dw, db = load().layer_norm_bwd(dy.contiguous(), x, weight, mean, rstd, None, False)
         launch_counter.count += 2
         return dx, dw, db, None, None
 
@@ -115,9 +115,11 @@ class _AddLayerNormFn(torch.autograd.Function):
         if dy is None:  # the normalised output was not used
             return ds, None if ds is None else ds.to(ctx.res_dtype), None, None, None, None
         ds = None if ds is None else ds.contiguous()
-        dx, dw, db = load().layer_norm_bwd(dy.contiguous(), s, weight, mean, rstd, ds)
+        # a bf16 residual branch gets its gradient from the same kernel (no cast pass over dx)
+        out = load().layer_norm_bwd(dy.contiguous(), s, weight, mean, rstd, ds, ctx.res_dtype == torch.bfloat16)
         launch_counter.count += 2
-        return dx, dx.to(ctx.res_dtype), dw, db, None, None
+        dx, dw, db = out[:3]
+        return dx, out[3] if len(out) == 4 else dx.to(ctx.res_dtype), dw, db, None, None
 
 
 def _ln_kernel_applies(x: torch.Tensor, weight, bias) -> bool:

@@ -330,6 +330,8 @@ def split_linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, n: i
     """``n`` outputs ``x @ weight[i]^T + bias[i]`` for the ``n`` equal row blocks of a packed projection (q, k, v),
     each dense.  Under bf16 autocast on sm_100a one autograd node covers all of them (see :class:`_SplitLinearFn`);
     elsewhere it is ``n`` calls of ``F.linear`` on row slices."""
+    if n < 1 or weight.shape[0] % n:
+        raise ValueError(f"split_linear: {weight.shape[0]} weight rows do not split into {n} equal blocks")
     rows = weight.shape[0] // n
     if _bf16_training(x):
         if w16 is None:

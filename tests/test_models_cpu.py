@@ -105,3 +105,5 @@ def test_split_linear_node_matches_autograd_of_the_packed_projection():
     assert torch.allclose(x.grad.float(), x2.grad, atol=0.2, rtol=2e-2)
     plain = split_linear(x.detach().float(), w.detach(), b.detach(), 3)
     assert torch.allclose(torch.cat(plain, -1), F.linear(x.detach().float(), w.detach(), b.detach()), atol=1e-5)
+    with pytest.raises(ValueError):
+        split_linear(x.detach().float(), w.detach(), b.detach(), 5)

@@ -8,6 +8,7 @@ Entry points
 ------------
 ``fused_chain``      one multi-tensor pass: decode -> MARS -> moment rule -> caution -> decay -> write
 ``sumsq``            per-tensor sum of squares (segmented reduction)
+``dot`` / ``absmax`` per-tensor dot products and absolute maxima (same chunk table)
 ``newton_schulz``    batched quintic Newton–Schulz / Polar-Express chain on tcgen05 tensor cores
 ``matmul3``          fp32 matrix product on the tf32 tensor cores (3-term split), for SOAP / PSGD algebra
 ``nn``               (sub-module) model-side ops: fused head + cross-entropy, LayerNorm (+ residual add), Linear with
@@ -163,6 +164,18 @@ def fused_chain(*, p=_EMPTY, pe=_EMPTY, g=_EMPTY, u=_EMPTY, s0=_EMPTY, s0e=_EMPT
 def sumsq(xs: Sequence[torch.Tensor]) -> torch.Tensor:
     launch_counter.count += 1
     return load().sumsq(list(xs), dtype_code(xs[0]))
+
+
+def dot(xs: Sequence[torch.Tensor], ys: Sequence[torch.Tensor]) -> torch.Tensor:
+    """fp32 ``[sum(x_i * y_i)]`` for contiguous tensors of one dtype (fp32 / bf16 / fp16), one launch."""
+    launch_counter.count += 1
+    return load().segmented_reduce(list(xs), list(ys), dtype_code(xs[0]), 0)
+
+
+def absmax(xs: Sequence[torch.Tensor]) -> torch.Tensor:
+    """fp32 ``[max |x_i|]`` for contiguous tensors of one dtype, one launch; a NaN element gives NaN."""
+    launch_counter.count += 1
+    return load().segmented_reduce(list(xs), [], dtype_code(xs[0]), 1)
 
 
 # ---------------------------------------------------------------------------------------- Newton–Schulz

@@ -138,6 +138,33 @@ at::Tensor sumsq(const std::vector<at::Tensor>& xs, int dt) {
   return out;
 }
 
+// out[i] = sum(x_i * y_i) (op 0) or max |x_i| (op 1, `ys` empty) in fp32; all tensors contiguous, one storage kind.
+at::Tensor segmented_reduce(const std::vector<at::Tensor>& xs, const std::vector<at::Tensor>& ys, int dt, int op) {
+  TORCH_CHECK(!xs.empty(), "segmented_reduce: empty list");
+  TORCH_CHECK(op == hb::kReduceAbsMax ? ys.empty() : ys.size() == xs.size(), "segmented_reduce: one y per x for the dot product");
+  c10::cuda::CUDAGuard guard(xs[0].device());
+  std::vector<hb::TensorMeta> metas(xs.size());
+  for (size_t i = 0; i < xs.size(); ++i) {
+    TORCH_CHECK(xs[i].is_cuda() && xs[i].is_contiguous() && xs[i].scalar_type() == xs[0].scalar_type(), "segmented_reduce: contiguous CUDA tensors of one dtype");
+    memset(&metas[i], 0, sizeof(hb::TensorMeta));
+    metas[i].u = xs[i].data_ptr();
+    metas[i].numel = xs[i].numel();
+    bool ok = aligned16(metas[i].u);
+    if (!ys.empty()) {
+      TORCH_CHECK(ys[i].is_cuda() && ys[i].is_contiguous() && ys[i].scalar_type() == xs[0].scalar_type() &&
+                      ys[i].numel() == xs[i].numel(), "segmented_reduce: y like x");
+      metas[i].g = ys[i].data_ptr();
+      ok = ok && aligned16(metas[i].g);
+    }
+    metas[i].vec_ok = ok ? 1 : 0;
+  }
+  Table t = upload(metas, xs[0].device());
+  at::Tensor out = at::zeros({(int64_t)xs.size()}, xs[0].options().dtype(at::kFloat));
+  check(hb::launch_segmented_reduce(t.metas, t.prefix, t.total_chunks, t.n, dt, op, out.data_ptr<float>(),
+                                    at::cuda::getCurrentCUDAStream()), "segmented_reduce launch");
+  return out;
+}
+
 // Normalise + stochastically round a batch of same-shape matrices into the two bf16 work layouts.
 void ns_prepare(const std::vector<at::Tensor>& srcs, int src_dt, int64_t R, int64_t C, const at::Tensor& sumsq_t, double eps,
                 at::Tensor same, int64_t ld_same, at::Tensor trans, int64_t ld_trans, uint64_t seed) {
@@ -357,6 +384,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.attr("MAX_WORLD") = hb::kMaxWorld;
   m.def("fused_chain", &fused_chain);
   m.def("sumsq", &sumsq);
+  m.def("segmented_reduce", &segmented_reduce);
   m.def("ns_prepare", &ns_prepare);
   m.def("ns_gemm", &ns_gemm);
   m.def("chunk_elems", &hb::chain_chunk_elems);

@@ -264,6 +264,59 @@ __global__ void __launch_bounds__(kThreads) sumsq_kernel(const TensorMeta* __res
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Segmented dot product and absolute maximum over the same chunk table: out[t] = sum(x_t * y_t) or max |x_t|.
+// x comes from TensorMeta::u, y from TensorMeta::g; `out` starts at zero.  One block per chunk; the block results
+// meet in out[t] through one atomic each (float add; for the maximum an unsigned integer max on the bit pattern,
+// which orders non-negative floats like their values and puts NaN above everything, so a NaN input gives NaN).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float nan_max(float acc, float a) { return (a > acc || a != a) ? a : acc; }
+
+template <int OP>
+__global__ void __launch_bounds__(kThreads) segmented_reduce_kernel(const TensorMeta* __restrict__ metas,
+                                                                   const int* __restrict__ chunk_prefix, int n_tensors,
+                                                                   int dt, float* __restrict__ out) {
+  int lo = 0, hi = n_tensors;
+  const int b = blockIdx.x;
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (chunk_prefix[mid] <= b) lo = mid; else hi = mid;
+  }
+  const TensorMeta M = metas[lo];
+  const int64_t base = (int64_t)(b - chunk_prefix[lo]) * kChunk;
+  float acc = 0.f;
+#pragma unroll 2
+  for (int it = 0; it < kChunk / (kThreads * 4); ++it) {
+    const int64_t i = base + ((int64_t)it * kThreads + threadIdx.x) * 4;
+    if (i >= M.numel) break;
+    const int nv = (int)min((int64_t)4, M.numel - i);
+    const F4 x = load4(M.u, nullptr, dt, i, nv, M.vec_ok != 0);
+    if (OP == kReduceDot) {
+      const F4 y = load4(M.g, nullptr, dt, i, nv, M.vec_ok != 0);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc += x.v[k] * y.v[k];
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc = nan_max(acc, fabsf(x.v[k]));  // lanes past the end read as zero
+    }
+  }
+  __shared__ float warp_res[kThreads / 32];
+  for (int o = 16; o > 0; o >>= 1) {
+    const float other = __shfl_down_sync(0xFFFFFFFFu, acc, o);
+    acc = OP == kReduceDot ? acc + other : nan_max(acc, other);
+  }
+  if ((threadIdx.x & 31) == 0) warp_res[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = warp_res[0];
+    for (int w = 1; w < kThreads / 32; ++w) tot = OP == kReduceDot ? tot + warp_res[w] : nan_max(tot, warp_res[w]);
+    if (OP == kReduceDot)
+      atomicAdd(out + lo, tot);
+    else
+      atomicMax(reinterpret_cast<unsigned int*>(out + lo), __float_as_uint(tot));
+  }
+}
+
 int chain_chunk_elems() { return kChunk; }
 
 cudaError_t launch_fused_chain(const TensorMeta* metas, const int* chunk_prefix, int total_chunks, const ChainParams& P,
@@ -280,6 +333,18 @@ cudaError_t launch_sumsq(const TensorMeta* metas, const int* chunk_prefix, int t
                          float* out, cudaStream_t stream) {
   if (total_chunks <= 0) return cudaSuccess;
   sumsq_kernel<<<total_chunks, kThreads, 0, stream>>>(metas, chunk_prefix, n_tensors, dt, out);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_segmented_reduce(const TensorMeta* metas, const int* chunk_prefix, int total_chunks, int n_tensors,
+                                    int dt, int op, float* out, cudaStream_t stream) {
+  if (total_chunks <= 0) return cudaSuccess;
+  if (op == kReduceDot)
+    segmented_reduce_kernel<kReduceDot><<<total_chunks, kThreads, 0, stream>>>(metas, chunk_prefix, n_tensors, dt, out);
+  else if (op == kReduceAbsMax)
+    segmented_reduce_kernel<kReduceAbsMax><<<total_chunks, kThreads, 0, stream>>>(metas, chunk_prefix, n_tensors, dt, out);
+  else
+    return cudaErrorInvalidValue;
   return cudaGetLastError();
 }
 

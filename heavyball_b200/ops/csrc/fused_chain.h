@@ -66,4 +66,10 @@ cudaError_t launch_fused_chain(const TensorMeta* metas, const int* chunk_prefix,
 cudaError_t launch_sumsq(const TensorMeta* metas, const int* chunk_prefix, int total_chunks, int n_tensors, int dt,
                          float* out, cudaStream_t stream);
 
+
+// out[t] = sum(u_t * g_t) (kReduceDot) or max |u_t| (kReduceAbsMax); `out` must be zero on entry.
+enum ReduceOp : int { kReduceDot = 0, kReduceAbsMax = 1 };
+cudaError_t launch_segmented_reduce(const TensorMeta* metas, const int* chunk_prefix, int total_chunks, int n_tensors,
+                                    int dt, int op, float* out, cudaStream_t stream);
+
 }  // namespace hb

@@ -469,3 +469,37 @@ def _tc_matmul(a: Tensor, b: Tensor, ta: bool = False, tb: bool = False):
 def _mm(a: Tensor, b: Tensor, ta: bool = False, tb: bool = False) -> Tensor:
     out = _tc_matmul(a, b, ta, tb)
     return out if out is not None else (a.mT if ta else a) @ (b.mT if tb else b)
+
+
+# ---------------------------------------------------------------------------------------- segmented reductions
+
+
+def _reducible(ts) -> bool:
+    first = ts[0]
+    if not (first.is_cuda and first.dtype in (torch.float32, torch.bfloat16, torch.float16)):
+        return False
+    from .. import ops
+
+    return ops.available() and all(t.is_cuda and t.dtype == first.dtype and t.is_contiguous() and t.numel() > 0 for t in ts)
+
+
+def _segmented_dot(xs, ys):
+    """``[sum(x * y) for x, y in zip(xs, ys)]`` as one fp32 tensor from one kernel launch over all pairs, or ``None``
+    when the kernel does not apply (CPU, mixed dtypes, non-contiguous tensors).  Block results are combined with
+    floating-point atomics, so the last bits can differ between runs."""
+    if not xs or len(xs) != len(ys) or not _reducible(list(xs) + list(ys)) or any(x.shape != y.shape for x, y in zip(xs, ys)):
+        return None
+    from .. import ops
+
+    return ops.dot(xs, ys)
+
+
+def _segmented_absmax_rows(ts):
+    """``[t.abs().amax(dim=all but the first) for t in ts]`` (one fp32 tensor per input) from one kernel launch over
+    every leading-index slice, or ``None`` when the kernel does not apply."""
+    if not ts or any(t.ndim < 2 for t in ts) or not _reducible(ts):
+        return None
+    from .. import ops
+
+    out = ops.absmax([row for t in ts for row in t.unbind(0)])
+    return list(out.split([t.shape[0] for t in ts]))

@@ -27,6 +27,7 @@ from .core import (
     _caution_impl,  # noqa: F401  (re-exported for monkeypatch parity)
     _decay_factor,
     _lerp,
+    _segmented_dot,
     as_float,
     as_int,
     beta_debias,
@@ -384,9 +385,11 @@ def sign_(grad, graft: bool = True):
 def orthogonalize_grad_to_param(weight, grad, eps, graft=True):
     """OrthoGrad: remove the component of the gradient along the weight vector."""
     weight, grad = list_guard(weight, grad)
-    for w, g in zip(weight, grad):
+    dots = _segmented_dot(list(weight) + list(weight), list(grad) + list(weight)) if weight else None  # w.g then w.w
+    for i, (w, g) in enumerate(zip(weight, grad)):
         w32, g32 = promote(w), promote(g)
-        out = g32 - ((w32 * g32).sum() / ((w32 * w32).sum() + eps)) * w32
+        wg, ww = ((w32 * g32).sum(), (w32 * w32).sum()) if dots is None else (dots[i], dots[len(weight) + i])
+        out = g32 - (wg / (ww + eps)) * w32
         copy_stochastic_(g, _compilable_grafting(g32, out) if graft else out)
     return grad
 

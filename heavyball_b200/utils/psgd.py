@@ -39,7 +39,7 @@ from .core import (
     warn_once,
 )
 from . import core as _core
-from .core import _mm, _tc_matmul
+from .core import _mm, _segmented_absmax_rows, _tc_matmul
 from .orthogonal import inplace_orthogonal_
 from .soap import compiled_einsum, einsum_base
 
@@ -425,7 +425,10 @@ def _kron_apply(g: Tensor, factors, twice: bool) -> Tensor:
 
 def psgd_balance_Q(Q):
     """Rescales factors (per slot) to a common max-abs, leaving their Kronecker product unchanged."""
-    logs = [promote(q.abs().amax(dim=tuple(range(1, q.ndim)))).log() for q in Q]
+    peaks = _segmented_absmax_rows(Q)  # one launch over every slot of every factor on sm_100a
+    if peaks is None:
+        peaks = [promote(q.abs().amax(dim=tuple(range(1, q.ndim)))) for q in Q]
+    logs = [pk.log() for pk in peaks]
     mean = sum(logs) / len(Q)
     for q, lg in zip(Q, logs):
         q *= (mean - lg).exp().view(-1, *([1] * (q.ndim - 1)))

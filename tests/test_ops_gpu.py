@@ -244,3 +244,51 @@ def test_peer_wait_gives_up_after_its_budget_and_reports_the_missing_rank():
     ext.peer_wait(flags, 0, 2, 1, 0.2, status)
     assert status.item() == 0
     assert torch.ones(4, device="cuda").sum().item() == 4.0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_segmented_dot_and_absmax_match_fp32_definitions(dtype):
+    torch.manual_seed(0)
+    sizes = [(1,), (7,), (1024, 1024), (33, 65), (70001,), (3, 5, 7)]
+    xs = [torch.randn(*s, device="cuda").to(dtype) for s in sizes]
+    ys = [torch.randn(*s, device="cuda").to(dtype) for s in sizes]
+    # starts that are not 16-byte aligned: the scalar load path
+    xs[3] = torch.randn(33 * 65 + 1, device="cuda").to(dtype)[1:].view(33, 65)
+    ys[3] = torch.randn(33 * 65 + 1, device="cuda").to(dtype)[1:].view(33, 65)
+    dots = ops.dot(xs, ys)
+    peaks = ops.absmax(xs)
+    ops.check_status()
+    assert dots.dtype == torch.float32 and dots.shape == (len(xs),)
+    for i, (x, y) in enumerate(zip(xs, ys)):
+        ref = (x.double() * y.double()).sum()
+        scale = (x.double() * y.double()).abs().sum()
+        assert abs(dots[i].item() - ref.item()) <= 1e-5 * scale.item() + 1e-12
+        assert peaks[i].item() == x.float().abs().max().item()  # a maximum is exact
+    bad = [x.clone() for x in xs]
+    bad[2][5, 7] = float("nan")
+    out = ops.absmax(bad)
+    assert torch.isnan(out[2]) and not torch.isnan(out[[0, 1, 3, 4, 5]]).any()
+
+
+def test_orthograd_and_kron_balance_use_the_segmented_reductions():
+    """Both call sites against their plain PyTorch definitions (the path they take on CPU)."""
+    from heavyball_b200.utils import first_order, psgd
+
+    torch.manual_seed(0)
+    ws = [torch.randn(64, 32, device="cuda"), torch.randn(1000, device="cuda")]
+    gs = [torch.randn_like(w) for w in ws]
+    got = [g.clone() for g in gs]
+    before = ops.launch_counter.count
+    first_order.orthogonalize_grad_to_param(ws, got, 1e-30, graft=False)
+    assert ops.launch_counter.count > before
+    for w, g, o in zip(ws, gs, got):
+        ref = g - ((w * g).sum() / ((w * w).sum() + 1e-30)) * w
+        assert torch.allclose(o, ref, atol=1e-5, rtol=1e-5)
+        assert abs((o * w).sum().item()) < 2e-2  # orthogonal to the weight
+
+    qs = [torch.randn(4, 48, 48, device="cuda").triu() * 3.0, torch.randn(4, 16, device="cuda") * 0.1]
+    ref = [q.clone().cpu() for q in qs]
+    psgd.psgd_balance_Q(qs)
+    psgd.psgd_balance_Q(ref)
+    for q, r in zip(qs, ref):
+        assert torch.allclose(q.cpu(), r, atol=1e-6, rtol=1e-5)

@@ -288,6 +288,26 @@ at::Tensor colsum_bf16(const at::Tensor& x) {
   return out;
 }
 
+// Concatenated fp32 column sums of up to four contiguous bf16 matrices of one shape: out[i * cols + c].
+at::Tensor colsum_bf16_batch(const std::vector<at::Tensor>& xs) {
+  TORCH_CHECK(!xs.empty() && xs.size() <= (size_t)hb::kColsumMaxBatch, "colsum_bf16_batch: one to four matrices");
+  const void* ptrs[hb::kColsumMaxBatch];
+  for (size_t i = 0; i < xs.size(); ++i) {
+    const at::Tensor& x = xs[i];
+    TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.size(1) % 8 == 0 &&
+                    aligned16(x.data_ptr()) && x.sizes() == xs[0].sizes() && x.device() == xs[0].device(),
+                "colsum_bf16_batch: contiguous bf16 [rows, cols] of one shape, cols % 8 == 0");
+    ptrs[i] = x.data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(xs[0].device());
+  const int64_t n = (int64_t)xs.size(), cols = xs[0].size(1);
+  at::Tensor out = at::empty({n * cols}, xs[0].options().dtype(at::kFloat));
+  at::Tensor partial = at::empty({n, hb::colsum_splits(), cols}, out.options());
+  check(hb::launch_colsum_bf16_batch(ptrs, (int)n, xs[0].size(0), (int)cols, partial.data_ptr<float>(), out.data_ptr<float>(),
+                                     at::cuda::getCurrentCUDAStream()), "colsum batch launch");
+  return out;
+}
+
 // y = gelu_tanh(u) for a contiguous bf16 tensor whose element count is a multiple of 8.
 at::Tensor gelu_fwd(const at::Tensor& u) {
   TORCH_CHECK(u.is_cuda() && u.scalar_type() == at::kBFloat16 && u.is_contiguous() && u.numel() % 8 == 0 &&
@@ -372,6 +392,7 @@ std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tf32x3_matmul", &tf32x3_matmul);
   m.def("colsum_bf16", &colsum_bf16);
+  m.def("colsum_bf16_batch", &colsum_bf16_batch);
   m.def("gelu_fwd", &gelu_fwd);
   m.def("gelu_bwd", &gelu_bwd);
   m.def("tall_t_mul", &tall_t_mul);

@@ -6,6 +6,10 @@
 // are 8 vector lanes x 32 row lanes; each thread adds up 8 columns over every 32nd row of the strip with 16-byte
 // loads, the 32 row lanes are combined through shared memory, and the strip's partial sums go to partial[split][c].
 // Stage 2 adds the kSplits partials (deterministic: no atomics).
+//
+// Up to kColsumMaxBatch matrices of one shape go through one pair of launches (blockIdx.z picks the matrix) and
+// land side by side in `out`: the three bias gradients of a packed q / k / v projection are one call, already
+// concatenated.  At 25 MB per matrix a launch is about half fixed cost (ramp-up, the shared-memory combine, tail).
 #include "colsum.h"
 
 #include <cuda_bf16.h>
@@ -15,8 +19,17 @@ namespace {
 
 constexpr int kSplits = 32;
 
-__global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16* __restrict__ x, long long rows, int cols,
-                                                            float* __restrict__ partial) {
+static_assert(kColsumMaxBatch == 4, "the pointer select below lists four entries");
+struct ColsumPtrs {
+  const __nv_bfloat16* x[kColsumMaxBatch];
+};
+
+__global__ void __launch_bounds__(256) colsum_partial_kernel(const ColsumPtrs ptrs, long long rows, int cols,
+                                                            float* __restrict__ partial_all) {
+  // selects instead of a dynamic index: the parameter struct stays in constant memory
+  const __nv_bfloat16* __restrict__ x =
+      blockIdx.z == 0 ? ptrs.x[0] : (blockIdx.z == 1 ? ptrs.x[1] : (blockIdx.z == 2 ? ptrs.x[2] : ptrs.x[3]));
+  float* __restrict__ partial = partial_all + (long long)blockIdx.z * kSplits * cols;
   const int vec = threadIdx.x & 7, lane_r = threadIdx.x >> 3;
   const int c0 = blockIdx.x * 64 + vec * 8;
   const long long per = (rows + kSplits - 1) / kSplits;
@@ -47,26 +60,35 @@ __global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16
   }
 }
 
-__global__ void colsum_final_kernel(const float* __restrict__ partial, int cols, float* __restrict__ out) {
+__global__ void colsum_final_kernel(const float* __restrict__ partial_all, int cols, float* __restrict__ out) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= cols) return;
+  const float* __restrict__ partial = partial_all + (long long)blockIdx.y * kSplits * cols;
   float s = 0.f;
 #pragma unroll
   for (int j = 0; j < kSplits; ++j) s += partial[(long long)j * cols + c];
-  out[c] = s;
+  out[(long long)blockIdx.y * cols + c] = s;
 }
 
 }  // namespace
 
 int colsum_splits() { return kSplits; }
 
-cudaError_t launch_colsum_bf16(const void* x, long long rows, int cols, float* partial, float* out, cudaStream_t stream) {
-  dim3 grid((cols + 63) / 64, kSplits);
-  colsum_partial_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), rows, cols, partial);
+cudaError_t launch_colsum_bf16_batch(const void* const* xs, int n, long long rows, int cols, float* partial, float* out,
+                                     cudaStream_t stream) {
+  if (n < 1 || n > kColsumMaxBatch) return cudaErrorInvalidValue;
+  ColsumPtrs ptrs;
+  for (int i = 0; i < kColsumMaxBatch; ++i) ptrs.x[i] = static_cast<const __nv_bfloat16*>(xs[i < n ? i : 0]);
+  dim3 grid((cols + 63) / 64, kSplits, n);
+  colsum_partial_kernel<<<grid, 256, 0, stream>>>(ptrs, rows, cols, partial);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  colsum_final_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(partial, cols, out);
+  colsum_final_kernel<<<dim3((cols + 255) / 256, n), 256, 0, stream>>>(partial, cols, out);
   return cudaGetLastError();
+}
+
+cudaError_t launch_colsum_bf16(const void* x, long long rows, int cols, float* partial, float* out, cudaStream_t stream) {
+  return launch_colsum_bf16_batch(&x, 1, rows, cols, partial, out, stream);
 }
 
 }  // namespace hb

@@ -114,6 +114,17 @@ def test_column_sum_kernel_matches_fp32_sum(rows, cols):
     assert torch.allclose(got.double(), ref, atol=1e-3 * rows**0.5, rtol=1e-5)
 
 
+@pytest.mark.parametrize("n", [1, 3, 4])
+def test_batched_column_sums_match_fp32_sum(n):
+    torch.manual_seed(0)
+    xs = [torch.randn(1000, 264, device="cuda").to(torch.bfloat16) for _ in range(n)]
+    out = ops.load().colsum_bf16_batch(xs)
+    ops.check_status()
+    assert out.shape == (n * 264,) and out.dtype == torch.float32
+    ref = torch.cat([x.float().sum(0) for x in xs])
+    assert torch.allclose(out, ref, atol=2e-3, rtol=1e-5)
+
+
 def test_linear_under_autocast_matches_framework_linear():
     from heavyball_b200.ops.nn import linear
 

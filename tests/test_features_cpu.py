@@ -146,3 +146,27 @@ def test_per_group_options_override_defaults():
     assert torch.equal(a.detach(), a0) and not torch.equal(b.detach(), b0)
     ecc_owners = [p for p, per in opt.state.items() if any(k.endswith("::ecc") for v in per.values() if isinstance(v, dict) for k in v)]
     assert len(ecc_owners) == 1 and ecc_owners[0] is b
+
+
+def test_segmented_reduction_call_sites_fall_back_on_cpu():
+    """OrthoGrad's projection and the Kron factor balance take their PyTorch definitions where the segmented
+    reduction kernels do not apply."""
+    import torch
+
+    from heavyball_b200.utils import core, first_order, psgd
+
+    torch.manual_seed(0)
+    assert core._segmented_dot([torch.randn(3)], [torch.randn(3)]) is None
+    assert core._segmented_absmax_rows([torch.randn(3, 3)]) is None
+    w, g = [torch.randn(8, 4)], [torch.randn(8, 4)]
+    out = [g[0].clone()]
+    first_order.orthogonalize_grad_to_param(w, out, 1e-30, graft=False)
+    ref = g[0] - ((w[0] * g[0]).sum() / ((w[0] * w[0]).sum() + 1e-30)) * w[0]
+    assert torch.allclose(out[0], ref, atol=1e-6)
+    assert abs((out[0] * w[0]).sum().item()) < 1e-4
+
+    q = [torch.randn(2, 5, 5) * 4.0, torch.randn(2, 5) * 0.1]
+    before = [torch.einsum("bij,bk->bijk", q[0], q[1]).clone()]
+    psgd.psgd_balance_Q(q)
+    assert torch.allclose(q[0].abs().amax((1, 2)), q[1].abs().amax(1), rtol=1e-5)  # common max-abs per slot
+    assert torch.allclose(torch.einsum("bij,bk->bijk", q[0], q[1]), before[0], rtol=1e-4, atol=1e-6)  # product unchanged

@@ -1558,6 +1558,10 @@ class ChainOpt(utils.StatefulOptimizer):
         )
         base = dict(self.global_defaults)
         base.update({k: v for k, v in defaults.items() if v is not use_default})
+        self._local_shards = _fsdp.LocalShards()
+        params = self._local_shards.localize(params)  # fully_shard (DTensor) parameters -> plain local-row proxies
+        if self._local_shards:
+            self._orig_shapes = {**(self._orig_shapes or {}), **self._local_shards.infos}
         super().__init__(params, base)
         self.fns = fns
         self._lowered = None
@@ -1618,9 +1622,23 @@ class ChainOpt(utils.StatefulOptimizer):
                     ecc.init_correction(st["param::ecc"], wide_views[i], pv.data)
 
     def add_param_group(self, param_group):
+        shards = getattr(self, "_local_shards", None)
+        if shards is not None and any(_is_dtensor(p) for p in _as_list(param_group.get("params", ()))):
+            param_group = shards.localize([param_group])[0]
+            self._orig_shapes = {**(self._orig_shapes or {}), **shards.infos}
         super().add_param_group(param_group)
         if hasattr(self, "mapping"):
             self._init_param_ecc_group(self.param_groups[-1])
+
+    def zero_grad(self, set_to_none: bool = True):
+        super().zero_grad(set_to_none)
+        if getattr(self, "_local_shards", None):
+            self._local_shards.clear_grads()
+
+    def step(self, closure=None):
+        if self._local_shards:
+            self._local_shards.refresh()
+        return super().step(closure)
 
     @staticmethod
     def _restore_ecc_dtypes(optimizer, *args):
@@ -1758,6 +1776,16 @@ class ChainOpt(utils.StatefulOptimizer):
             if lowering.try_run(self, state, group, list(g), list(p)):
                 return
         self._run_chain(state, group, list(g), list(p), caution)
+
+
+def _as_list(ps):
+    return [ps] if isinstance(ps, Tensor) else list(ps)
+
+
+def _is_dtensor(p):
+    from .parallel import fsdp as _fsdp
+
+    return _fsdp.is_dtensor(p)
 
 
 str_or_fn = Union[str, callable, None, Literal[use_default]]

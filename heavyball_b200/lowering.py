@@ -108,11 +108,24 @@ def _eligible(t: torch.Tensor) -> bool:
     return t.is_cuda and t.is_contiguous() and t.dtype in (torch.float32, torch.bfloat16, torch.float16)
 
 
+def _group_index(opt, group) -> int:
+    for i, g in enumerate(opt.param_groups):
+        if g is group:
+            return i
+    return 0
+
+
 def _seed(opt, group, launch: int) -> int:
+    """Philox seed of one launch.  Built only from values that are equal on every rank and in every run that
+    starts from the same ``torch.manual_seed``: the generator's seed at the optimizer's first step, the position of
+    the group in ``param_groups``, the step count and the launch number within the step.  Replicated execution
+    (every rank updating the same elements) therefore draws the same rounding noise everywhere."""
     base = getattr(opt, "_rng_base", None)
     if base is None:
         base = opt._rng_base = torch.initial_seed() & 0xFFFFFFFFFFFF
-    return (base * 0x9E3779B1 + group["step"] * 1315423911 + launch * 2654435761 + id(group) % 8191) & 0x7FFFFFFFFFFFFFFF
+    return (
+        base * 0x9E3779B1 + group["step"] * 1315423911 + launch * 2654435761 + _group_index(opt, group) * 40503
+    ) & 0x7FFFFFFFFFFFFFFF
 
 
 def _slots(tr, states, names, ecc: bool):
@@ -229,6 +242,9 @@ def try_run(opt, states, group, grads, params) -> bool:
         by_id = {id(p): i for i, p in enumerate(params)}
         group_pos = {id(p): j for j, p in enumerate(group["params"])}
         pos_to_local = {group_pos[pid]: i for pid, i in by_id.items() if pid in group_pos}
+        missing = [j for j, _ in plan["sel"] if j not in pos_to_local]
+        if missing and all(group["params"][j].grad is not None for j in missing):
+            raise RuntimeError("peer data parallelism: the step's parameters do not match the partition plan of their group")
         sel = [(pos_to_local[j], seg) for j, seg in plan["sel"] if j in pos_to_local]
         args = peer.peer_args()
         peer_in = {"g_delta": args["g_delta"], "g_scale": args["g_scale"]}
@@ -237,6 +253,9 @@ def try_run(opt, states, group, grads, params) -> bool:
         sel = [(i, None) for i in range(len(params))]
     pick = lambda xs: [_cut(xs[i], seg) for i, seg in sel] if len(xs) else []  # noqa: E731
     params_v, grads_v = pick(params), pick(grads)
+    if plan is not None:  # the kernels add cross-GPU offsets to these addresses: never launch on anything but slab views
+        for (i, seg), pv, gv in zip(sel, params_v, grads_v):
+            peer.validate(params[i], seg, pv, gv)
     sub_states = [states[i] for i, _ in sel]
     s0, s0e, s1, s1e, s2, s2e = (
         [_cut(t, seg) for t, (_, seg) in zip(lst, sel)] for lst in _slots(prog.rule, sub_states, names, bool(ecc_mode))

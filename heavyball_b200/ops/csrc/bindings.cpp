@@ -75,6 +75,39 @@ void fused_chain(const TList& p, const TList& pe, const TList& g, const TList& u
   if (n == 0) return;
   const at::Tensor& ref = !g.empty() ? *g[0] : (!u.empty() ? *u[0] : *p[0]);
   c10::cuda::CUDAGuard guard(ref.device());
+  {  // the kernel trusts the table: every buffer must be a contiguous CUDA tensor of the element count and storage
+     // kind its slot is declared with, on the device of the launch
+    // storage kinds as in common.cuh: 0 fp32, 1 bf16, 2 fp16, 3 bf16+8, 4 bf16+16, 5 fp16+8, 6 fp16+16, 7 none
+    auto dt_of = [&](const char* k) { return cfg.contains(k) ? cfg[k].cast<int>() : 0; };
+    auto primary_bytes = [](int dt) { return dt == 0 ? 4 : (dt == 7 ? 0 : 2); };
+    auto residual_bytes = [](int dt) { return (dt == 3 || dt == 5) ? 1 : ((dt == 4 || dt == 6) ? 2 : 0); };
+    struct Slot { const TList* list; const char* name; int dt; bool residual; };
+    const int dp = dt_of("dt_p"), dg = dt_of("dt_g"), du = dt_of("dt_u"), ds = dt_of("dt_s");
+    const Slot slots[] = {{&p, "p", dp, false}, {&pe, "pe", dp, true}, {&g, "g", dg, false}, {&u, "u", du, false},
+                          {&s0, "s0", ds, false}, {&s0e, "s0e", ds, true}, {&s1, "s1", ds, false}, {&s1e, "s1e", ds, true},
+                          {&s2, "s2", ds, false}, {&s2e, "s2e", ds, true}, {&mars, "mars", ds, false}, {&marse, "marse", ds, true}};
+    for (const Slot& sl : slots) {
+      if (sl.list->empty()) continue;
+      TORCH_CHECK(sl.list->size() == n, "fused_chain: list '", sl.name, "' has ", sl.list->size(), " entries, expected ", n);
+      const int want = sl.residual ? residual_bytes(sl.dt) : primary_bytes(sl.dt);
+      for (size_t i = 0; i < n; ++i) {
+        const OptT& t = (*sl.list)[i];
+        TORCH_CHECK(t.has_value() && t->defined(), "fused_chain: '", sl.name, "'[", i, "] is missing");
+        TORCH_CHECK(t->is_cuda() && t->device() == ref.device() && t->is_contiguous(), "fused_chain: '", sl.name, "'[", i,
+                    "] must be a contiguous CUDA tensor on the launch device");
+        TORCH_CHECK(want != 0 && (int)t->element_size() == want, "fused_chain: '", sl.name, "'[", i, "] has ", t->element_size(),
+                    "-byte elements, its storage kind needs ", want);
+      }
+    }
+    for (const at::Tensor* aux : {scale.has_value() ? &*scale : nullptr, masked.has_value() ? &*masked : nullptr}) {
+      if (aux == nullptr) continue;
+      TORCH_CHECK(aux->is_cuda() && aux->is_contiguous() && (size_t)aux->numel() >= n && aux->element_size() == 4,
+                  "fused_chain: per-tensor scalars need one 4-byte entry per tensor");
+    }
+    if (cfg.contains("g_delta") || cfg.contains("p_delta"))
+      TORCH_CHECK(pe.empty() && s0e.empty() && s1e.empty() && s2e.empty() && marse.empty(),
+                  "fused_chain: peer sources / destinations cannot be combined with ECC residual buffers");
+  }
   std::vector<hb::TensorMeta> metas(n);
   for (size_t i = 0; i < n; ++i) {
     hb::TensorMeta& m = metas[i];
@@ -85,6 +118,8 @@ void fused_chain(const TList& p, const TList& pe, const TList& g, const TList& u
     m.masked = masked.has_value() ? masked->data_ptr<int>() + i : nullptr;
     const at::Tensor& any = !g.empty() && g[i].has_value() ? *g[i] : (!u.empty() && u[i].has_value() ? *u[i] : *p[i]);
     m.numel = any.numel();
+    for (const TList* l : {&p, &pe, &g, &u, &s0, &s0e, &s1, &s1e, &s2, &s2e, &mars, &marse})
+      TORCH_CHECK(l->empty() || (*l)[i]->numel() == m.numel, "fused_chain: buffers of tensor ", i, " differ in element count");
     bool ok = true;
     for (void* q : {m.p, m.pe, m.g, m.u, m.s0, m.s0e, m.s1, m.s1e, m.s2, m.s2e, m.mars, m.marse}) ok = ok && aligned16(q);
     m.vec_ok = ok ? 1 : 0;

@@ -4,10 +4,9 @@
 // this library's kernels where the caller owns all memory.
 //
 // Who needs it: code that runs the optimizer from a place where calling cudaMalloc (or anything that
-// may call it, such as a framework's caching allocator) is not possible or not allowed - a step
-// replayed inside a captured region, a real-time training loop with a fixed memory budget, a host
-// process that has handed the whole device to another allocator, or a plain C / ctypes client with
-// no tensor library at all.  The regular path (`heavyball_b200.ops.fused_chain`) takes its scratch
+// may call it, such as a framework's caching allocator) is not possible or not allowed - a real-time
+// training loop with a fixed memory budget, a host process that has handed the whole device to
+// another allocator, or a plain C / ctypes client with no tensor library at all.  The regular path (`heavyball_b200.ops.fused_chain`) takes its scratch
 // space - the parked masked update and the per-tensor mask counter that caution needs, plus the
 // tensor table - from the PyTorch allocator on every call; this variant keeps that scratch in a
 // fixed array inside the loaded library instead.

@@ -48,6 +48,25 @@ def _inner_optimizers(optimizer):
     return list(getattr(optimizer, "optimizers", None) or [optimizer])
 
 
+def check_slab_view(what: str, ptr: int, nbytes: int, dtype, slab_ptr: int, slab_bytes: int, slab_dtype,
+                    expected_offset_bytes: Optional[int] = None):  # fmt: skip
+    """Raises unless ``[ptr, ptr + nbytes)`` lies inside ``[slab_ptr, slab_ptr + slab_bytes)``, has the slab's dtype
+    and (when given) starts at the expected byte offset.  The peer kernels add cross-GPU byte offsets to these
+    addresses, so a tensor outside its slab would be read or written at an arbitrary address on another GPU."""
+    if dtype != slab_dtype:
+        raise RuntimeError(
+            f"peer data parallelism: {what} has dtype {dtype}, the symmetric slab holds {slab_dtype} "
+            "(was the gradient promoted or re-created outside the slab?)"
+        )
+    if ptr < slab_ptr or ptr + nbytes > slab_ptr + slab_bytes:
+        raise RuntimeError(
+            f"peer data parallelism: {what} does not live in the symmetric slab (it was re-allocated, e.g. by "
+            "`model.zero_grad(set_to_none=True)`, `.contiguous()` or a dtype cast); the step was not launched"
+        )
+    if expected_offset_bytes is not None and ptr - slab_ptr != expected_offset_bytes:
+        raise RuntimeError(f"peer data parallelism: {what} sits at byte {ptr - slab_ptr} of the slab, expected {expected_offset_bytes}")
+
+
 class PeerContext:
     """Owns the symmetric slabs, the work partition and the step barriers."""
 
@@ -141,6 +160,21 @@ class PeerContext:
             off = self.offsets[id(p)]
             p.grad = self.G[off : off + p.numel()].view(p.shape)
 
+    def _check_grads_in_slab(self):
+        """Backward must have accumulated into the slab views.  A gradient that was set to ``None`` and re-created by
+        autograd lives elsewhere; publishing the (zero) slab for it would silently drop that gradient."""
+        lo, es = self.G.data_ptr(), self.G.element_size()
+        for p in self.params:
+            g = p.grad
+            if g is None:
+                continue  # parameter unused in this step: its slab range is zero
+            if g.dtype != self.dtype or g.data_ptr() != lo + self.offsets[id(p)] * es:
+                raise RuntimeError(
+                    "peer data parallelism: a parameter's .grad is no longer the symmetric-slab view (it was set to "
+                    "None and re-created, cast or replaced).  Use `optimizer.zero_grad()` / `model.zero_grad()` of the "
+                    "wrapped objects, which keep the views, and do not replace `.grad`."
+                )
+
     @staticmethod
     def _coalesce(ranges):
         out = []
@@ -194,6 +228,7 @@ class PeerContext:
         """After backward: publish "my gradients are complete" and wait for every peer's."""
         self.epoch += 1
         self.stale_state = True
+        self._check_grads_in_slab()
         self._barrier(0)
         for off, n in self.fallback_ranges:
             dist.all_reduce(self.G[off : off + n], op=dist.ReduceOp.AVG, group=self.group)
@@ -257,6 +292,20 @@ class PeerContext:
     def plan_for(self, group) -> Optional[dict]:
         return self.plans.get(id(group))
 
+    def validate(self, param, seg, p_view, g_view):
+        """Checks, on the host and before any launch, that the slices handed to a peer kernel are the slab views
+        this context created (same dtype, inside the slab, at the parameter's slab offset plus the slice start)."""
+        off = self.offsets.get(id(param))
+        if off is None:
+            raise RuntimeError("peer data parallelism: parameter is not part of the wrapped model")
+        es = self.P.element_size()
+        start = 0 if seg is None else seg[0]
+        for what, view, slab in (("parameter", p_view, self.P), ("gradient", g_view, self.G)):
+            check_slab_view(
+                what, view.data_ptr(), view.numel() * view.element_size(), view.dtype, slab.data_ptr(),
+                slab.numel() * es, slab.dtype, (off + start) * es,
+            )  # fmt: skip
+
     def peer_args(self):
         return {"g_delta": self.g_delta, "g_scale": 1.0 / self.world, "p_delta": self.p_delta}
 
@@ -294,6 +343,7 @@ def wrap(model: torch.nn.Module, optimizer=None, mode: str = "peer", **kwargs):
 
         optimizer.step = step
         optimizer.zero_grad = lambda set_to_none=True: None  # the slab is cleared by end_step
+        model.zero_grad = lambda set_to_none=True: None  # likewise: dropping .grad would detach it from the slab
         real_state_dict = optimizer.state_dict
 
         def state_dict(*a, **kw):

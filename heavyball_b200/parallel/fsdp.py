@@ -67,6 +67,138 @@ def assign_owners(entries, shard_sizes, world_size):
     return owners
 
 
+# ---------------------------------------------------------------------------------------- FSDP2 (DTensor parameters)
+
+
+def _dtensor_type():
+    try:
+        from torch.distributed.tensor import DTensor
+    except ImportError:  # pragma: no cover - older torch
+        return None
+    return DTensor
+
+
+def is_dtensor(p) -> bool:
+    cls = _dtensor_type()
+    return cls is not None and isinstance(p, cls)
+
+
+def _row_chunks(rows: int, ws: int) -> List[int]:
+    """Row counts of ``torch.chunk(t, ws, dim=0)``, which is how ``fully_shard`` cuts dim 0 (trailing ranks may hold
+    fewer rows or none)."""
+    per = -(-rows // ws) if rows else 0
+    out = []
+    for r in range(ws):
+        lo = min(rows, r * per)
+        out.append(min(rows, lo + per) - lo)
+    return out
+
+
+class LocalShards:
+    """Stand-ins for ``fully_shard`` (FSDP2) parameters inside an optimizer.
+
+    ``fully_shard`` turns every parameter into a ``DTensor`` sharded along dim 0 over a 1-D device mesh.  The chain
+    kernels work on plain tensors, so each such parameter is represented in ``param_groups`` by a plain
+    ``torch.nn.Parameter`` (the *proxy*) whose ``.data`` aliases the rank's local rows and whose ``.grad`` aliases the
+    local rows of the DTensor gradient.  Updates written through the proxy land in the model's storage.  The local
+    tensor object can be replaced by the sharding runtime (it re-pads its storage when it initialises lazily), so the
+    aliases are renewed at the start of every step.
+
+    The global shape, the first local row and the row counts of all ranks follow from the placement, so owners of
+    shape-dependent work are assigned without any collective: greedily by estimated work, in construction order,
+    which is the same on every rank."""
+
+    def __init__(self):
+        self.pairs = []  # (proxy, dtensor parameter)
+        self.infos: Dict[int, ShapeInfo] = {}
+        self._loads = None
+
+    def __bool__(self):
+        return bool(self.pairs)
+
+    def proxy_for(self, p):
+        import torch.distributed.tensor as dt
+
+        mesh = p.device_mesh
+        if mesh.ndim != 1 or len(p.placements) != 1:
+            raise NotImplementedError("sharded parameters are supported on a 1-D device mesh (plain fully_shard)")
+        placement = p.placements[0]
+        ws = mesh.size()
+        if ws != _world():
+            raise NotImplementedError("the sharding mesh must span the default process group")
+        local = p._local_tensor
+        proxy = torch.nn.Parameter(local.detach(), requires_grad=p.requires_grad)
+        shape = tuple(p.shape)
+        if isinstance(placement, dt.Shard):
+            if placement.dim != 0:
+                raise NotImplementedError("only dim-0 sharding (the fully_shard default) is supported")
+            inner = math.prod(shape[1:]) if len(shape) > 1 else 1
+            rows = _row_chunks(shape[0] if shape else 1, ws)
+            sizes = [r * inner for r in rows]
+            rank = mesh.get_local_rank()
+            offset = sum(sizes[:rank])
+            if self._loads is None:
+                self._loads = [0] * ws
+            holders = [r for r, n in enumerate(sizes) if n] or list(range(ws))
+            owner = min(holders, key=self._loads.__getitem__)
+            self._loads[owner] += work_estimate(shape, local.element_size())
+            info = ShapeInfo(shape, offset, math.prod(shape), owner=owner, param_idx=len(self.pairs), sizes=sizes)
+        else:  # replicated: every rank holds (and updates) the whole tensor
+            info = ShapeInfo(shape, 0, math.prod(shape), owner=None, param_idx=len(self.pairs), sizes=None)
+        self.infos[id(proxy)] = info
+        self.pairs.append((proxy, p))
+        return proxy
+
+    def localize(self, params):
+        """``params`` as given to an optimizer constructor (tensors or group dicts), with DTensors replaced by proxies."""
+        params = list(params)
+        if params and isinstance(params[0], dict):
+            out = []
+            for g in params:
+                g = dict(g)
+                ps = g["params"]
+                ps = [ps] if isinstance(ps, torch.Tensor) else list(ps)
+                g["params"] = [self.proxy_for(p) if is_dtensor(p) else p for p in ps]
+                out.append(g)
+            return out
+        return [self.proxy_for(p) if is_dtensor(p) else p for p in params]
+
+    def refresh(self):
+        """Re-aliases every proxy to the current local rows of its parameter and gradient (start of a step)."""
+        for proxy, p in self.pairs:
+            local = p._local_tensor
+            if proxy.data.data_ptr() != local.data_ptr() or proxy.data.shape != local.shape:
+                proxy.data = local.detach()
+            g = p.grad
+            if g is None or local.numel() == 0:
+                proxy.grad = None
+            else:
+                gl = g._local_tensor if is_dtensor(g) else g
+                proxy.grad = gl.detach()
+
+    def clear_grads(self):
+        for proxy, p in self.pairs:
+            proxy.grad = None
+            p.grad = None
+
+
+def shard(model, mesh=None, **kwargs):
+    """Applies ``fully_shard`` (FSDP2) to every member of every ``ModuleList`` of ``model`` and then to ``model``
+    itself: one communication group per transformer layer plus one for what is left (embeddings, final norm, head).
+    Build the optimizer afterwards, from ``model.parameters()``; the optimizers of this package accept the resulting
+    DTensor parameters directly."""
+    from torch.distributed.fsdp import fully_shard
+
+    if mesh is not None:
+        kwargs["mesh"] = mesh
+    for module in list(model.modules()):
+        if isinstance(module, torch.nn.ModuleList):
+            for child in module:
+                fully_shard(child, **kwargs)
+    fully_shard(model, **kwargs)
+    return model
+
+
 def _flat_param_lookup():
     try:
         from torch.distributed.fsdp._flat_param import FlatParameter

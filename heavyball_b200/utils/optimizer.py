@@ -166,7 +166,11 @@ class StatefulOptimizer(torch.optim.Optimizer):
             if k in self._REMOVED_STATS:
                 continue
             if k == "precond_schedule":
-                v = pickle_compat.loads(v)
+                try:
+                    v = pickle_compat.loads(v)
+                except Exception as err:  # noqa: BLE001 - a schedule that may not be loaded must not lose the checkpoint
+                    warn_once(f"checkpoint's precond_schedule was not loaded, keeping the optimizer's own: {err}")
+                    continue
             setattr(self, k, v)
 
     # ------------------------------------------------------------------ state addressing

@@ -54,6 +54,19 @@ def dumps(schedule) -> bytes:
     return buf.getvalue()
 
 
+# Extra globals a user has declared loadable: {"module.qualname": object}.  Empty by default.
+allowed_globals: dict = {}
+
+
+def allow_global(obj, module: str = None, name: str = None):
+    """Declares a user-defined schedule function loadable from checkpoints (by its module path and name, which is
+    how pickle refers to it).  Returns ``obj`` so it can be used as a decorator."""
+    module = obj.__module__ if module is None else module
+    name = obj.__qualname__ if name is None else name
+    allowed_globals[f"{module}.{name}"] = obj
+    return obj
+
+
 class _RestrictedUnpickler(pickle.Unpickler):
     def find_class(self, module, name):
         if module == "functools" and name == "partial":
@@ -62,7 +75,13 @@ class _RestrictedUnpickler(pickle.Unpickler):
             table = _exported()
             if name in table:
                 return table[name]
-        raise pickle.UnpicklingError(f"precond_schedule refers to disallowed global {module}.{name}")
+        hit = allowed_globals.get(f"{module}.{name}")
+        if hit is not None:
+            return hit
+        raise pickle.UnpicklingError(
+            f"precond_schedule refers to global {module}.{name}, which is not on the allow-list; register it with "
+            "heavyball_b200.utils.pickle_compat.allow_global(fn) before loading"
+        )
 
 
 def loads(data: bytes):

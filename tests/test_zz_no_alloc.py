@@ -1,7 +1,7 @@
 """The allocation-free cautious AdamW entry point against the regular (allocating) caution path.
 
 Some callers of the optimizer kernels cannot allocate device memory while stepping (fixed memory
-budgets, replayed regions, C clients without a tensor library); for them the library exports one C
+budgets, a device handed to another allocator, C clients without a tensor library); for them the library exports one C
 symbol whose scratch lives in a fixed in-library array.  This test calls that exported symbol through
 ctypes twice in a row - the second call reuses the array the first one dirtied - and checks parameters
 and both moments against ``ops.fused_chain``'s two-phase caution path on identical inputs.
@@ -41,8 +41,15 @@ def test_noalloc_matches_regular_path_twice(numel):
         b1 = 1 - (1 - 0.9) / (1 - 0.9**step)
         b2 = 1 - (1 - 0.99) / (1 - 0.99**step)
         pa, ma, va = state["a"]
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        reserved_before = torch.cuda.memory_reserved()
         noalloc.cautious_adamw_step(pa, g, ma, va, lr=hyper["lr"], beta1=b1, beta2=b2, eps=hyper["eps"],
                                     weight_decay=hyper["wd"])  # fmt: skip
+        torch.cuda.synchronize()
+        if step == 2:  # the first call on a device may load the kernels' module; from then on nothing may move
+            assert torch.cuda.mem_get_info()[0] == free_before, "the allocation-free step changed free device memory"
+        assert torch.cuda.memory_reserved() == reserved_before
         pb, mb, vb = state["b"]
         _regular_path(pb, g, mb, vb, lr=hyper["lr"], b1=b1, b2=b2, eps=hyper["eps"], wd=hyper["wd"])
         torch.cuda.synchronize()

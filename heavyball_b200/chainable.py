@@ -1770,11 +1770,10 @@ class ChainOpt(utils.StatefulOptimizer):
 
     def _chain(self, group, g, p, caution):
         state = [self.state_(pi) for pi in p]
-        if p[0].is_cuda:
-            from . import lowering
+        from . import lowering
 
-            if lowering.try_run(self, state, group, list(g), list(p)):
-                return
+        if (p[0].is_cuda or lowering.cpu_programs) and lowering.try_run(self, state, group, list(g), list(p)):
+            return
         self._run_chain(state, group, list(g), list(p), caution)
 
 

@@ -14,6 +14,14 @@ Programs
 ``orthogonal``    ``[mars] [palm] <momentum rule> orthogonalize_update``: momentum launch -> batched
                   Newton–Schulz per shape bucket (tcgen05 GEMM chain) -> parameter-update launch.
 
+``soap``          ``[mars] [palm] scale_by_soap | scale_by_soap_laprop``: gradients -> bucket-major fp32 buffer (one
+                  launch) -> per shape bucket the batched stage of ``matrix_stage.SoapBucket`` (projections with the
+                  Adam step fused into a GEMM epilogue, statistics with the lerp fused, cached split eigenbases) ->
+                  parameter-update launch.  Vectors (no eigenbasis) take one Adam launch.
+``psgd``          ``[mars] [palm] [<element-wise rule>] scale_by_psgd | update_by_psgd [trust_region_clip_]``: rule launch
+                  into the bucket-major buffer -> ``matrix_stage.PsgdBucket`` (cached ``Q^T Q`` applied with two
+                  products, fitting on preconditioner steps) -> update launch with the clip folded in.
+
 State is created by the PyTorch path on the first step of a parameter (``ZeroSlots`` hands out views
 of one slab per slot, so buffers of a group are contiguous); lowering engages once all state exists,
 and writes the same state keys, so checkpoints do not depend on which path ran.
@@ -21,13 +29,14 @@ and writes the same state keys, so checkpoints do not depend on which path ran.
 
 from __future__ import annotations
 
+import functools
 import os
 from typing import List, Optional
 
 import torch
 
 from . import chainable as C
-from . import ops, utils
+from . import matrix_stage, ops, utils
 
 enabled = os.environ.get("HB200_DISABLE_LOWERING") != "1"
 
@@ -51,12 +60,28 @@ _RULES = {
 }
 
 
-class _Program:
-    __slots__ = ("kind", "mars", "palm", "rule", "ortho", "workspace")
+_SOAP_INNER = {"scale_by_soap": "adam", "scale_by_soap_laprop": "laprop"}
+# name -> (writes the parameter itself, fits after applying)
+_PSGD_STAGES = {
+    "scale_by_psgd": (False, False), "update_by_psgd": (True, False),
+    "scale_by_delayed_psgd": (False, True), "update_by_delayed_psgd": (True, True),
+}  # fmt: skip
 
-    def __init__(self, kind, mars, palm, rule, ortho):
+
+class _Program:
+    __slots__ = ("kind", "mars", "palm", "rule", "ortho", "stage", "stage_kw", "u_op", "workspace")
+
+    def __init__(self, kind, mars, palm, rule, ortho=None, stage=None, stage_kw=None, u_op=0):
         self.kind, self.mars, self.palm, self.rule, self.ortho = kind, mars, palm, rule, ortho
+        self.stage, self.stage_kw, self.u_op = stage, stage_kw or {}, u_op
         self.workspace = {}
+
+
+def _unwrap(fn):
+    """``(transform, bound keyword arguments)`` of a chain entry that may be a ``functools.partial``."""
+    if isinstance(fn, functools.partial) and not fn.args:
+        return fn.func, dict(fn.keywords)
+    return fn, {}
 
 
 def _match(fns) -> Optional[_Program]:
@@ -66,9 +91,31 @@ def _match(fns) -> Optional[_Program]:
         mars = fns.pop(0)
     if fns and getattr(fns[0], "__name__", "") == "palm_beta2" and not isinstance(fns[0], C.FunctionTransform):
         palm = fns.pop(0)
-    if not fns or not all(isinstance(f, C.FunctionTransform) for f in fns):
+    if not fns:
         return None
+    u_op = 0
+    if getattr(fns[-1], "wrapped_fn", None) is utils.trust_region_clip_ and fns[-1].__name__.endswith("_to_2"):
+        fns.pop()
+        u_op = 1
+    pairs = [_unwrap(f) for f in fns]
+    if not pairs or not all(isinstance(f, C.FunctionTransform) for f, _ in pairs):
+        return None
+    last, last_kw = pairs[-1]
+    if last.fn_name in _PSGD_STAGES and len(pairs) <= 2:
+        rule = None
+        if len(pairs) == 2:
+            rule, rule_kw = pairs[0]
+            if rule.fn_name not in _RULES or rule_kw or rule.fn_name.startswith("update_by"):
+                return None
+        if last_kw.get("cached", False):
+            return None
+        return _Program("psgd", mars, palm, rule, stage=last, stage_kw=last_kw, u_op=u_op)
+    if u_op or any(kw for _, kw in pairs):
+        return None
+    fns = [f for f, _ in pairs]
     rule = fns[0]
+    if len(fns) == 1 and rule.fn_name in _SOAP_INNER:
+        return _Program("soap", mars, palm, None, stage=rule)
     if rule.fn_name not in _RULES:
         return None
     if len(fns) == 1:
@@ -92,7 +139,7 @@ def _mark_initialized(tr: C.FunctionTransform, st: dict):
 
 
 def _state_ready(tr: C.FunctionTransform, states: List[dict], ecc: bool) -> bool:
-    keys = list(tr._val_names.values())
+    keys = [k for layer in tr.layers if not isinstance(layer, C.AccumSlots) for k in layer.keys.values()]
     warm = [(layer.counter, len(layer.warmup_fns)) for layer in tr.layers if isinstance(layer, C.Warmup)]
     for st in states:
         for k in keys:
@@ -189,11 +236,21 @@ def _cut(t, seg):
     return t if seg is None else t.view(-1)[seg[0] : seg[1]]
 
 
+cpu_programs = False  # tests: run the staged programs with PyTorch products on CPU to check their logic
+
+
 def try_run(opt, states, group, grads, params) -> bool:
-    if not enabled or not ops.available():
+    if not enabled:
+        return False
+    on_gpu = params[0].is_cuda and ops.available()
+    if not on_gpu and not (cpu_programs and not params[0].is_cuda):
         return False
     prog = _program(opt)
     if prog is None:
+        return False
+    if prog.kind in ("soap", "psgd"):
+        return _run_precond(opt, prog, states, group, grads, params, on_gpu)
+    if not on_gpu:
         return False
     if not all(_eligible(p) for p in params):
         return False
@@ -377,3 +434,180 @@ def _bucket_out(prog: _Program, key, device) -> torch.Tensor:
     if hit is None:
         hit = prog.workspace[("ns", key)] = torch.empty(B, R, Cc, dtype=torch.float32, device=device)
     return hit
+
+
+# ======================================================================================== SOAP / PSGD programs
+
+
+def _bucket_layout(prog: _Program, params):
+    """Bucket-major fp32 buffers: for every distinct parameter shape one ``(B, *shape)`` input and one output tensor;
+    returns ``(buckets, u_views, out_views)`` with per-parameter views in parameter order.  Cached on the program."""
+    key = ("layout", tuple(tuple(p.shape) for p in params), params[0].device)
+    hit = prog.workspace.get(key)
+    if hit is not None:
+        return hit
+    by_shape = {}
+    for i, p in enumerate(params):
+        by_shape.setdefault(tuple(p.shape), []).append(i)
+    dev = params[0].device
+    buckets, u_views, out_views = [], [None] * len(params), [None] * len(params)
+    for shape, idx in by_shape.items():
+        U = torch.empty((len(idx), *shape), dtype=torch.float32, device=dev)
+        O = torch.empty_like(U)
+        for b, i in enumerate(idx):
+            u_views[i], out_views[i] = U[b], O[b]
+        buckets.append((shape, idx, U, O))
+    prog.workspace = {k: v for k, v in prog.workspace.items() if k[0] != "layout"}
+    hit = prog.workspace[key] = (buckets, u_views, out_views)
+    return hit
+
+
+def _stage_bucket(prog: _Program, group, shape, n: int, make):
+    key = ("bucket", _group_key(group), shape, n)
+    hit = prog.workspace.get(key)
+    if hit is None:
+        hit = prog.workspace[key] = make()
+    return hit
+
+
+def _group_key(group):
+    return id(group)
+
+
+def _precond_unsupported(opt, prog, group, params) -> bool:
+    """Options the staged programs do not cover (the PyTorch definitions handle them)."""
+    if group.get("storage_dtype", "float32") != "float32" or group.get("precond_grad_accum", False):
+        return True
+    if getattr(opt, "hessian_approx", False) or group.get("sqrt", False) or group.get("param_ecc"):
+        return True
+    if prog.kind == "soap" and group.get("ecc"):
+        return True
+    if prog.kind == "psgd" and (not group.get("momentum_into_precond_update", True) or group.get("q_dtype", "float32") != "float32"):
+        return True
+    if any(p.dtype != torch.float32 or not p.is_contiguous() for p in params):
+        return True
+    return False
+
+
+def _run_precond(opt, prog: _Program, states, group, grads, params, on_gpu: bool) -> bool:
+    if _precond_unsupported(opt, prog, group, params):
+        return False
+    if getattr(opt, "_peer", None) is not None and opt._peer.plan_for(group) is not None:
+        return False
+    stage = prog.stage
+    ecc_mode = group.get("ecc")
+    if not _state_ready(stage, states, False):
+        return False  # first step of a parameter: the PyTorch path initialises (and, for SOAP, skips the update)
+    for tr in (prog.rule, prog.mars):
+        if tr is not None and not _state_ready(tr, states, bool(ecc_mode)):
+            return False
+    keys = stage._val_names
+    if prog.kind == "soap":
+        if any(len(st[keys["Q"]]) > 2 or st[keys["exp_avg"]].ndim > 3 for st in states):
+            return False  # tensors of order > 2 after dimension merging
+    elif any(len(st[keys["Q"]]) > 2 for st in states):
+        return False
+    grads = [g if g.is_contiguous() else g.contiguous() for g in grads]
+    if on_gpu and any(g.dtype != grads[0].dtype or g.dtype not in (torch.float32, torch.bfloat16, torch.float16) for g in grads):
+        return False
+
+    if prog.palm is not None:
+        prog.palm(None, group, None, None, None)
+    buckets, u_views, out_views = _bucket_layout(prog, params)
+    step = group["step"]
+    caution = bool(group["caution"])
+
+    # ---- stage A: gradients -> [mars] -> [rule] -> bucket-major fp32 updates
+    if on_gpu:
+        kw = dict(dt_g=ops.dtype_code(grads[0]), dt_u=ops.F32, dt_p=ops.NONE, out_mode=ops.OUT_UPDATE, seed=_seed(opt, group, 0))
+        if prog.rule is not None:
+            algo, names = _RULES[prog.rule.fn_name]
+            key0 = prog.rule._val_names[next(n for n in names if n is not None)]
+            s0, s0e, s1, s1e, s2, s2e = _slots(prog.rule, states, names, bool(ecc_mode))
+            kw.update(algo=algo, n_state=len(names), dt_s=ops.dtype_code(states[0][key0], ecc_mode), s0=s0, s0e=s0e, s1=s1,
+                      s1e=s1e, s2=s2, s2e=s2e, **_rule_scalars(prog.rule.fn_name, group))  # fmt: skip
+        else:
+            kw.update(algo=ops.IDENTITY, n_state=0, dt_s=ops.dtype_code(None))
+        if prog.mars is not None:
+            mkey = prog.mars._val_names["mars_old_grad"]
+            gamma, beta1 = utils.get_beta1(group), group["mars_gamma"]  # argument order of the transform
+            if prog.rule is None:
+                kw["dt_s"] = ops.dtype_code(states[0][mkey], ecc_mode)
+            kw.update(mars=[st[mkey] for st in states], marse=[st[mkey + "::ecc"] for st in states] if ecc_mode else [],
+                      mars_a=-gamma * beta1 / (1 - beta1))  # fmt: skip
+        ops.fused_chain(g=grads, u=u_views, **kw)
+    else:
+        upd = [g.float().clone() for g in grads]
+        for tr in (prog.mars, prog.rule):
+            if tr is not None:
+                upd = tr(states, group, upd, grads, params)
+        for dst, src in zip(u_views, upd):
+            dst.copy_(src.view(dst.shape))
+
+    # ---- stage B: per shape bucket
+    if prog.kind == "soap":
+        b1 = utils.beta_debias(utils.get_beta1(group), step - 1)
+        b2 = utils.beta_debias(utils.get_beta2(group), step - 1)
+        stat_w = 1 - utils.beta_debias(group["shampoo_beta"], step)
+        vec = []  # members without any eigenbasis: plain Adam / LaProp on the update
+        for shape, idx, U, O in buckets:
+            members = [states[i] for i in idx]
+            if all(q is None for q in members[0][keys["Q"]]):
+                vec += idx
+                continue
+            U3, O3 = (U, O) if U.ndim == 3 else (U.unsqueeze(1), O.unsqueeze(1))
+            bucket = _stage_bucket(prog, group, shape, len(idx), lambda: matrix_stage.SoapBucket(keys, _SOAP_INNER[stage.fn_name]))
+            bucket.run(members, U3, O3, group, b1=b1, b2=b2, eps=group["eps"], stat_w=stat_w,
+                       refresh=bool(group["is_preconditioning"]))  # fmt: skip
+        if vec:
+            m = [states[i][keys["exp_avg"]] for i in vec]
+            v = [states[i][keys["exp_avg_sq"]] for i in vec]
+            if on_gpu:
+                algo = ops.ADAM if _SOAP_INNER[stage.fn_name] == "adam" else ops.LAPROP
+                ops.fused_chain(g=[u_views[i] for i in vec], u=[out_views[i] for i in vec], s0=m, s1=v, algo=algo, n_state=2,
+                                out_mode=ops.OUT_UPDATE, dt_g=ops.F32, dt_u=ops.F32, dt_s=ops.F32, dt_p=ops.NONE, b1=b1, b2=b2,
+                                eps=group["eps"], seed=_seed(opt, group, 1))  # fmt: skip
+            else:
+                fn = utils.adam_ if _SOAP_INNER[stage.fn_name] == "adam" else utils.laprop_
+                res = fn(m, v, [u_views[i].clone().view(mm.shape) for i, mm in zip(vec, m)], utils.get_beta1(group),
+                         utils.get_beta2(group), step - 1, group["eps"])  # fmt: skip
+                for i, r in zip(vec, res):
+                    out_views[i].copy_(r.view(out_views[i].shape))
+        fused_caution_ref = None
+    else:
+        fused, delayed = _PSGD_STAGES[stage.fn_name]
+        line = bool(group["store_triu_as_line"])
+        fit = bool(group["is_preconditioning"])
+        if fit:
+            group["is_cached"] = False
+        for shape, idx, U, O in buckets:
+            members = [states[i] for i in idx]
+            bucket = _stage_bucket(prog, group, shape, len(idx), lambda: matrix_stage.PsgdBucket(keys, line))
+            inner = [len(idx), *(d for d in shape if d != 1)]  # the transform sees size-1 dims squeezed away
+            bucket.run(members, U.view(inner), O.view(inner), group, fit=fit, delayed=delayed)
+        # the fused form masks against the incoming update, the unfused one against the gradient
+        fused_caution_ref = u_views if fused else None
+
+    # ---- stage C: [clip] -> [caution] -> weight decay -> parameter write
+    lr, wd = group["lr"], group["weight_decay"]
+    cwd = bool(group.get("cautious_weight_decay", False))
+    if on_gpu:
+        epilogue = dict(lr=lr, wd=wd, cautious_wd=int(cwd))
+        common = dict(algo=ops.IDENTITY, u_is_input=1, dt_u=ops.F32, dt_s=ops.NONE)
+        if caution:
+            ref = fused_caution_ref if fused_caution_ref is not None else grads
+            masked = torch.zeros(len(params), dtype=torch.int32, device=params[0].device)
+            ops.fused_chain(g=ref, u=out_views, masked=masked, count_caution=1, out_mode=ops.OUT_UPDATE, dt_g=ops.dtype_code(ref[0]),
+                            dt_p=ops.NONE, u_op=prog.u_op, seed=_seed(opt, group, 2), **common)  # fmt: skip
+            ops.fused_chain(p=params, u=out_views, masked=masked, caution_apply=1, out_mode=ops.OUT_PARAM, dt_g=ops.NONE,
+                            dt_p=ops.dtype_code(params[0]), seed=_seed(opt, group, 3), **common, **epilogue)  # fmt: skip
+        else:
+            ops.fused_chain(p=params, u=out_views, out_mode=ops.OUT_PARAM, dt_g=ops.NONE, dt_p=ops.dtype_code(params[0]),
+                            u_op=prog.u_op, seed=_seed(opt, group, 3), **common, **epilogue)  # fmt: skip
+    else:
+        final = [o.clone().view(p.shape) for o, p in zip(out_views, params)]
+        if prog.u_op:
+            utils.trust_region_clip_(final)
+        ref = [u.view(p.shape) for u, p in zip(fused_caution_ref, params)] if fused_caution_ref is not None else grads
+        utils.update_param_(params, final, lr, wd, caution=caution, cautious_decay=cwd, grad=ref)
+    return True

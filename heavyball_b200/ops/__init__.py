@@ -284,6 +284,36 @@ def matmul_supported(a: torch.Tensor, b: torch.Tensor) -> bool:
     )  # fmt: skip
 
 
+EPI_STORE, EPI_LERP, EPI_ADAM, EPI_LAPROP = range(4)  # mirror of hb::Tf32EpilogueMode
+SPLIT_NONE, SPLIT_ROWS, SPLIT_COLS = range(3)
+
+
+def tf32_split(x: torch.Tensor, same: bool = True, trans: bool = False):
+    """Split-tf32 operands of a contiguous fp32 ``[batch, R, C]`` tensor, one pass over ``x``.  Returns ``(same, trans)``:
+    ``same`` has the rows of ``x`` as operand rows (``K = C``), ``trans`` its columns (``K = R``); an orientation that
+    was not asked for is ``None``.  Either buffer can be the left or the right operand of :func:`tf32_gemm`, so matrices
+    that rarely change (eigenbases, preconditioner factors) are split once and kept."""
+    launch_counter.count += 1
+    s, t = load().tf32_split(x, same, trans)
+    return (s if same else None), (t if trans else None)
+
+
+def tf32_gemm(a2: torch.Tensor, b2: torch.Tensor, K: int, *, mode: int = EPI_STORE, alpha: float = 1.0, w: float = 0.0,
+              b1: float = 0.0, b2c: float = 0.0, eps: float = 0.0, out: Optional[torch.Tensor] = None,
+              split_out: int = SPLIT_NONE, m: Optional[torch.Tensor] = None, v: Optional[torch.Tensor] = None):  # fmt: skip
+    """``epilogue(A @ B^T)`` over split operands (``a2``: ``[batch, M, 2 kp(K)]``, ``b2``: ``[batch, N, 2 kp(K)]``) at
+    fp32-level accuracy on the tf32 tensor cores.
+
+    ``mode``: ``EPI_STORE`` writes ``alpha * acc``; ``EPI_LERP`` updates ``out <- out + (alpha * acc - out) * w`` in place;
+    ``EPI_ADAM`` / ``EPI_LAPROP`` advance the fp32 moments ``m``, ``v`` (``[batch, M, N]``, in place, coefficients ``b1``,
+    ``b2c`` already debiased) with ``alpha * acc`` as the gradient and pass the preconditioned value on.
+    ``out`` (fp32 ``[batch, M, N]``) receives the result; ``split_out`` additionally (or instead) returns it as a split
+    operand for the next product: ``SPLIT_ROWS`` with the result's rows as operand rows, ``SPLIT_COLS`` with its columns."""
+    launch_counter.count += 1
+    s = load().tf32_gemm(a2, b2, K, mode, alpha, w, b1, b2c, eps, out, split_out, m, v, _status(a2.device))
+    return s if split_out else None
+
+
 def matmul3(a: torch.Tensor, b: torch.Tensor, trans_a: bool = False, trans_b: bool = False, alpha: float = 1.0) -> torch.Tensor:
     """``alpha * op(a) @ op(b)`` for fp32 matrices (optionally batched, equal leading shapes) on the tf32 tensor
     cores with the 3-term split (measured error about 2^-18 of ``|a| @ |b|``; one tf32 pass gives 2^-11, fp32 SIMT 2^-21)."""

@@ -134,7 +134,7 @@ void fused_chain(const TList& p, const TList& pe, const TList& g, const TList& u
   P.dt_p = geti("dt_p"); P.dt_g = geti("dt_g"); P.dt_u = geti("dt_u"); P.dt_s = geti("dt_s");
   P.u_is_input = geti("u_is_input"); P.mars = geti("mars"); P.cautious_wd = geti("cautious_wd");
   P.caution_apply = geti("caution_apply"); P.use_tensor_scale = geti("use_tensor_scale");
-  P.accum_sumsq = geti("accum_sumsq");
+  P.accum_sumsq = geti("accum_sumsq"); P.u_op = geti("u_op");
   P.lr = getf("lr"); P.wd = getf("wd"); P.eps = getf("eps");
   P.b1 = getf("b1"); P.b2 = getf("b2"); P.b3 = getf("b3"); P.alpha = getf("alpha"); P.mars_a = getf("mars_a");
   P.seed = cfg.contains("seed") ? cfg["seed"].cast<uint64_t>() : 0;
@@ -271,6 +271,62 @@ at::Tensor cross_entropy_(at::Tensor& logits, const at::Tensor& targets, const a
   return loss;
 }
 
+// Split-tf32 operands of a contiguous fp32 [batch, R, C] tensor: rows of [hi | lo] (see tf32_gemm.h).  Returns
+// (same, trans): same = [batch, R, 2 kp(C)] (operand rows = rows of x), trans = [batch, C, 2 kp(R)] (operand rows =
+// columns of x); an orientation that was not asked for comes back undefined.
+std::vector<at::Tensor> tf32_split(const at::Tensor& x, bool want_same, bool want_trans) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.dim() == 3 && x.is_contiguous(),
+              "tf32_split: contiguous fp32 [batch, rows, cols] CUDA tensor");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t batch = x.size(0), R = x.size(1), C = x.size(2);
+  at::Tensor same = want_same ? at::empty({batch, R, 2 * hb::tf32_split_kp(C)}, x.options()) : at::Tensor();
+  at::Tensor trans = want_trans ? at::empty({batch, C, 2 * hb::tf32_split_kp(R)}, x.options()) : at::Tensor();
+  check(hb::launch_tf32_split(x.data_ptr<float>(), C, R * C, (int)R, (int)C, (int)batch,
+                              want_same ? same.data_ptr<float>() : nullptr, want_trans ? trans.data_ptr<float>() : nullptr,
+                              at::cuda::getCurrentCUDAStream()), "tf32 split");
+  return {same, trans};
+}
+
+// epilogue(A * B^T) over split operands a2: [batch, M, 2 kp(K)], b2: [batch, N, 2 kp(K)] (see tf32_gemm.h).
+//   mode 0 store, 1 lerp into `c` with weight w, 2 Adam / 3 LaProp on the moments m, v ([batch, M, N] fp32, in place).
+//   c: fp32 [batch, M, >= N] output (optional unless mode 1).  split_out: 0 none, 1 also / instead write the result as
+//   a split operand with rows = output rows, 2 with rows = output columns; it is returned (undefined when 0).
+at::Tensor tf32_gemm(const at::Tensor& a2, const at::Tensor& b2, int64_t K, int mode, double alpha, double w, double b1,
+                     double b2c, double eps, const OptT& c, int split_out, const OptT& m, const OptT& v,
+                     const at::Tensor& status) {
+  TORCH_CHECK(a2.is_cuda() && b2.is_cuda() && a2.scalar_type() == at::kFloat && b2.scalar_type() == at::kFloat &&
+                  a2.dim() == 3 && b2.dim() == 3 && a2.is_contiguous() && b2.is_contiguous() && a2.size(0) == b2.size(0),
+              "tf32_gemm: contiguous fp32 split operands [batch, rows, 2 kp]");
+  const int64_t batch = a2.size(0), M = a2.size(1), N = b2.size(1), kp = hb::tf32_split_kp(K);
+  TORCH_CHECK(a2.size(2) == 2 * kp && b2.size(2) == 2 * kp, "tf32_gemm: operands were not split for K = ", K);
+  c10::cuda::CUDAGuard guard(a2.device());
+  hb::Tf32Epilogue E{};
+  E.mode = mode; E.alpha = (float)alpha; E.w = (float)w; E.b1 = (float)b1; E.b2 = (float)b2c; E.eps = (float)eps;
+  if (c.has_value() && c->defined()) {
+    TORCH_CHECK(c->is_cuda() && c->scalar_type() == at::kFloat && c->dim() == 3 && c->size(0) == batch && c->size(1) == M &&
+                    c->size(2) >= N && c->stride(2) == 1 && c->stride(1) >= N && c->device() == a2.device(),
+                "tf32_gemm: c must be fp32 [batch, M, >= N] with unit inner stride");
+    E.C = c->data_ptr<float>(); E.ldc = c->stride(1); E.strideC = c->stride(0);
+  }
+  at::Tensor s;
+  if (split_out != 0) {
+    const int64_t rows = split_out == 1 ? M : N, kps = hb::tf32_split_kp(split_out == 1 ? N : M);
+    s = at::empty({batch, rows, 2 * kps}, a2.options());
+    E.S = s.data_ptr<float>(); E.kpS = kps; E.strideS = rows * 2 * kps; E.s_transposed = split_out == 2 ? 1 : 0;
+  }
+  if (mode == hb::kEpiAdam || mode == hb::kEpiLaProp) {
+    TORCH_CHECK(m.has_value() && v.has_value(), "tf32_gemm: moment buffers required");
+    for (const at::Tensor* t : {&*m, &*v})
+      TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == batch * M * N &&
+                      t->device() == a2.device(), "tf32_gemm: moments must be contiguous fp32 [batch, M, N]");
+    E.m = m->data_ptr<float>(); E.v = v->data_ptr<float>();
+  }
+  TORCH_CHECK(E.C != nullptr || E.S != nullptr, "tf32_gemm: no output requested");
+  check(hb::launch_tf32_gemm(a2.data_ptr<float>(), b2.data_ptr<float>(), (int)M, (int)N, (int)K, (int)batch, E,
+                             status.data_ptr<int>(), at::cuda::getCurrentCUDAStream()), "tf32 gemm");
+  return s;
+}
+
 // op(a) @ op(b) for batched fp32 matrices on the split-tf32 tensor-core path.  a: [batch, R, C]; ta = 0 uses a as
 // [M, K], ta = 1 as [K, M]; likewise b is [K, N] for tb = 0 and [N, K] for tb = 1.  Returns [batch, M, N].
 at::Tensor tf32x3_matmul(const at::Tensor& a, const at::Tensor& b, bool ta, bool tb, double alpha, const at::Tensor& status) {
@@ -284,15 +340,22 @@ at::Tensor tf32x3_matmul(const at::Tensor& a, const at::Tensor& b, bool ta, bool
   c10::cuda::CUDAGuard guard(a.device());
   auto stream = at::cuda::getCurrentCUDAStream();
   const int64_t kp = hb::tf32_split_kp(K), ldc = (N + 3) / 4 * 4;
-  at::Tensor a3 = at::empty({batch, M, 3 * kp}, a.options()), b3 = at::empty({batch, N, 3 * kp}, a.options());
+  at::Tensor a2 = at::empty({batch, M, 2 * kp}, a.options());
+  const bool same_operand = a.data_ptr() == b.data_ptr() && a.sizes() == b.sizes() && ta != tb;  // X X^T or X^T X
+  at::Tensor b2 = same_operand ? a2 : at::empty({batch, N, 2 * kp}, a.options());
   at::Tensor c = at::empty({batch, M, ldc}, a.options());
   check(hb::launch_tf32_split(a.data_ptr<float>(), a.size(2), a.size(1) * a.size(2), (int)a.size(1), (int)a.size(2),
-                              (int)batch, ta ? 1 : 0, 0, a3.data_ptr<float>(), stream), "tf32 split A");
+                              (int)batch, ta ? nullptr : a2.data_ptr<float>(), ta ? a2.data_ptr<float>() : nullptr, stream),
+        "tf32 split A");
   // B as the K-major [N, K] operand: b given as [K, N] must be transposed, b given as [N, K] is used as it is
-  check(hb::launch_tf32_split(b.data_ptr<float>(), b.size(2), b.size(1) * b.size(2), (int)b.size(1), (int)b.size(2),
-                              (int)batch, tb ? 0 : 1, 1, b3.data_ptr<float>(), stream), "tf32 split B");
-  check(hb::launch_tf32_gemm(a3.data_ptr<float>(), b3.data_ptr<float>(), (int)M, (int)N, (int)K, (int)batch, (float)alpha,
-                             c.data_ptr<float>(), ldc, M * ldc, status.data_ptr<int>(), stream), "tf32 gemm");
+  if (!same_operand)
+    check(hb::launch_tf32_split(b.data_ptr<float>(), b.size(2), b.size(1) * b.size(2), (int)b.size(1), (int)b.size(2),
+                                (int)batch, tb ? b2.data_ptr<float>() : nullptr, tb ? nullptr : b2.data_ptr<float>(), stream),
+          "tf32 split B");
+  hb::Tf32Epilogue E{};
+  E.mode = hb::kEpiStore; E.alpha = (float)alpha; E.C = c.data_ptr<float>(); E.ldc = ldc; E.strideC = M * ldc;
+  check(hb::launch_tf32_gemm(a2.data_ptr<float>(), b2.data_ptr<float>(), (int)M, (int)N, (int)K, (int)batch, E,
+                             status.data_ptr<int>(), stream), "tf32 gemm");
   return ldc == N ? c : c.narrow(2, 0, N);
 }
 
@@ -426,6 +489,8 @@ std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tf32x3_matmul", &tf32x3_matmul);
+  m.def("tf32_split", &tf32_split);
+  m.def("tf32_gemm", &tf32_gemm);
   m.def("colsum_bf16", &colsum_bf16);
   m.def("colsum_bf16_batch", &colsum_bf16_batch);
   m.def("gelu_fwd", &gelu_fwd);

@@ -87,6 +87,15 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
       g = load4(M.g, nullptr, P.dt_g, i, nv, vec_ok);
     }
     F4 u = P.u_is_input ? load4(M.u, nullptr, P.dt_u, i, nv, vec_ok) : g;
+    if (P.u_is_input && P.u_op == kUopTrustRegion) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float x = u.v[k] * (1.0f / 1.5f);
+        const float t = tanhf(x);
+        const float y = copysignf(log1pf(fabsf(x)), t) * 0.1f + t * 0.9f;
+        u.v[k] = fminf(fmaxf(y * 1.5f, -2.0f), 2.0f);
+      }
+    }
     F4 p = P.out_mode == kOutParam ? load4(M.p, M.pe, P.dt_p, i, nv, vec_ok) : F4{};
     F4 out;
 

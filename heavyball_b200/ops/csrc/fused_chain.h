@@ -34,6 +34,8 @@ enum Algo : int {
   kNesterovMom
 };
 enum OutMode : int { kOutParam = 0, kOutUpdate = 1 };
+// kUopTrustRegion: 0.9 tanh(x / 1.5) + 0.1 sign(x) log1p(|x| / 1.5), times 1.5, limited to +-2 (PSGD's default update clip)
+enum UpdateOp : int { kUopNone = 0, kUopTrustRegion = 1 };
 
 struct ChainParams {
   int n_tensors;
@@ -47,6 +49,7 @@ struct ChainParams {
   int caution_apply; // phase two: rescale by numel / (numel - masked)
   int use_tensor_scale;
   int accum_sumsq;   // kOutUpdate: add sum(update^2) of every tensor into its `scale` slot
+  int u_op;          // transformation of an incoming update (u_is_input) before anything else: see UpdateOp
   float lr, wd, eps;
   float b1, b2, b3, alpha;  // already debiased / scheduled on the host
   float mars_a;

@@ -1,19 +1,26 @@
-// fp32-in / fp32-out batched GEMM at near-fp32 accuracy on the tf32 tensor-core path of sm_100a ("3xTF32").
+// fp32-in / fp32-out batched GEMM at near-fp32 accuracy on the tf32 tensor-core path of sm_100a ("3xTF32"), with the
+// element-wise stages of SOAP and PSGD fused into its epilogue.
 //
 // The preconditioner algebra of SOAP and PSGD (eigenbasis projections, Gram statistics, Kronecker factor
-// products; heavyball/utils.py:1211-1324, 2079-2236 of the reference run them as fp32 cuBLAS einsums) needs more
-// than tf32's 10 mantissa bits, and fp32 SIMT GEMMs run at a twentieth of the tensor-core rate.  Each operand is
-// therefore split once into hi = tf32(x) and lo = tf32(x - hi), and the product is taken as
+// products; heavyball/utils.py:1205-1259, 1391-1411, 3084-3122, 3557-3576 of the reference run them as fp32 cuBLAS
+// einsums) needs more than tf32's 10 mantissa bits, and fp32 SIMT GEMMs run at a twentieth of the tensor-core rate.
+// Each operand is therefore split once into hi = tf32(x) and lo = tf32(x - hi), stored side by side as rows of
+// [hi | lo], and the product is taken as
 //     A B^T ~= hi_a hi_b^T + hi_a lo_b^T + lo_a hi_b^T
-// The split kernel lays the three terms out along K - A rows as [hi | hi | lo], B rows as [hi | lo | hi] - so the
-// whole sum is ONE K-major tf32 GEMM over 3K with a single fp32 accumulator in tensor memory; the dropped
-// lo*lo term and the rounding of lo to tf32 are both below 2^-21.  Measured error: about 2^-18 of |A||B|^T for
-// K = 2048 (fp32 SIMT: 2^-21, one tf32 pass: 2^-11); it is set by the rounding of the tensor core's accumulator.
+// by walking A as (hi, hi, lo) and B as (hi, lo, hi) along K: ONE K-major tf32 GEMM over 3K with a single fp32
+// accumulator in tensor memory.  The dropped lo*lo term and the rounding of lo to tf32 are both below 2^-21.
+// Measured error: about 2^-18 of |A||B|^T for K = 2048 (fp32 SIMT: 2^-21, one tf32 pass: 2^-11); it is set by the
+// rounding of the tensor core's accumulator.  One split buffer serves as either operand, so a symmetric product
+// X X^T needs one split of X, and matrices that change rarely (eigenbases, preconditioner factors) stay split.
 //
 // GEMM kernel (one 128x128 output tile per CTA, 192 threads, two CTAs per SM):
 //   warp 0     : TMA producer, cp.async.bulk.tensor 3-D loads (128-byte swizzle, 32 fp32 per row) into a 3-stage ring
 //   warp 1     : tcgen05.mma.cta_group::1.kind::tf32, 128x128x8 per instruction, accumulator in 128 TMEM columns
-//   warps 2..5 : tcgen05.ld, scale by alpha, stage the fp32 tile in the (now idle) ring, four bulk tensor stores
+//   warps 2..5 : tcgen05.ld, then the epilogue.  Plain stores go through the (now idle) ring and four bulk tensor
+//                stores.  Fused epilogues work in registers and store directly: scale; lerp into the statistics
+//                matrix (GG <- lerp(GG, G G^T)); Adam / LaProp in the eigenbasis (moments read and written in
+//                place, the preconditioned value goes on); and, for any of them, the result written in the split
+//                [hi | lo] layout - as it is or transposed - so the next product of the chain needs no split pass.
 // Waits are bounded as in the bf16 kernels: on expiry the CTA flags `status`, drains, frees TMEM and returns.
 #include "tf32_gemm.h"
 
@@ -33,9 +40,149 @@ constexpr uint32_t kTTmemCols = 128;
 constexpr uint32_t kTf32InstrDesc =
     (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(TBN >> 3) << 17) | ((uint32_t)(TBM >> 4) << 24);
 
+__device__ __forceinline__ float tf32_hi(float x) {
+  uint32_t bits;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(bits) : "f"(x));
+  return __uint_as_float(bits);
+}
+
+__device__ __forceinline__ float lerp_w(float s, float x, float w) { return s * (1.0f - w) + x * w; }
+
+// Fused epilogue of one thread: row `r` of the 128x128 tile, 32 accumulator columns at a time.  Values outside
+// [M, N] are never stored; the zero padding of a split output (columns [K, kp) of the operand being produced) is.
+__device__ __forceinline__ void epilogue_direct(uint32_t tmem_base, int quarter, int r, int tm, int tn, int batch, int M, int N,
+                                                const Tf32Epilogue& E) {
+  const int row = tm * TBM + r;
+  const int64_t b64 = batch;
+  const bool state_vec = (N & 3) == 0;
+  const bool c_vec = (E.ldc & 3) == 0 && ((E.strideC & 3) == 0);
+#pragma unroll 1
+  for (int cb = 0; cb < TBN / 32; ++cb) {
+    uint32_t acc[32];
+    tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cb * 32), acc);
+    tmem_ld_wait();
+    const int col0 = tn * TBN + cb * 32;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]) * E.alpha;
+
+    if (E.mode == kEpiAdam || E.mode == kEpiLaProp) {
+      if (row < M) {
+        float* mrow = E.m + (b64 * M + row) * (int64_t)N;
+        float* vrow = E.v + (b64 * M + row) * (int64_t)N;
+        const float w1 = 1.0f - E.b1, w2 = 1.0f - E.b2;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const int col = col0 + q * 4;
+          if (col >= N) break;
+          float m4[4], s4[4];
+          const bool fast = state_vec && col + 3 < N;
+          if (fast) {
+            const float4 a = *(const float4*)(mrow + col), c = *(const float4*)(vrow + col);
+            m4[0] = a.x; m4[1] = a.y; m4[2] = a.z; m4[3] = a.w;
+            s4[0] = c.x; s4[1] = c.y; s4[2] = c.z; s4[3] = c.w;
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              m4[e] = col + e < N ? mrow[col + e] : 0.f;
+              s4[e] = col + e < N ? vrow[col + e] : 0.f;
+            }
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float x = v[q * 4 + e];
+            s4[e] = lerp_w(s4[e], x * x, w2);
+            const float d = fmaxf(sqrtf(s4[e]), E.eps);
+            if (E.mode == kEpiAdam) {
+              m4[e] = lerp_w(m4[e], x, w1);
+              v[q * 4 + e] = m4[e] / d;
+            } else {
+              m4[e] = lerp_w(m4[e], x / d, w1);
+              v[q * 4 + e] = m4[e];
+            }
+          }
+          if (fast) {
+            *(float4*)(mrow + col) = make_float4(m4[0], m4[1], m4[2], m4[3]);
+            *(float4*)(vrow + col) = make_float4(s4[0], s4[1], s4[2], s4[3]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (col + e < N) { mrow[col + e] = m4[e]; vrow[col + e] = s4[e]; }
+          }
+        }
+      }
+    }
+
+    if (E.C != nullptr && row < M) {
+      float* crow = E.C + b64 * E.strideC + (int64_t)row * E.ldc;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const int col = col0 + q * 4;
+        if (col >= N) break;
+        const bool fast = c_vec && col + 3 < N;
+        if (E.mode == kEpiLerp) {
+          if (fast) {
+            const float4 o = *(const float4*)(crow + col);
+            v[q * 4] = o.x + (v[q * 4] - o.x) * E.w; v[q * 4 + 1] = o.y + (v[q * 4 + 1] - o.y) * E.w;
+            v[q * 4 + 2] = o.z + (v[q * 4 + 2] - o.z) * E.w; v[q * 4 + 3] = o.w + (v[q * 4 + 3] - o.w) * E.w;
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (col + e < N) { const float o = crow[col + e]; v[q * 4 + e] = o + (v[q * 4 + e] - o) * E.w; }
+          }
+        }
+        if (fast) {
+          *(float4*)(crow + col) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (col + e < N) crow[col + e] = v[q * 4 + e];
+        }
+      }
+    }
+
+    if (E.S != nullptr) {
+      float* sb = E.S + b64 * E.strideS;
+      const int64_t ld = 2 * E.kpS;
+      if (!E.s_transposed) {  // operand rows = output rows, K runs over the output columns (zero from N up to kp)
+        if (row < M) {
+          float* srow = sb + (int64_t)row * ld;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const int col = col0 + q * 4;
+            if (col >= E.kpS) break;
+            float hi[4], lo[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float x = col + e < N ? v[q * 4 + e] : 0.f;
+              hi[e] = tf32_hi(x);
+              lo[e] = tf32_hi(x - hi[e]);
+            }
+            *(float4*)(srow + col) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+            *(float4*)(srow + E.kpS + col) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+          }
+        }
+      } else if (row < E.kpS) {  // operand rows = output columns, K runs over the output rows (zero from M up to kp)
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int col = col0 + j;
+          if (col < N) {
+            const float x = row < M ? v[j] : 0.f;
+            const float hi = tf32_hi(x);
+            float* dst = sb + (int64_t)col * ld + row;
+            dst[0] = hi;
+            dst[E.kpS] = tf32_hi(x - hi);
+          }
+        }
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kTThreads, 2)
 tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 const __grid_constant__ CUtensorMap map_c, int M, int N, int K3, float alpha, int* status) {
+                 const __grid_constant__ CUtensorMap map_c, int M, int N, int kp, const Tf32Epilogue E, int bulk_store,
+                 int* status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kTStages];
   __shared__ __align__(8) uint64_t empty_bar[kTStages];
@@ -48,7 +195,9 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int tiles_n = (N + TBN - 1) / TBN;
   const int tm = blockIdx.x / tiles_n, tn = blockIdx.x % tiles_n, batch = blockIdx.y;
-  const int num_kb = (K3 + TBK - 1) / TBK;
+  const int seg_kb = kp / TBK;      // K blocks per term of the split product
+  const int num_kb = 3 * seg_kb;    // hi*hi, hi*lo, lo*hi
+  const float alpha = E.alpha;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kTStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -69,9 +218,10 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int s = kb % kTStages, round = kb / kTStages;
         if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &abort_flag)) break;
         uint8_t* dst = tiles + s * kTStageBytes;
+        const int seg = kb / seg_kb, k0 = (kb - seg * seg_kb) * TBK;
         mbar_expect_tx(&full_bar[s], kTStageBytes);
-        tma_load_3d(dst, &map_a, &full_bar[s], kb * TBK, tm * TBM, batch);
-        tma_load_3d(dst + kTTileBytes, &map_b, &full_bar[s], kb * TBK, tn * TBN, batch);
+        tma_load_3d(dst, &map_a, &full_bar[s], k0 + (seg == 2 ? kp : 0), tm * TBM, batch);               // hi, hi, lo
+        tma_load_3d(dst + kTTileBytes, &map_b, &full_bar[s], k0 + (seg == 1 ? kp : 0), tn * TBN, batch);  // hi, lo, hi
         issued = kb + 1;
       }
     }
@@ -96,19 +246,14 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int quarter = warp & 3, r = quarter * 32 + lane;
     const bool have = (num_kb == 0) || mbar_wait(&accum_bar, 0, &abort_flag);
     tc_fence_after();
-    if (have) {
+    if (have && bulk_store) {
       // every load has landed and every MMA has retired: the ring is free and stages the output tile as four
       // [128 rows x 32 fp32] boxes in the swizzled layout the bulk store expects
 #pragma unroll 1
       for (int cb = 0; cb < TBN / 32; ++cb) {
         uint32_t acc[32];
-        if (num_kb > 0) {
-          tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cb * 32), acc);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) acc[j] = 0u;
-        }
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cb * 32), acc);
+        tmem_ld_wait();
         uint8_t* box = tiles + cb * kTTileBytes;
 #pragma unroll
         for (int q = 0; q < 8; ++q)
@@ -116,16 +261,20 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               make_float4(__uint_as_float(acc[q * 4]) * alpha, __uint_as_float(acc[q * 4 + 1]) * alpha,
                           __uint_as_float(acc[q * 4 + 2]) * alpha, __uint_as_float(acc[q * 4 + 3]) * alpha);
       }
+    } else if (have) {
+      epilogue_direct(tmem_base, quarter, r, tm, tn, batch, M, N, E);
     }
     tc_fence_before();
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (have && warp == 2 && lane == 0) {
+    if (bulk_store) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (have && warp == 2 && lane == 0) {
 #pragma unroll
-      for (int cb = 0; cb < TBN / 32; ++cb)
-        if (tn * TBN + cb * 32 < N) tma_store_3d(&map_c, tiles + cb * kTTileBytes, tn * TBN + cb * 32, tm * TBM, batch);
-      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        for (int cb = 0; cb < TBN / 32; ++cb)
+          if (tn * TBN + cb * 32 < N) tma_store_3d(&map_c, tiles + cb * kTTileBytes, tn * TBN + cb * 32, tm * TBM, batch);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      }
     }
   }
 
@@ -141,31 +290,21 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, kTTmemCols); }
 }
 
-__device__ __forceinline__ float tf32_hi(float x) {
-  uint32_t bits;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(bits) : "f"(x));
-  return __uint_as_float(bits);
-}
-
-// One block moves a 64 x 64 tile of the source through shared memory and writes the three K segments of the
-// operand rows it covers.  k runs over the source columns (transpose = 0) or rows (transpose = 1); the range
-// [K, kp) of every segment is zero-filled.  256 threads = 16 float4 lanes x 16 rows, four passes each way; global
-// accesses are 16 bytes wide (the source falls back to scalars when its rows are not 16-byte aligned).
-// Grid: (ceil(kp / 64), ceil(rows / 64), batch).
+// One block moves a 64 x 64 tile of the source through shared memory and writes the [hi | lo] rows it covers of either
+// or both operand orientations (see tf32_gemm.h).  The zero padding [K, kp) of every row is written too.  256 threads
+// = 16 float4 lanes x 16 rows, four passes each way; global accesses are 16 bytes wide (the source falls back to
+// scalars when its rows are not 16-byte aligned).  Grid: (ceil(kp(C) / 64), ceil(kp(R) / 64), batch).
 __global__ void __launch_bounds__(256) tf32_split_kernel(const float* __restrict__ src, int64_t ld_src, int64_t stride_src,
-                                                        int R, int C, int transpose, int role_b, float* __restrict__ dst,
-                                                        int rows, int K, int kp) {
-  __shared__ float tile[64][65];  // [operand row][k]
+                                                        int R, int C, float* __restrict__ dst_same,
+                                                        float* __restrict__ dst_trans, int kpC, int kpR) {
+  __shared__ float tile[64][65];  // [source row][source column]
   const float* s = src + (int64_t)blockIdx.z * stride_src;
-  float* d = dst + (int64_t)blockIdx.z * rows * 3 * kp;
-  const int k0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
+  const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
   const int lane4 = (threadIdx.x & 15) * 4, line = threadIdx.x >> 4;
   const bool vec_ok = (ld_src & 3) == 0 && (stride_src & 3) == 0 && (((uintptr_t)src) & 15) == 0;
-  // source tile: `line` walks the source rows, `lane4` the (contiguous) source columns
-  const int src_row0 = transpose ? k0 : r0, src_col0 = transpose ? r0 : k0;
 #pragma unroll
   for (int pass = 0; pass < 4; ++pass) {
-    const int lr = line + 16 * pass, sr = src_row0 + lr, sc = src_col0 + lane4;
+    const int lr = line + 16 * pass, sr = r0 + lr, sc = c0 + lane4;
     float v[4] = {0.f, 0.f, 0.f, 0.f};
     if (sr < R) {
       const float* row = s + (int64_t)sr * ld_src;
@@ -179,29 +318,45 @@ __global__ void __launch_bounds__(256) tf32_split_kernel(const float* __restrict
       }
     }
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      if (transpose) tile[lane4 + e][lr] = v[e];
-      else tile[lr][lane4 + e] = v[e];
-    }
+    for (int e = 0; e < 4; ++e) tile[lr][lane4 + e] = v[e];
   }
   __syncthreads();
+  if (dst_same != nullptr) {  // rows = source rows, k = source columns
+    float* d = dst_same + (int64_t)blockIdx.z * R * 2 * kpC;
 #pragma unroll
-  for (int pass = 0; pass < 4; ++pass) {
-    const int lr = line + 16 * pass, r = r0 + lr, k = k0 + lane4;
-    if (r >= rows || k >= kp) continue;  // kp is a multiple of 32, so a float4 never straddles it
-    float hi[4], lo[4];
+    for (int pass = 0; pass < 4; ++pass) {
+      const int lr = line + 16 * pass, r = r0 + lr, k = c0 + lane4;
+      if (r >= R || k >= kpC) continue;  // kp is a multiple of 32, so a float4 never straddles it
+      float hi[4], lo[4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float x = tile[lr][lane4 + e];
-      // lo is rounded to tf32 here (the tensor core would truncate it): halves the error of the two cross terms
-      hi[e] = tf32_hi(x);
-      lo[e] = tf32_hi(x - hi[e]);
+      for (int e = 0; e < 4; ++e) {
+        const float x = tile[lr][lane4 + e];
+        // lo is rounded to tf32 here (the tensor core would truncate it): halves the error of the two cross terms
+        hi[e] = tf32_hi(x);
+        lo[e] = tf32_hi(x - hi[e]);
+      }
+      float* row = d + (int64_t)r * 2 * kpC + k;
+      *reinterpret_cast<float4*>(row) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+      *reinterpret_cast<float4*>(row + kpC) = make_float4(lo[0], lo[1], lo[2], lo[3]);
     }
-    const float4 h4 = make_float4(hi[0], hi[1], hi[2], hi[3]), l4 = make_float4(lo[0], lo[1], lo[2], lo[3]);
-    float* row = d + (int64_t)r * 3 * kp + k;
-    *reinterpret_cast<float4*>(row) = h4;
-    *reinterpret_cast<float4*>(row + kp) = role_b ? l4 : h4;
-    *reinterpret_cast<float4*>(row + 2 * kp) = role_b ? h4 : l4;
+  }
+  if (dst_trans != nullptr) {  // rows = source columns, k = source rows
+    float* d = dst_trans + (int64_t)blockIdx.z * C * 2 * kpR;
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+      const int lc = line + 16 * pass, c = c0 + lc, k = r0 + lane4;
+      if (c >= C || k >= kpR) continue;
+      float hi[4], lo[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float x = tile[lane4 + e][lc];
+        hi[e] = tf32_hi(x);
+        lo[e] = tf32_hi(x - hi[e]);
+      }
+      float* row = d + (int64_t)c * 2 * kpR + k;
+      *reinterpret_cast<float4*>(row) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+      *reinterpret_cast<float4*>(row + kpR) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+    }
   }
 }
 
@@ -220,18 +375,17 @@ bool make_f32_map(CUtensorMap* map, const void* base, int rows, int64_t cols, in
 
 }  // namespace
 
-cudaError_t launch_tf32_split(const float* src, int64_t ld_src, int64_t stride_src, int R, int C, int batch, int transpose,
-                              int role_b, float* dst, cudaStream_t stream) {
-  const int rows = transpose ? C : R, K = transpose ? R : C;
-  const int kp = (int)tf32_split_kp(K);
-  if (rows == 0 || batch == 0) return cudaSuccess;
-  dim3 grid((kp + 63) / 64, (rows + 63) / 64, batch);
-  tf32_split_kernel<<<grid, 256, 0, stream>>>(src, ld_src, stride_src, R, C, transpose, role_b, dst, rows, K, kp);
+cudaError_t launch_tf32_split(const float* src, int64_t ld_src, int64_t stride_src, int R, int C, int batch, float* dst_same,
+                              float* dst_trans, cudaStream_t stream) {
+  if (R == 0 || C == 0 || batch == 0 || (dst_same == nullptr && dst_trans == nullptr)) return cudaSuccess;
+  const int kpC = (int)tf32_split_kp(C), kpR = (int)tf32_split_kp(R);
+  dim3 grid((kpC + 63) / 64, (kpR + 63) / 64, batch);
+  tf32_split_kernel<<<grid, 256, 0, stream>>>(src, ld_src, stride_src, R, C, dst_same, dst_trans, kpC, kpR);
   return cudaGetLastError();
 }
 
-cudaError_t launch_tf32_gemm(const float* A3, const float* B3, int M, int N, int K, int batch, float alpha, float* C,
-                             int64_t ldc, int64_t strideC, int* status, cudaStream_t stream) {
+cudaError_t launch_tf32_gemm(const float* A2, const float* B2, int M, int N, int K, int batch, const Tf32Epilogue& E,
+                             int* status, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(tf32_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTSmemBytes);
@@ -239,13 +393,19 @@ cudaError_t launch_tf32_gemm(const float* A3, const float* B3, int M, int N, int
     configured = true;
   }
   if (M == 0 || N == 0 || batch == 0) return cudaSuccess;
-  const int64_t k3 = 3 * tf32_split_kp(K);
+  if ((E.mode == kEpiAdam || E.mode == kEpiLaProp) && (E.m == nullptr || E.v == nullptr)) return cudaErrorInvalidValue;
+  if (E.mode == kEpiLerp && E.C == nullptr) return cudaErrorInvalidValue;
+  const int64_t kp = tf32_split_kp(K), ld = 2 * kp;
+  // plain products leave through the bulk-store path; everything else is written by the epilogue threads themselves
+  const int bulk = (E.mode == kEpiStore && E.S == nullptr && E.C != nullptr && (E.ldc & 3) == 0 && (E.strideC & 3) == 0 &&
+                    (((uintptr_t)E.C) & 15) == 0) ? 1 : 0;
   CUtensorMap ma, mb, mc;
-  if (!make_f32_map(&ma, A3, M, k3, k3, (int64_t)M * k3, batch) || !make_f32_map(&mb, B3, N, k3, k3, (int64_t)N * k3, batch) ||
-      !make_f32_map(&mc, C, M, N, ldc, strideC, batch))
+  if (!make_f32_map(&ma, A2, M, ld, ld, (int64_t)M * ld, batch) || !make_f32_map(&mb, B2, N, ld, ld, (int64_t)N * ld, batch))
     return cudaErrorInvalidValue;
+  mc = ma;  // placeholder when the bulk-store path is not taken (never dereferenced then)
+  if (bulk && !make_f32_map(&mc, E.C, M, N, E.ldc, E.strideC, batch)) return cudaErrorInvalidValue;
   dim3 grid(((M + TBM - 1) / TBM) * ((N + TBN - 1) / TBN), batch);
-  tf32_gemm_kernel<<<grid, kTThreads, kTSmemBytes, stream>>>(ma, mb, mc, M, N, (int)k3, alpha, status);
+  tf32_gemm_kernel<<<grid, kTThreads, kTSmemBytes, stream>>>(ma, mb, mc, M, N, (int)kp, E, bulk, status);
   return cudaGetLastError();
 }
 

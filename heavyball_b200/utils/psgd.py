@@ -496,9 +496,10 @@ def psgd_calc_A_and_conjB(G: Tensor, Q, conjB: Optional[Tensor]):
     return A, conjB
 
 
-def _outer(expr: str, x: Tensor, mode: int) -> Tensor:
-    """Per-mode second moment ``x_(mode) x_(mode)^T`` (fp32); matrices take the tensor-core product."""
-    if x.ndim == 3:
+def _outer(expr: str, x: Tensor, mode: int, dense: bool = True) -> Tensor:
+    """Per-mode second moment (fp32): ``x_(mode) x_(mode)^T`` for a dense factor (matrices take the tensor-core
+    product), only its diagonal for a diagonal factor."""
+    if dense and x.ndim == 3:
         x32 = promote(x)
         out = _tc_matmul(x32, x32, mode == 1, mode == 0)
         if out is not None:
@@ -522,8 +523,8 @@ def psgd_update_precond(G, precond_lr, oq, store_triu_as_line, beta2, V, running
     A, conjB = psgd_calc_A_and_conjB(G, Q, V)
     del V
     for mode, (oq_i, q, expr, lb) in enumerate(zip(oq, Q, exprs, running_lower_bound)):
-        t1 = _outer(expr, A, mode)
-        t2 = _outer(expr, conjB, mode)
+        t1 = _outer(expr, A, mode, q.ndim == 3)
+        t2 = _outer(expr, conjB, mode, q.ndim == 3)
         if q.ndim < 3:
             total = t1 + t2
             ell = _update_lb(total if q.ndim == 1 else total.amax(dim=-1), lb, lower_bount_beta)

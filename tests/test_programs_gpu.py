@@ -1,0 +1,173 @@
+"""Split-tf32 GEMM epilogues and the staged SOAP / PSGD programs on a B200, against fp64 / PyTorch definitions."""
+
+import pytest
+import torch
+
+import heavyball_b200 as hb
+from heavyball_b200 import lowering, ops
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(*shape, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return torch.randn(*shape, device="cuda", generator=g)
+
+
+def _unsplit(s, K):
+    """Dense value of a split operand: hi + lo of the first K columns."""
+    kp = s.shape[-1] // 2
+    return (s[..., :K].double() + s[..., kp : kp + K].double())
+
+
+def _tol(a, b):
+    return 3e-5 * float((a.abs() @ b.abs().transpose(-1, -2)).max())
+
+
+@pytest.mark.parametrize("B,M,N,K", [(2, 256, 128, 384), (3, 200, 136, 160), (1, 129, 300, 130)])
+def test_split_and_plain_product(B, M, N, K):
+    a, b = _rand(B, M, K, seed=1), _rand(B, N, K, seed=2)
+    a_s, a_t = ops.tf32_split(a, True, True)
+    assert torch.allclose(_unsplit(a_s, K), a.double(), atol=1e-6)
+    assert torch.allclose(_unsplit(a_t, M), a.double().transpose(1, 2), atol=1e-6)
+    kpK, kpM = a_s.shape[-1] // 2, a_t.shape[-1] // 2
+    assert float(a_s[..., K:kpK].abs().max() if kpK > K else 0) == 0 and float(a_t[..., M:kpM].abs().max() if kpM > M else 0) == 0
+    b_s, _ = ops.tf32_split(b, True, False)
+    want = a.double() @ b.double().transpose(1, 2)
+    out = torch.empty(B, M, N, device="cuda")
+    ops.tf32_gemm(a_s, b_s, K, out=out, alpha=0.5)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert float((out.double() - 0.5 * want).abs().max()) < _tol(a.double(), b.double())
+
+
+@pytest.mark.parametrize("B,M,N,K", [(2, 256, 128, 256), (2, 200, 136, 160)])
+def test_split_outputs_feed_the_next_product(B, M, N, K):
+    a, b = _rand(B, M, K, seed=3), _rand(B, N, K, seed=4)
+    a_s, _ = ops.tf32_split(a, True, False)
+    b_s, _ = ops.tf32_split(b, True, False)
+    want = a.double() @ b.double().transpose(1, 2)
+    tol = _tol(a.double(), b.double())
+    rows = ops.tf32_gemm(a_s, b_s, K, split_out=ops.SPLIT_ROWS)
+    cols = ops.tf32_gemm(a_s, b_s, K, split_out=ops.SPLIT_COLS)
+    torch.cuda.synchronize()
+    assert rows.shape == (B, M, 2 * ((N + 31) // 32 * 32)) and cols.shape == (B, N, 2 * ((M + 31) // 32 * 32))
+    assert float((_unsplit(rows, N) - want).abs().max()) < tol
+    assert float((_unsplit(cols, M) - want.transpose(1, 2)).abs().max()) < tol
+    kpN, kpM = rows.shape[-1] // 2, cols.shape[-1] // 2
+    if kpN > N:
+        assert float(rows[..., N:kpN].abs().max()) == 0 and float(rows[..., kpN + N :].abs().max()) == 0
+    if kpM > M:
+        assert float(cols[..., M:kpM].abs().max()) == 0 and float(cols[..., kpM + M :].abs().max()) == 0
+    # chain: (A B^T) C^T through the split output, no intermediate split pass
+    c = _rand(B, 144, N, seed=5)
+    c_s, _ = ops.tf32_split(c, True, False)
+    out = torch.empty(B, M, 144, device="cuda")
+    ops.tf32_gemm(rows, c_s, N, out=out)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want2 = want @ c.double().transpose(1, 2)
+    assert float((out.double() - want2).abs().max()) < 3e-5 * float((want.abs() @ c.double().abs().transpose(1, 2)).max())
+
+
+@pytest.mark.parametrize("B,M,N,K", [(2, 256, 256, 128), (2, 136, 136, 200)])
+def test_lerp_epilogue(B, M, N, K):
+    x = _rand(B, M, K, seed=6)
+    x_s, _ = ops.tf32_split(x, True, False)
+    gg = _rand(B, M, M, seed=7)
+    want = gg.double() + (x.double() @ x.double().transpose(1, 2) - gg.double()) * 0.25
+    ops.tf32_gemm(x_s, x_s, K, mode=ops.EPI_LERP, w=0.25, out=gg)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert float((gg.double() - want).abs().max()) < _tol(x.double(), x.double())
+
+
+@pytest.mark.parametrize("mode", ["adam", "laprop"])
+@pytest.mark.parametrize("B,M,N,K", [(2, 256, 128, 256), (2, 200, 138, 160)])
+def test_moment_epilogues(mode, B, M, N, K):
+    a, b = _rand(B, M, K, seed=8), _rand(B, N, K, seed=9)
+    a_s, _ = ops.tf32_split(a, True, False)
+    b_s, _ = ops.tf32_split(b, True, False)
+    m, v = _rand(B, M, N, seed=10) * 0.1, _rand(B, M, N, seed=11).abs()
+    m64, v64 = m.double(), v.double()
+    x = a.double() @ b.double().transpose(1, 2)
+    b1, b2, eps = 0.9, 0.95, 1e-8
+    v64 = v64 * b2 + x * x * (1 - b2)
+    d = v64.sqrt().clamp(min=eps)
+    if mode == "adam":
+        m64 = m64 * b1 + x * (1 - b1)
+        want = m64 / d
+    else:
+        m64 = m64 * b1 + (x / d) * (1 - b1)
+        want = m64
+    out = torch.empty(B, M, N, device="cuda")
+    s = ops.tf32_gemm(a_s, b_s, K, mode=ops.EPI_ADAM if mode == "adam" else ops.EPI_LAPROP, b1=b1, b2c=b2, eps=eps, m=m, v=v,
+                      out=out, split_out=ops.SPLIT_ROWS)  # fmt: skip
+    torch.cuda.synchronize()
+    ops.check_status()
+    tol = 1e-3
+    assert float((m.double() - m64).abs().max()) < tol * float(m64.abs().max())
+    assert float((v.double() - v64).abs().max()) < tol * float(v64.abs().max())
+    assert float((out.double() - want).abs().max()) < tol * float(want.abs().max())
+    assert float((_unsplit(s, N) - out.double()).abs().max()) < 1e-6 * float(want.abs().max()) + 1e-6
+
+
+def _train(name, kwargs, lowered, shapes, steps=6):
+    torch.manual_seed(0)
+    params = [torch.nn.Parameter(torch.randn(*s, device="cuda") * 0.1) for s in shapes]
+    before = lowering.enabled
+    lowering.enabled = lowered
+    try:
+        torch.manual_seed(1)
+        opt = getattr(hb, name)(params, **kwargs)
+        g = torch.Generator(device="cuda").manual_seed(5)
+        for _ in range(steps):
+            for p in params:
+                p.grad = torch.randn(p.shape, device="cuda", generator=g) * 0.1
+            opt.step()
+        torch.cuda.synchronize()
+        ops.check_status()
+        return [p.detach().clone() for p in params], opt
+    finally:
+        lowering.enabled = before
+
+
+PROGRAM_SHAPES = [(256, 384), (256, 384), (384, 128), (512,), (130, 200), (64, 32), (1, 256)]
+PROGRAM_CASES = [
+    ("SOAP", dict(lr=1e-2, precondition_frequency=100, max_precond_dim=512)),  # no refresh: moments and statistics only
+    ("SOAP", dict(lr=1e-2, precondition_frequency=3, max_precond_dim=300, caution=True)),
+    ("SOLP", dict(lr=1e-2, precondition_frequency=100, max_precond_dim=512)),
+    ("PSGDKron", dict(lr=1e-2, preconditioner_update_probability=1.0)),
+    ("PSGDKron", dict(lr=1e-2, preconditioner_update_probability=0.5, max_size_triangular=300, ecc="bf16+8")),
+    ("PSGDKron", dict(lr=1e-2, preconditioner_update_probability=1.0, update_clipping=None, caution=True)),
+]
+
+
+@pytest.mark.parametrize("name,kwargs", PROGRAM_CASES, ids=[f"{n}-{i}" for i, (n, _) in enumerate(PROGRAM_CASES)])
+def test_staged_program_follows_the_pytorch_path(name, kwargs):
+    """Same chain with and without lowering.  Exact agreement is not expected (different product kernels, and for PSGD
+    the random probe of the fit is drawn per bucket in both paths but the fit is chaotic), so the bound is relative to
+    the distance travelled."""
+    start, _ = _train(name, kwargs, True, PROGRAM_SHAPES, steps=0)
+    want, _ = _train(name, kwargs, False, PROGRAM_SHAPES)
+    got, opt = _train(name, kwargs, True, PROGRAM_SHAPES)
+    prog = lowering._program(opt)
+    assert prog is not None and any(k[0] == "bucket" for k in prog.workspace)
+    loose = name == "PSGDKron" or kwargs.get("precondition_frequency", 100) < 100
+    for s, w, g in zip(start, want, got):
+        moved = float((w - s).abs().max())
+        assert torch.isfinite(g).all() and moved > 0
+        assert float((g - w).abs().max()) <= (0.25 if loose else 0.02) * moved, (name, tuple(s.shape))
+
+
+def test_psgd_diagonal_factor_statistics_on_the_gpu():
+    """A dimension above ``max_size_triangular`` gets a diagonal factor; its statistics are a diagonal, not a matrix."""
+    torch.manual_seed(0)
+    p = torch.nn.Parameter(torch.randn(640, 256, device="cuda") * 0.1)
+    opt = hb.PSGDKron([p], lr=1e-3, max_size_triangular=512, preconditioner_update_probability=1.0)
+    for _ in range(3):
+        p.grad = torch.randn_like(p) * 0.1
+        opt.step()
+    assert torch.isfinite(p).all()
+    q = opt.state[p][0][opt._find_val_name("Q")]
+    assert q[0][0] is None and q[0][1].shape == (1, 640)  # packed form: diagonal factor for the 640 side

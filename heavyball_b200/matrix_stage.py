@@ -116,6 +116,52 @@ def backend_for(t: Tensor, dims: Sequence[int]):
     return TorchBackend
 
 
+# ---------------------------------------------------------------------------------------- captured regions
+
+GRAPH_MAX_BYTES = 256 << 20  # buckets larger than this run their fit / refresh eagerly (they are device-bound anyway)
+use_graphs = True
+_pool = None
+
+
+class Captured:
+    """Runs ``fn()`` - a fixed sequence of kernels over tensors at fixed addresses with fixed scalars - eagerly the
+    first time (libraries create their handles and workspaces outside capture), captures it into a CUDA graph the
+    second time and replays it afterwards.  A preconditioner fit or an eigenbasis refresh is hundreds of small
+    launches; replayed, the host no longer sets their duration.  ``key`` names everything the sequence depends on
+    (addresses, shapes, scalars): a different key drops the graph.  If capture fails the region stays eager."""
+
+    def __init__(self):
+        self.key = None
+        self.calls = 0
+        self.graph = None
+        self.failed = False
+
+    def __call__(self, fn, key, device):
+        global _pool
+        if not use_graphs or device.type != "cuda" or self.failed or torch.cuda.is_current_stream_capturing():
+            return fn()
+        if key != self.key:
+            self.key, self.calls, self.graph = key, 0, None
+        self.calls += 1
+        if self.calls == 1:
+            return fn()
+        if self.graph is None:
+            try:
+                if _pool is None:
+                    _pool = torch.cuda.graph_pool_handle()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, pool=_pool):
+                    fn()
+                self.graph = graph
+            except Exception as err:  # noqa: BLE001 - whatever stops capture, the eager sequence is still correct
+                self.failed = True
+                import warnings
+
+                warnings.warn(f"CUDA graph capture of a preconditioner update failed ({type(err).__name__}: {err}); running it eagerly")
+                return fn()
+        self.graph.replay()
+
+
 # ---------------------------------------------------------------------------------------- state adoption
 
 
@@ -162,6 +208,7 @@ class SoapBucket:
         self.GG: List[Optional[Tensor]] = [None, None]
         self.q_ops = None  # cached operands of the eigenbases, rebuilt after a refresh / re-adoption
         self.q_ptrs = None
+        self.refresh_region = Captured()
 
     def _adopt(self, members):
         k = self.keys
@@ -225,7 +272,10 @@ class SoapBucket:
         if len(self.GG) > 1 and self.GG[1] is not None:
             be.gemm(u_trans, u_trans, mode=ops.EPI_LERP, w=stat_w, out=self.GG[1])
         if refresh:
-            utils.get_orthogonal_matrix_QR(self.GG, self.Q, self.m)
+            small = U.numel() * 4 <= GRAPH_MAX_BYTES
+            key = (self.q_ptrs, self.m.data_ptr(), tuple(None if g is None else g.data_ptr() for g in self.GG), tuple(U.shape))
+            run = lambda: utils.get_orthogonal_matrix_QR(self.GG, self.Q, self.m)  # noqa: E731 - in place on the adopted state
+            self.refresh_region(run, key, U.device) if small else run()
             self.q_ops = None
 
 
@@ -246,6 +296,7 @@ class PsgdBucket:
         self.shapes = None
         self.p_ops = None  # (backend, [operand or diagonal scale per mode])
         self.q_ptrs = None
+        self.fit_region = Captured()
 
     def _adopt(self, members):
         kq, kl = self.keys["Q"], self.keys["running_lower_bound"]
@@ -298,11 +349,20 @@ class PsgdBucket:
 
     def fit(self, U: Tensor, group, param_like):
         """Preconditioner fitting step on the batched factors (in place on the adopted state)."""
-        vector, hessian_vector = utils.dampen_grad(U, group["dampening"])
-        utils.psgd_update_precond(
-            hessian_vector, group["precond_lr"], self._batched_q(), self.line, utils.get_beta2(group), vector, self.lb,
-            group["lower_bound_beta"], group["precond_update_power_iterations"],
-        )  # fmt: skip
+        scalars = (group["dampening"], group["precond_lr"], utils.get_beta2(group), group["lower_bound_beta"],
+                   group["precond_update_power_iterations"])  # fmt: skip
+
+        def run():
+            vector, hessian_vector = utils.dampen_grad(U, scalars[0])
+            utils.psgd_update_precond(
+                hessian_vector, scalars[1], self._batched_q(), self.line, scalars[2], vector, self.lb, scalars[3], scalars[4]
+            )
+
+        if U.numel() * 4 <= GRAPH_MAX_BYTES:
+            key = (self.q_ptrs, tuple(t.data_ptr() for t in self.lb), U.data_ptr(), tuple(U.shape), scalars)
+            self.fit_region(run, key, U.device)
+        else:
+            run()
         self.p_ops = None
 
     def run(self, members: List[dict], U: Tensor, out: Tensor, group, *, fit: bool, delayed: bool):

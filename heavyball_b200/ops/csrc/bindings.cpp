@@ -374,6 +374,19 @@ at::Tensor tall_t_mul(const at::Tensor& base, int64_t m, const at::Tensor& w) {
   return c;
 }
 
+// Inverses of the 128 x 128 diagonal blocks of a batch of upper-triangular fp32 matrices q: [batch, n, n] (unit inner
+// stride).  Returns [batch, ceil(n / 128), 128, 128]; entries below the diagonal of q are ignored.
+at::Tensor tri_inv_blocks(const at::Tensor& q) {
+  TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kFloat && q.dim() == 3 && q.size(1) == q.size(2) && q.stride(2) == 1,
+              "tri_inv_blocks: fp32 [batch, n, n] CUDA tensor with unit inner stride");
+  c10::cuda::CUDAGuard guard(q.device());
+  const int64_t batch = q.size(0), n = q.size(1), nb = (n + hb::kTriBlock - 1) / hb::kTriBlock;
+  at::Tensor x = at::empty({batch, nb, hb::kTriBlock, hb::kTriBlock}, q.options());
+  check(hb::launch_tri_inv_blocks(q.data_ptr<float>(), q.stride(1), q.stride(0), (int)batch, (int)n, x.data_ptr<float>(),
+                                  at::cuda::getCurrentCUDAStream()), "tri_inv_blocks launch");
+  return x;
+}
+
 // fp32 column sums of a contiguous bf16 matrix [rows, cols] (cols % 8 == 0).
 at::Tensor colsum_bf16(const at::Tensor& x) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kBFloat16 && x.is_contiguous() &&
@@ -496,6 +509,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gelu_fwd", &gelu_fwd);
   m.def("gelu_bwd", &gelu_bwd);
   m.def("tall_t_mul", &tall_t_mul);
+  m.def("tri_inv_blocks", &tri_inv_blocks);
   m.def("layer_norm_fwd", &layer_norm_fwd);
   m.def("layer_norm_bwd", &layer_norm_bwd);
   m.def("layer_norm_supported", &hb::layer_norm_supported);

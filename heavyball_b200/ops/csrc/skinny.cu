@@ -137,4 +137,57 @@ cudaError_t launch_tall_t_mul(const float* X, long long ldx, long long strideX, 
   return cudaGetLastError();
 }
 
+namespace {
+
+// One CTA inverts one upper-triangular block by back substitution; thread j produces column j of the inverse:
+//   x_jj = 1 / t_jj,   x_ij = -(sum_{k = i+1 .. j} t_ik x_kj) / t_ii   for i = j-1 .. 0.
+// Both the block and its inverse sit in shared memory (2 x 128 x 129 floats).  The work is O(blk^3 / 6) FMAs spread
+// over 128 threads; at 64 blocks per call this takes tens of microseconds, against a library triangular solve per
+// leaf that walks the batch one matrix at a time.
+__global__ void __launch_bounds__(kTriBlock) tri_inv_blocks_kernel(const float* __restrict__ Q, long long ld, long long strideQ,
+                                                                 int n, float* __restrict__ X) {
+  extern __shared__ float tri_smem[];
+  float (*t)[kTriBlock + 1] = reinterpret_cast<float (*)[kTriBlock + 1]>(tri_smem);
+  float (*x)[kTriBlock + 1] = reinterpret_cast<float (*)[kTriBlock + 1]>(tri_smem + kTriBlock * (kTriBlock + 1));
+  const int blk = blockIdx.x, b = blockIdx.y, nblk = gridDim.x;
+  const int r0 = blk * kTriBlock, size = min(kTriBlock, n - r0);
+  const float* q = Q + (long long)b * strideQ + (long long)r0 * ld + r0;
+  const int j = threadIdx.x;
+  for (int i = 0; i < kTriBlock; ++i) {  // row i of the block, coalesced over j
+    float v = (i == j) ? 1.f : 0.f;
+    if (i < size && j < size && j >= i) v = q[(long long)i * ld + j];
+    t[i][j] = v;
+    x[i][j] = 0.f;
+  }
+  __syncthreads();
+  {
+    x[j][j] = 1.0f / t[j][j];
+    for (int i = j - 1; i >= 0; --i) {
+      float s = 0.f;
+      for (int k = i + 1; k <= j; ++k) s = fmaf(t[i][k], x[k][j], s);
+      x[i][j] = -s / t[i][i];
+    }
+  }
+  __syncthreads();
+  float* out = X + ((long long)b * nblk + blk) * kTriBlock * kTriBlock;
+  for (int i = 0; i < kTriBlock; ++i) out[i * kTriBlock + j] = x[i][j];
+}
+
+}  // namespace
+
+cudaError_t launch_tri_inv_blocks(const float* Q, long long ld, long long strideQ, int batch, int n, float* X,
+                                  cudaStream_t stream) {
+  if (batch == 0 || n == 0) return cudaSuccess;
+  constexpr int kBytes = 2 * kTriBlock * (kTriBlock + 1) * (int)sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(tri_inv_blocks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  dim3 grid((n + kTriBlock - 1) / kTriBlock, batch);
+  tri_inv_blocks_kernel<<<grid, kTriBlock, kBytes, stream>>>(Q, ld, strideQ, n, X);
+  return cudaGetLastError();
+}
+
 }  // namespace hb

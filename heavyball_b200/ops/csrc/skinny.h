@@ -11,4 +11,11 @@ int tall_splits(int n);
 cudaError_t launch_tall_t_mul(const float* X, long long ldx, long long strideX, const float* W, long long ldw,
                               long long strideW, int batch, int n, int m, int p, float* C, cudaStream_t stream);
 
+// Inverses of the diagonal blocks of upper-triangular matrices: for T = Q[b] (n x n, row stride ld, batch stride
+// strideQ) and block index i, X[b][i] = inverse of T[i*blk : (i+1)*blk, i*blk : (i+1)*blk] (the last block may be
+// smaller; it is completed with an identity).  X: [batch, ceil(n / blk), blk, blk] fp32, blk = kTriBlock.
+constexpr int kTriBlock = 128;
+cudaError_t launch_tri_inv_blocks(const float* Q, long long ld, long long strideQ, int batch, int n, float* X,
+                                  cudaStream_t stream);
+
 }  // namespace hb

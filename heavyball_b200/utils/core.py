@@ -480,6 +480,8 @@ def _reducible(ts) -> bool:
         return False
     from .. import ops
 
+    if torch.cuda.is_current_stream_capturing():
+        return False  # these kernels read a pointer table uploaded from host memory, which a graph cannot replay
     return ops.available() and all(t.is_cuda and t.dtype == first.dtype and t.is_contiguous() and t.numel() > 0 for t in ts)
 
 

@@ -225,7 +225,12 @@ def _panel_qr_replayed(x: Tensor, fallback: Tensor = None):
             return _panel_cholesky_qr(x)
         slot = _qr_graphs[key] = [0, None]
     slot[0] += 1
-    if slot[1] is False or slot[0] == 1 or torch.cuda.is_current_stream_capturing():
+    if torch.cuda.is_current_stream_capturing():  # part of a larger captured region: no replay, and no host read
+        if fallback is None:
+            raise RuntimeError("a captured eigenbasis refresh needs a fallback basis (the host cannot read failure flags)")
+        out, bad = _panel_cholesky_qr(x, defer_check=True)
+        return torch.where(bad.view(*x.shape[:-2], 1, 1) > 0, fallback.to(out.dtype), out)
+    if slot[1] is False or slot[0] == 1:
         return _panel_cholesky_qr(x)
     if slot[1] is None:
         try:

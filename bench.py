@@ -588,7 +588,11 @@ _SCRUB = ("RANK", "LOCAL_RANK", "WORLD_SIZE", "LOCAL_WORLD_SIZE", "GROUP_RANK", 
 
 
 def child_command(args, config, extra, port):
-    own = [os.path.join(ROOT, "bench.py"), "--gpus", str(args.gpus), "--steps", str(args.secondary_steps), "--warmup", "3",
+    # SOAP refreshes its eigenbases every 10th step and PSGD fits on every 10th: a timed window spans one whole period,
+    # and the warm-up covers the first two refreshes / fits (the first runs eagerly, the second is captured)
+    periodic = CONFIGS[config]["optimizer"] in ("soap", "psgd")
+    steps, warmup = (10, 22) if periodic else (args.secondary_steps, 3)
+    own = [os.path.join(ROOT, "bench.py"), "--gpus", str(args.gpus), "--steps", str(steps), "--warmup", str(warmup),
            "--windows", "3", "--impl", args.impl, "--config", config, "--secondary", "off", "--ddp-mode", args.ddp_mode,
            *extra]  # fmt: skip
     if args.no_clocks:

@@ -1770,6 +1770,14 @@ class ChainOpt(utils.StatefulOptimizer):
 
     def _chain(self, group, g, p, caution):
         state = [self.state_(pi) for pi in p]
+        pecc = ECCConfig.from_group(group, key="param_ecc")
+        if pecc is not None:
+            # a parameter gathered on its owner rank is larger than the local rows its residual was created for: the
+            # owner keeps the residual of the whole tensor, like the rest of the state
+            for st, pi in zip(state, p):
+                held = st.get("param::ecc")
+                if held is None or held.shape != pi.shape:
+                    st["param::ecc"] = torch.zeros_like(pi, dtype=pecc.corr_dtype)
         from . import lowering
 
         if (p[0].is_cuda or lowering.cpu_programs) and lowering.try_run(self, state, group, list(g), list(p)):

@@ -57,7 +57,13 @@ _RULES = {
     "nesterov_ema": (ops.NESTEROV_EMA, ("momentum",)),
     "heavyball_momentum": (ops.HEAVYBALL, ("momentum",)),
     "nesterov_momentum": (ops.NESTEROV_MOM, ("momentum",)),
+    "update_by_nadam": (ops.NADAM, ("exp_avg", "exp_avg_sq")),
 }
+# gradient clips that become a segmented sum of squares plus a factor applied on load: (mode, over the whole group)
+_GRAD_CLIPS = {
+    "l2_clip_": (ops.CLIP_L2, False), "rmsnorm_clip_": (ops.CLIP_RMS, False),
+    "global_l2norm_clip": (ops.CLIP_L2, True), "global_rmsnorm_clip": (ops.CLIP_RMS, True),
+}  # fmt: skip
 
 
 _SOAP_INNER = {"scale_by_soap": "adam", "scale_by_soap_laprop": "laprop"}
@@ -69,11 +75,15 @@ _PSGD_STAGES = {
 
 
 class _Program:
-    __slots__ = ("kind", "mars", "palm", "rule", "ortho", "stage", "stage_kw", "u_op", "workspace")
+    __slots__ = ("kind", "mars", "palm", "rule", "ortho", "stage", "stage_kw", "u_op", "gclip", "post", "routes", "workspace")
 
-    def __init__(self, kind, mars, palm, rule, ortho=None, stage=None, stage_kw=None, u_op=0):
+    def __init__(self, kind, mars, palm, rule, ortho=None, stage=None, stage_kw=None, u_op=0, gclip=None, post=None,
+                 routes=None):  # fmt: skip
         self.kind, self.mars, self.palm, self.rule, self.ortho = kind, mars, palm, rule, ortho
         self.stage, self.stage_kw, self.u_op = stage, stage_kw or {}, u_op
+        self.gclip = gclip  # (mode, global) of a leading gradient clip, or None
+        self.post = post  # transform that consumes the rule's output inside the same launch (schedule-free)
+        self.routes = routes  # kind "route": [(predicate or None for the default, sub-program)]
         self.workspace = {}
 
 
@@ -89,10 +99,35 @@ def _match(fns) -> Optional[_Program]:
     mars = palm = None
     if fns and isinstance(fns[0], C.FunctionTransform) and fns[0].fn_name == "mars":
         mars = fns.pop(0)
+    gclip = None
+    clip_fn = getattr(fns[0], "wrapped_fn", None) if fns else None
+    if clip_fn is not None and fns[0].__name__.endswith("_to_2") and getattr(utils, getattr(clip_fn, "__name__", ""), None) is clip_fn:
+        if clip_fn.__name__ in _GRAD_CLIPS and mars is None:  # the norm is taken of the update the rule sees
+            gclip = _GRAD_CLIPS[clip_fn.__name__]
+            fns.pop(0)
     if fns and getattr(fns[0], "__name__", "") == "palm_beta2" and not isinstance(fns[0], C.FunctionTransform):
         palm = fns.pop(0)
     if not fns:
         return None
+    if len(fns) == 1 and isinstance(fns[0], C.Route) and mars is None and gclip is None:
+        routes = []
+        for pred, sub in [*fns[0].routes, (None, fns[0].default)]:
+            if sub is None:
+                return None
+            inner = _match(sub)
+            if inner is None or inner.kind == "route" or inner.palm is not None:
+                return None
+            routes.append((pred, inner))
+        return _Program("route", None, palm, None, routes=routes)
+    prog = _match_tail(fns, mars, palm)
+    if prog is not None and gclip is not None:
+        if prog.kind not in ("elementwise", "orthogonal"):
+            return None
+        prog.gclip = gclip
+    return prog
+
+
+def _match_tail(fns, mars, palm) -> Optional[_Program]:
     u_op = 0
     if getattr(fns[-1], "wrapped_fn", None) is utils.trust_region_clip_ and fns[-1].__name__.endswith("_to_2"):
         fns.pop()
@@ -120,6 +155,8 @@ def _match(fns) -> Optional[_Program]:
         return None
     if len(fns) == 1:
         return _Program("elementwise", mars, palm, rule, None)
+    if len(fns) == 2 and rule.fn_name == "scale_by_exp_avg_sq" and fns[1].fn_name == "update_by_schedule_free" and mars is None:
+        return _Program("elementwise", mars, palm, rule, None, post=fns[1])
     if len(fns) == 2 and fns[1].fn_name == "orthogonalize_update":
         return _Program("orthogonal", mars, palm, rule, fns[1])
     return None
@@ -219,6 +256,26 @@ def _weight_decay(rule_name, group):
     return group["weight_decay"]
 
 
+def _nadam_scalars(prog, states, group):
+    """NAdam's momentum schedule: the running product of ``mu`` is a 0-d state tensor per parameter (all equal).  It
+    is advanced on the device with one multi-tensor multiply and mirrored on the host, which is read from the device
+    only when the mirror is not from the previous step (first lowered step, or after a checkpoint was loaded)."""
+    step = group["step"]
+    beta1, beta2 = utils.get_beta1(group), utils.get_beta2(group)
+    mu, mu_next = utils._nadam_moments(beta1, step, group["momentum_decay"])
+    key = prog.rule._val_names["mu_product"]
+    cache_key = ("mu_product", id(group))
+    held = prog.workspace.get(cache_key)
+    product = held[1] if held is not None and held[0] == step - 1 else float(states[0][key])
+    product *= mu
+    torch._foreach_mul_([st[key] for st in states], mu)
+    prog.workspace[cache_key] = (step, product)
+    return {
+        "eps": group["eps"], "b1": beta1, "b2": utils.beta_debias(beta2, step),
+        "b3": (1 - mu) / (1 - product), "alpha": mu_next / (1 - product * mu_next),
+    }  # fmt: skip
+
+
 def _materialize_zero_state(tr: C.FunctionTransform, states, group, params):
     """Allocates the (all-zero) state of a rule without running it; used when gradients must not be
     consumed by the PyTorch path (peer data parallelism reduces them inside the kernels)."""
@@ -236,6 +293,7 @@ def _cut(t, seg):
     return t if seg is None else t.view(-1)[seg[0] : seg[1]]
 
 
+_NS_WORKSPACE_BYTES = 2 << 30  # Newton–Schulz work copies per call; larger buckets are processed in chunks
 cpu_programs = False  # tests: run the staged programs with PyTorch products on CPU to check their logic
 
 
@@ -248,8 +306,36 @@ def try_run(opt, states, group, grads, params) -> bool:
     prog = _program(opt)
     if prog is None:
         return False
+    if prog.kind == "route":
+        return _run_route(opt, prog, states, group, grads, params, on_gpu)
+    return _run(opt, prog, states, group, grads, params, on_gpu, False)
+
+
+def _run_route(opt, prog, states, group, grads, params, on_gpu) -> bool:
+    """Every parameter goes through the program of the first route whose predicate accepts it.  All routes are checked
+    before any of them runs, so a step is either lowered as a whole or left to the PyTorch definitions as a whole."""
+    if getattr(opt, "_peer", None) is not None and opt._peer.plan_for(group) is not None:
+        return False
+    taken, parts = set(), []
+    for pred, sub in prog.routes:
+        idx = [i for i, p in enumerate(params) if i not in taken and (pred is None or pred(p))]
+        taken.update(idx)
+        if idx:
+            pick = lambda xs: [xs[i] for i in idx]  # noqa: E731
+            parts.append((sub, pick(states), pick(grads), pick(params)))
+    if not all(_run(opt, sub, st, group, g, p, on_gpu, True) for sub, st, g, p in parts):
+        return False
+    if prog.palm is not None:
+        prog.palm(None, group, None, None, None)
+    for sub, st, g, p in parts:
+        if not _run(opt, sub, st, group, g, p, on_gpu, False):
+            raise RuntimeError("a routed sub-chain refused to run after it had been accepted")
+    return True
+
+
+def _run(opt, prog, states, group, grads, params, on_gpu, check_only) -> bool:
     if prog.kind in ("soap", "psgd"):
-        return _run_precond(opt, prog, states, group, grads, params, on_gpu)
+        return _run_precond(opt, prog, states, group, grads, params, on_gpu, check_only)
     if not on_gpu:
         return False
     if not all(_eligible(p) for p in params):
@@ -283,6 +369,18 @@ def try_run(opt, states, group, grads, params) -> bool:
     sdt = states[0][key0].dtype
     if any(st[key0].dtype != sdt for st in states):
         return False
+    post = prog.post
+    if post is not None:  # schedule-free: point-wise, but its caution rescaling would need a second pass
+        if group["caution"] or plan is not None or ecc_mode or pecc_mode or not _state_ready(post, states, False):
+            return False
+        if any(st[post._val_names["z"]].dtype != sdt for st in states):
+            return False
+    if algo == ops.NADAM and group["weight_decay"] != 0 and not group.get("decoupled_weight_decay", False):
+        return False  # L2-style decay enters the moments: left to the PyTorch definition
+    if prog.gclip is not None and plan is not None:
+        return False  # the clip needs the norm of the reduced gradient, which peer kernels never materialise
+    if check_only:
+        return True
 
     if prog.palm is not None:
         prog.palm(None, group, None, None, None)
@@ -292,6 +390,8 @@ def try_run(opt, states, group, grads, params) -> bool:
             _mark_initialized(prog.mars, st)
         if prog.ortho is not None:
             _mark_initialized(prog.ortho, st)
+        if post is not None:
+            _mark_initialized(post, st)
 
     # ---- selection: everything (single process / replicated) or this rank's share (peer data parallelism)
     peer_in, peer_out = {}, {}
@@ -321,7 +421,14 @@ def try_run(opt, states, group, grads, params) -> bool:
         dt_g=ops.dtype_code(grads[0]), dt_s=ops.dtype_code(states[0][key0], ecc_mode),
         dt_p=ops.dtype_code(params[0], pecc_mode), n_state=len(names), algo=algo,
     )  # fmt: skip
-    base.update(_rule_scalars(rule_name, group))
+    base.update(_nadam_scalars(prog, states, group) if algo == ops.NADAM else _rule_scalars(rule_name, group))
+    if prog.gclip is not None:  # F2 pre-pass: per-tensor sums of squares, folded to one value for the global clips
+        mode, whole_group = prog.gclip
+        gsq = ops.sumsq(grads_v)
+        if whole_group:
+            gsq = gsq.double().sum().float().reshape(1)
+            base["g_clip_numel"] = float(sum(g.numel() for g in grads_v))
+        base.update(gsq=gsq, g_clip_mode=mode, g_clip_at=1.0)
     mars_kw = {}
     if prog.mars is not None:
         mkey = prog.mars._val_names["mars_old_grad"]
@@ -340,6 +447,18 @@ def try_run(opt, states, group, grads, params) -> bool:
     if not params_v:
         return True  # this rank owns nothing in this group
 
+    if prog.kind == "elementwise" and post is not None:
+        step = group["step"]
+        if group.get("_sf_step") != step:  # the running weight sum advances once per optimizer step
+            group["weight_sum"] = group.get("weight_sum", 0) + C._sf_weight(group)
+            group["_sf_step"] = step
+        total = group["weight_sum"]
+        ckp1 = C._sf_weight(group) / total if total != 0 else 0
+        z = [_cut(st[post._val_names["z"]], seg) for st, (_, seg) in zip(sub_states, sel)]
+        base.update(b3=ckp1, alpha=utils.get_beta1(group))
+        launch(p=params_v, g=grads_v, s0=s0, s1=s1, s2=z, out_mode=ops.OUT_SCHEDULE_FREE, seed=_seed(opt, group, 0),
+               **base, **epilogue)  # fmt: skip
+        return True
     if prog.kind == "elementwise":
         if not caution:
             launch(p=params_v, pe=pe, g=grads_v, s0=s0, s0e=s0e, s1=s1, s1e=s1e, s2=s2, s2e=s2e, out_mode=ops.OUT_PARAM,
@@ -355,17 +474,16 @@ def try_run(opt, states, group, grads, params) -> bool:
         return True
 
     # ---- orthogonal program: momentum -> Newton–Schulz per shape bucket -> parameter update
-    scratch = _scratch(prog, params_v)
+    # updates live bucket-major (same-shape matrices adjacent), so a bucket is one (B, R, C) tensor and the
+    # iteration writes its result over its own input: no second buffer of the group's size
+    layout, scratch, _ = _bucket_layout(prog, params_v)
     dev = params[0].device
     sq = torch.zeros(len(scratch), dtype=torch.float32, device=dev)  # squared norms, accumulated by the momentum kernel
     launch(g=grads_v, u=scratch, s0=s0, s0e=s0e, s1=s1, s1e=s1e, s2=s2, s2e=s2e, out_mode=ops.OUT_UPDATE, dt_u=ops.F32,
            scale=sq, accum_sumsq=1, seed=_seed(opt, group, 0), **base, **mars_kw, **peer_in)  # fmt: skip
     scale_mode = "scale"
-    buckets = {}
-    for i, u in enumerate(scratch):
-        if u.ndim >= 2:
-            buckets.setdefault((u.shape[0], u[0].numel()), []).append(i)
     final = list(scratch)
+    buckets = [(shape, idx, U) for shape, idx, U, _ in layout if len(shape) >= 2]
     # shape buckets are independent chains of small launches: run them on side streams so they share the GPU
     main = torch.cuda.current_stream(dev)
     streams = prog.workspace.get("streams")
@@ -374,13 +492,13 @@ def try_run(opt, states, group, grads, params) -> bool:
     ready = torch.cuda.Event()
     ready.record(main)
     used = []
-    for k, ((R, Cc), idx) in enumerate(buckets.items()):
+    for k, (shape, idx, U) in enumerate(buckets):
+        R, Cc = shape[0], U[0].numel() // shape[0]
+        U3 = U.view(len(idx), R, Cc)
         if not ops.ns_supported(R, Cc):
-            for i in idx:
-                flat = scratch[i].view(R, Cc)
-                utils.inplace_orthogonal_(flat, out=flat, scale_mode=scale_mode)
+            for b in range(len(idx)):
+                utils.inplace_orthogonal_(U3[b], out=U3[b], scale_mode=scale_mode)
             continue
-        out = _bucket_out(prog, (R, Cc, len(idx)), dev)
         sel_idx = prog.workspace.get(("idx", R, Cc, tuple(idx)))
         if sel_idx is None:
             sel_idx = prog.workspace[("idx", R, Cc, tuple(idx))] = torch.tensor(idx, dtype=torch.long, device=dev)
@@ -388,13 +506,15 @@ def try_run(opt, states, group, grads, params) -> bool:
         if side is not main:
             side.wait_event(ready)
             used.append(side)
+        chunk = max(1, _NS_WORKSPACE_BYTES // (R * Cc * 8))  # four bf16 work copies per matrix
         with torch.cuda.stream(side):
-            ops.newton_schulz_batched(
-                [scratch[i].view(R, Cc) for i in idx], utils.NS5_COEFFS, out=out, out_scale=max(1, R / Cc) ** 0.5,
-                seed=_seed(opt, group, 2 + len(final) + R), sumsq=sq.index_select(0, sel_idx),
-            )
-        for b, i in enumerate(idx):
-            final[i] = out[b].view(params_v[i].shape)
+            norms = sq.index_select(0, sel_idx)
+            for c0 in range(0, len(idx), chunk):
+                c1 = min(len(idx), c0 + chunk)
+                ops.newton_schulz_batched(
+                    list(U3[c0:c1].unbind(0)), utils.NS5_COEFFS, out=U3[c0:c1], out_scale=max(1, R / Cc) ** 0.5,
+                    seed=_seed(opt, group, 2 + len(final) + R + c0), sumsq=norms[c0:c1],
+                )
     for side in used:
         main.wait_stream(side)
     if caution:
@@ -425,14 +545,6 @@ def _scratch(prog: _Program, params) -> List[torch.Tensor]:
             off += n
         prog.workspace = {k: v for k, v in prog.workspace.items() if k[0] != "u"}
         prog.workspace[key] = hit
-    return hit
-
-
-def _bucket_out(prog: _Program, key, device) -> torch.Tensor:
-    R, Cc, B = key
-    hit = prog.workspace.get(("ns", key))
-    if hit is None:
-        hit = prog.workspace[("ns", key)] = torch.empty(B, R, Cc, dtype=torch.float32, device=device)
     return hit
 
 
@@ -489,7 +601,7 @@ def _precond_unsupported(opt, prog, group, params) -> bool:
     return False
 
 
-def _run_precond(opt, prog: _Program, states, group, grads, params, on_gpu: bool) -> bool:
+def _run_precond(opt, prog: _Program, states, group, grads, params, on_gpu: bool, check_only: bool = False) -> bool:
     if _precond_unsupported(opt, prog, group, params):
         return False
     if getattr(opt, "_peer", None) is not None and opt._peer.plan_for(group) is not None:
@@ -510,6 +622,8 @@ def _run_precond(opt, prog: _Program, states, group, grads, params, on_gpu: bool
     grads = [g if g.is_contiguous() else g.contiguous() for g in grads]
     if on_gpu and any(g.dtype != grads[0].dtype or g.dtype not in (torch.float32, torch.bfloat16, torch.float16) for g in grads):
         return False
+    if check_only:
+        return True
 
     if prog.palm is not None:
         prog.palm(None, group, None, None, None)

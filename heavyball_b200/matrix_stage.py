@@ -120,7 +120,6 @@ def backend_for(t: Tensor, dims: Sequence[int]):
 
 GRAPH_MAX_BYTES = 256 << 20  # buckets larger than this run their fit / refresh eagerly (they are device-bound anyway)
 use_graphs = True
-_pool = None
 
 
 class Captured:
@@ -137,7 +136,6 @@ class Captured:
         self.failed = False
 
     def __call__(self, fn, key, device):
-        global _pool
         if not use_graphs or device.type != "cuda" or self.failed or torch.cuda.is_current_stream_capturing():
             return fn()
         if key != self.key:
@@ -147,10 +145,8 @@ class Captured:
             return fn()
         if self.graph is None:
             try:
-                if _pool is None:
-                    _pool = torch.cuda.graph_pool_handle()
                 graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, pool=_pool):
+                with torch.cuda.graph(graph):  # own memory pool: it lives exactly as long as this graph
                     fn()
                 self.graph = graph
             except Exception as err:  # noqa: BLE001 - whatever stops capture, the eager sequence is still correct

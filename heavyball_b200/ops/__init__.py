@@ -40,8 +40,9 @@ _load_error: Optional[BaseException] = None
 # storage kinds (mirror of hb::DType)
 F32, BF16, F16, BF16E8, BF16E16, F16E8, F16E16, NONE = range(8)
 # algorithms (mirror of hb::Algo)
-IDENTITY, ADAM, LAPROP, ADOPT, ADEMAMIX, RMSPROP, UNSCALED_ADAM, EXP_AVG, NESTEROV_EMA, HEAVYBALL, NESTEROV_MOM = range(11)
-OUT_PARAM, OUT_UPDATE = 0, 1
+IDENTITY, ADAM, LAPROP, ADOPT, ADEMAMIX, RMSPROP, UNSCALED_ADAM, EXP_AVG, NESTEROV_EMA, HEAVYBALL, NESTEROV_MOM, NADAM = range(12)
+OUT_PARAM, OUT_UPDATE, OUT_SCHEDULE_FREE = 0, 1, 2
+CLIP_NONE, CLIP_L2, CLIP_RMS = 0, 1, 2
 MODE_GRAM, MODE_POLY, MODE_APPLY = 0, 1, 2
 
 CUDA_FLAGS = [
@@ -152,12 +153,12 @@ _EMPTY: List = []
 
 
 def fused_chain(*, p=_EMPTY, pe=_EMPTY, g=_EMPTY, u=_EMPTY, s0=_EMPTY, s0e=_EMPTY, s1=_EMPTY, s1e=_EMPTY, s2=_EMPTY,
-                s2e=_EMPTY, mars=_EMPTY, marse=_EMPTY, scale=None, masked=None, **cfg):  # fmt: skip
+                s2e=_EMPTY, mars=_EMPTY, marse=_EMPTY, scale=None, masked=None, gsq=None, **cfg):  # fmt: skip
     cfg["mars"] = 1 if len(mars) else 0
     launch_counter.count += 1
     load().fused_chain(
         list(p), list(pe), list(g), list(u), list(s0), list(s0e), list(s1), list(s1e), list(s2), list(s2e), list(mars),
-        list(marse), scale, masked, cfg,
+        list(marse), scale, masked, gsq, cfg,
     )  # fmt: skip
 
 

@@ -70,7 +70,7 @@ Table upload(std::vector<hb::TensorMeta>& metas, const at::Device& dev) {
 // use_tensor_scale, count_caution (ints); lr, wd, eps, b1, b2, b3, alpha, mars_a (floats); seed.
 void fused_chain(const TList& p, const TList& pe, const TList& g, const TList& u, const TList& s0, const TList& s0e,
                  const TList& s1, const TList& s1e, const TList& s2, const TList& s2e, const TList& mars,
-                 const TList& marse, const OptT& scale, const OptT& masked, const py::dict& cfg) {
+                 const TList& marse, const OptT& scale, const OptT& masked, const OptT& gsq, const py::dict& cfg) {
   const size_t n = !g.empty() ? g.size() : (!u.empty() ? u.size() : p.size());
   if (n == 0) return;
   const at::Tensor& ref = !g.empty() ? *g[0] : (!u.empty() ? *u[0] : *p[0]);
@@ -104,6 +104,9 @@ void fused_chain(const TList& p, const TList& pe, const TList& g, const TList& u
       TORCH_CHECK(aux->is_cuda() && aux->is_contiguous() && (size_t)aux->numel() >= n && aux->element_size() == 4,
                   "fused_chain: per-tensor scalars need one 4-byte entry per tensor");
     }
+    if (gsq.has_value())
+      TORCH_CHECK(gsq->is_cuda() && gsq->is_contiguous() && gsq->scalar_type() == at::kFloat &&
+                      (gsq->numel() == 1 || (size_t)gsq->numel() >= n), "fused_chain: gsq needs one fp32 entry, or one per tensor");
     if (cfg.contains("g_delta") || cfg.contains("p_delta"))
       TORCH_CHECK(pe.empty() && s0e.empty() && s1e.empty() && s2e.empty() && marse.empty(),
                   "fused_chain: peer sources / destinations cannot be combined with ECC residual buffers");
@@ -116,6 +119,7 @@ void fused_chain(const TList& p, const TList& pe, const TList& g, const TList& u
     m.s2 = ptr_or_null(s2, i); m.s2e = ptr_or_null(s2e, i); m.mars = ptr_or_null(mars, i); m.marse = ptr_or_null(marse, i);
     m.scale = scale.has_value() ? scale->data_ptr<float>() + i : nullptr;
     m.masked = masked.has_value() ? masked->data_ptr<int>() + i : nullptr;
+    m.gsq = gsq.has_value() ? gsq->data_ptr<float>() + (gsq->numel() == 1 ? 0 : (int64_t)i) : nullptr;
     const at::Tensor& any = !g.empty() && g[i].has_value() ? *g[i] : (!u.empty() && u[i].has_value() ? *u[i] : *p[i]);
     m.numel = any.numel();
     for (const TList* l : {&p, &pe, &g, &u, &s0, &s0e, &s1, &s1e, &s2, &s2e, &mars, &marse})
@@ -135,6 +139,7 @@ void fused_chain(const TList& p, const TList& pe, const TList& g, const TList& u
   P.u_is_input = geti("u_is_input"); P.mars = geti("mars"); P.cautious_wd = geti("cautious_wd");
   P.caution_apply = geti("caution_apply"); P.use_tensor_scale = geti("use_tensor_scale");
   P.accum_sumsq = geti("accum_sumsq"); P.u_op = geti("u_op");
+  P.g_clip_mode = geti("g_clip_mode"); P.g_clip_at = getf("g_clip_at"); P.g_clip_numel = getf("g_clip_numel");
   P.lr = getf("lr"); P.wd = getf("wd"); P.eps = getf("eps");
   P.b1 = getf("b1"); P.b2 = getf("b2"); P.b3 = getf("b3"); P.alpha = getf("alpha"); P.mars_a = getf("mars_a");
   P.seed = cfg.contains("seed") ? cfg["seed"].cast<uint64_t>() : 0;

@@ -50,6 +50,12 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
     float n = (float)M.numel;
     cscale *= n / fmaxf(n - (float)(*M.masked), 1.0f);
   }
+  float gclip = 1.0f;
+  if (P.g_clip_mode != kClipNone && M.gsq != nullptr) {
+    float sq = *M.gsq;
+    if (P.g_clip_mode == kClipRms) sq /= (P.g_clip_numel > 0.f ? P.g_clip_numel : (float)M.numel);
+    gclip = P.g_clip_at / fmaxf(sqrtf(sq), fmaxf(P.g_clip_at, 1e-8f));
+  }
   int masked_local = 0;
   float sumsq_local = 0.f;
 
@@ -99,6 +105,10 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
     F4 p = P.out_mode == kOutParam ? load4(M.p, M.pe, P.dt_p, i, nv, vec_ok) : F4{};
     F4 out;
 
+    if (P.g_clip_mode != kClipNone && !P.u_is_input) {  // the clip acts on the update, caution still sees the raw gradient
+#pragma unroll
+      for (int k = 0; k < 4; ++k) u.v[k] *= gclip;
+    }
     if (P.mars) {  // g <- lerp(g, g_prev, a); g_prev <- raw g
       F4 old = load4(M.mars, M.marse, P.dt_s, i, nv, vec_ok);
       F4 raw = u;
@@ -161,6 +171,12 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
           s0.v[k] = s0.v[k] * P.b1 + x;
           r = x + s0.v[k] * P.b1;
         } break;
+        case kNadam: {  // b3 = (1 - mu) / (1 - mu_product), alpha = mu_next / (1 - mu_product mu_next), set on the host
+          s0.v[k] = lerp_to(s0.v[k], x, P.b1);
+          s1.v[k] = lerp_to(s1.v[k], x * x, P.b2);
+          float d = fmaxf(sqrtf(s1.v[k]), P.eps);
+          r = x / d * P.b3 + s0.v[k] / d * P.alpha;
+        } break;
         default:
           r = x;
       }
@@ -176,6 +192,23 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
              P.dt_s == kBF16 ? make_uint4(r0.x >> 16, r0.y >> 16, r0.z >> 16, r0.w >> 16)
                              : draw(P.dt_s, rng, ctr, ctr_hi, (uint32_t)t, 1u));
     if (P.n_state >= 3) store4(M.s2, M.s2e, P.dt_s, i, nv, vec_ok, s2, draw(P.dt_s, rng, ctr, ctr_hi, (uint32_t)t, 2u));
+    if (P.out_mode == kOutScheduleFree) {  // z lives in slot s2 (loaded above), p and z are both written
+      F4 pp = load4(M.p, M.pe, P.dt_p, i, nv, vec_ok);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float uu = out.v[k];
+        if (P.wd != 0.f) {
+          float d = P.wd;
+          if (P.cautious_wd && ((__float_as_uint(pp.v[k]) ^ __float_as_uint(uu)) >> 31)) d = 0.f;
+          uu += pp.v[k] * d;
+        }
+        pp.v[k] = pp.v[k] + (s2.v[k] - pp.v[k]) * P.b3 + uu * (P.lr * (P.alpha * (1.0f - P.b3)) - P.lr);
+        s2.v[k] = s2.v[k] + uu * -P.lr;
+      }
+      store4(M.s2, M.s2e, P.dt_s, i, nv, vec_ok, s2, draw(P.dt_s, rng, ctr, ctr_hi, (uint32_t)t, 2u));
+      store4(M.p, M.pe, P.dt_p, i, nv, vec_ok, pp, draw(P.dt_p, rng, ctr, ctr_hi, (uint32_t)t, 3u));
+      continue;
+    }
 
     if (kCountCaution) {  // phase one of caution: mask, count, park the masked update
 #pragma unroll

@@ -22,6 +22,7 @@ struct TensorMeta {
   void* marse;
   float* scale; // optional per-tensor multiplier applied to the update
   int* masked;  // caution: number of masked elements (written by phase one, read by phase two)
+  const float* gsq;  // gradient clipping: sum of squares the clip factor is derived from (this tensor's, or the group's)
   int64_t numel;
   int32_t vec_ok;  // all buffers of this tensor are aligned for 4-wide access
   int32_t pad;
@@ -31,9 +32,13 @@ constexpr int kMaxPeers = 16;
 
 enum Algo : int {
   kIdentity = 0, kAdam, kLaProp, kAdopt, kAdemamix, kRmsprop, kUnscaledAdam, kExpAvg, kNesterovEma, kHeavyball,
-  kNesterovMom
+  kNesterovMom, kNadam
 };
-enum OutMode : int { kOutParam = 0, kOutUpdate = 1 };
+// kOutScheduleFree: the update moves the averaged iterate: with z in slot s2,
+//   p <- lerp(p, z, b3) + u (lr (alpha (1 - b3)) - lr),  z <- z - lr u     (b3 = c_{k+1}, alpha = beta1)
+enum OutMode : int { kOutParam = 0, kOutUpdate = 1, kOutScheduleFree = 2 };
+// incoming-gradient clip: g <- g * clip_at / max(norm, clip_at, 1e-8), norm = sqrt(gsq) (kClipL2) or sqrt(gsq / n) (kClipRms)
+enum ClipMode : int { kClipNone = 0, kClipL2 = 1, kClipRms = 2 };
 // kUopTrustRegion: 0.9 tanh(x / 1.5) + 0.1 sign(x) log1p(|x| / 1.5), times 1.5, limited to +-2 (PSGD's default update clip)
 enum UpdateOp : int { kUopNone = 0, kUopTrustRegion = 1 };
 
@@ -50,6 +55,9 @@ struct ChainParams {
   int use_tensor_scale;
   int accum_sumsq;   // kOutUpdate: add sum(update^2) of every tensor into its `scale` slot
   int u_op;          // transformation of an incoming update (u_is_input) before anything else: see UpdateOp
+  int g_clip_mode;   // see ClipMode; needs TensorMeta::gsq
+  float g_clip_at;
+  float g_clip_numel;  // kClipRms: element count behind gsq (0 = this tensor's)
   float lr, wd, eps;
   float b1, b2, b3, alpha;  // already debiased / scheduled on the host
   float mars_a;

@@ -2,7 +2,7 @@
 
 Every rank trains the same small model on the same batch, once un-sharded in a single process (the
 oracle, computed by every rank for simplicity) and once wrapped in ``FullyShardedDataParallel`` with
-``use_orig_params=True``; parameters gathered from the sharded run must match the oracle.
+``use_orig_params=True`` (or, with a trailing ``fsdp2`` argument, sharded by ``fully_shard``); parameters gathered from the sharded run must match the oracle.
 """
 
 import os
@@ -39,6 +39,7 @@ def main():
     name, width, depth, steps = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4])
     tol = float(sys.argv[5]) if len(sys.argv) > 5 else 1e-6
     norm = len(sys.argv) > 6 and sys.argv[6] == "norm"
+    fsdp2 = len(sys.argv) > 7 and sys.argv[7] == "fsdp2"
     use_cuda = torch.cuda.is_available() and os.environ.get("HB_TEST_CPU") != "1"
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     if use_cuda:
@@ -61,12 +62,21 @@ def main():
     want = torch.cat([p.detach().flatten() for p in ref.parameters()])
 
     model = make_model(width, depth, norm=norm).to(device)
-    fsdp = FSDP(model, use_orig_params=True, device_id=device if use_cuda else None)
-    torch.manual_seed(7)
-    opt = cls(fsdp.parameters(), lr=1e-2)
-    train(fsdp, opt, steps, x, y)
-    with FSDP.summon_full_params(fsdp):
-        got = torch.cat([p.detach().flatten() for p in fsdp.parameters()])
+    if fsdp2:  # fully_shard: DTensor parameters, the optimizer works on their local rows
+        from heavyball_b200.parallel import fsdp as hb_fsdp
+
+        fsdp = hb_fsdp.shard(model)
+        torch.manual_seed(7)
+        opt = cls(fsdp.parameters(), lr=1e-2)
+        train(fsdp, opt, steps, x, y)
+        got = torch.cat([p.full_tensor().detach().flatten() for p in fsdp.parameters()])
+    else:
+        fsdp = FSDP(model, use_orig_params=True, device_id=device if use_cuda else None)
+        torch.manual_seed(7)
+        opt = cls(fsdp.parameters(), lr=1e-2)
+        train(fsdp, opt, steps, x, y)
+        with FSDP.summon_full_params(fsdp):
+            got = torch.cat([p.detach().flatten() for p in fsdp.parameters()])
     err = (got - want).abs().max().item()
     ok = err <= tol * max(1.0, want.abs().max().item())
     if rank == 0:

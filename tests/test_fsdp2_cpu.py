@@ -43,16 +43,18 @@ def _train(model, opt, steps, x, y):
 def _worker(rank, world, store_path, name, kwargs, steps, tol, result_path):
     dist.init_process_group("gloo", store=dist.FileStore(store_path, world), rank=rank, world_size=world)
     try:
+        kwargs = dict(kwargs)
+        dtype = kwargs.pop("model_dtype", torch.float32)
         torch.manual_seed(1)
-        x, y = torch.randn(16, 7), torch.randn(16, 4)
-        ref = _Net()
+        x, y = torch.randn(16, 7, dtype=dtype), torch.randn(16, 4, dtype=dtype)
+        ref = _Net().to(dtype)
         torch.manual_seed(7)
         _train(ref, getattr(hb, name)(ref.parameters(), **kwargs), steps, x, y)
         want = [p.detach().clone() for p in ref.parameters()]
 
         from torch.distributed.device_mesh import init_device_mesh
 
-        model = fsdp.shard(_Net(), mesh=init_device_mesh("cpu", (world,)))
+        model = fsdp.shard(_Net().to(dtype), mesh=init_device_mesh("cpu", (world,)))
         assert all(fsdp.is_dtensor(p) for p in model.parameters())
         torch.manual_seed(7)
         opt = getattr(hb, name)(model.parameters(), **kwargs)
@@ -60,7 +62,7 @@ def _worker(rank, world, store_path, name, kwargs, steps, tol, result_path):
         assert all(p.grad is None for p in model.parameters())  # zero_grad reaches the DTensor parameters
         worst = 0.0
         for p, w in zip(model.parameters(), want):
-            worst = max(worst, (p.full_tensor() - w).abs().max().item())
+            worst = max(worst, (p.full_tensor().float() - w.float()).abs().max().item())
         # the state of a gathered parameter lives on its owner only, at the full shape
         if opt._needs_gather:
             for proxy, p in opt._local_shards.pairs:
@@ -90,10 +92,13 @@ CASES = [
     ("Muon", {"lr": 1e-2}, 2e-2, 2),
     ("SOAP", {"lr": 1e-2, "precondition_frequency": 2}, 2e-2, 2),
     ("PSGDKron", {"lr": 1e-2}, 2e-2, 2),
+    # bf16 parameters with residuals (param_ecc): the owner of a gathered matrix keeps the residual of the whole matrix
+    ("Muon", {"lr": 1e-2, "ecc": "bf16+8", "param_ecc": "bf16+8", "mars": True, "caution": True,
+              "model_dtype": torch.bfloat16}, 4e-2, 2),
 ]
 
 
-@pytest.mark.parametrize("name,kwargs,tol,world", CASES, ids=[f"{c[0]}-w{c[3]}" for c in CASES])
+@pytest.mark.parametrize("name,kwargs,tol,world", CASES, ids=[f"{c[0]}-w{c[3]}-{i}" for i, c in enumerate(CASES)])
 def test_fully_shard_matches_single_process(name, kwargs, tol, world):
     with tempfile.TemporaryDirectory() as tmp:
         store, result = os.path.join(tmp, "store"), os.path.join(tmp, "result")

@@ -188,6 +188,11 @@ def _state_ready(tr: C.FunctionTransform, states: List[dict], ecc: bool) -> bool
     return True
 
 
+def _state_keys_present(tr: C.FunctionTransform, states: List[dict], ecc: bool) -> bool:
+    keys = [k for layer in tr.layers if not isinstance(layer, C.AccumSlots) for k in layer.keys.values()]
+    return all(k in st and (not ecc or k + "::ecc" in st) for st in states for k in keys)
+
+
 def _eligible(t: torch.Tensor) -> bool:
     return t.is_cuda and t.is_contiguous() and t.dtype in (torch.float32, torch.bfloat16, torch.float16)
 
@@ -345,11 +350,17 @@ def _run(opt, prog, states, group, grads, params, on_gpu, check_only) -> bool:
         return False
     peer = getattr(opt, "_peer", None)
     plan = peer.plan_for(group) if peer is not None else None
-    if plan is not None:  # state is created here: the PyTorch path would see unreduced gradients
-        if not _state_ready(prog.rule, states, False):
-            _materialize_zero_state(prog.rule, states, group, params)
-        if prog.mars is not None and not _state_ready(prog.mars, states, False):
-            _materialize_zero_state(prog.mars, states, group, params)
+    warming = []
+    if plan is not None and not check_only:  # state is created here: the PyTorch path would see unreduced gradients
+        for tr in (prog.rule, prog.mars):
+            if tr is not None and not _state_keys_present(tr, states, bool(ecc_mode)):
+                _materialize_zero_state(tr, states, group, params)
+        # a warm-up step (ADOPT seeds its second moment and makes no update) runs through the same kernel below
+        warming = [layer for layer in prog.rule.layers if isinstance(layer, C.Warmup)
+                   and any(st.get(layer.counter, 0) < len(layer.warmup_fns) for st in states)]  # fmt: skip
+        for layer in warming:
+            for st in states:
+                st[layer.counter] = st.get(layer.counter, 0) + 1
     if not _state_ready(prog.rule, states, bool(ecc_mode)):
         return False
     if prog.mars is not None and not _state_ready(prog.mars, states, bool(ecc_mode)):
@@ -403,7 +414,7 @@ def _run(opt, prog, states, group, grads, params, on_gpu, check_only) -> bool:
         if missing and all(group["params"][j].grad is not None for j in missing):
             raise RuntimeError("peer data parallelism: the step's parameters do not match the partition plan of their group")
         sel = [(pos_to_local[j], seg) for j, seg in plan["sel"] if j in pos_to_local]
-        args = peer.peer_args()
+        args = peer.peer_args(params[0].dtype)
         peer_in = {"g_delta": args["g_delta"], "g_scale": args["g_scale"]}
         peer_out = {"p_delta": args["p_delta"]}
     else:
@@ -443,6 +454,10 @@ def _run(opt, prog, states, group, grads, params, on_gpu, check_only) -> bool:
         lr=group["lr"], wd=_weight_decay(rule_name, group), cautious_wd=int(bool(group.get("cautious_weight_decay", False)))
     )
     caution = bool(group["caution"])
+    if warming:  # seed the second moment from this gradient; moments' first slot and the parameters stay as they are
+        base.update(b1=1.0, b3=1.0)
+        epilogue.update(lr=0.0, wd=0.0)
+        caution = False
     launch = ops.fused_chain
     if not params_v:
         return True  # this rank owns nothing in this group
@@ -467,10 +482,10 @@ def _run(opt, prog, states, group, grads, params, on_gpu, check_only) -> bool:
         scratch = _scratch(prog, params_v)
         masked = torch.zeros(len(params_v), dtype=torch.int32, device=params[0].device)
         launch(g=grads_v, u=scratch, s0=s0, s0e=s0e, s1=s1, s1e=s1e, s2=s2, s2e=s2e, masked=masked, count_caution=1,
-               out_mode=ops.OUT_UPDATE, dt_u=ops.F32, seed=_seed(opt, group, 0), **base, **mars_kw)  # fmt: skip
+               out_mode=ops.OUT_UPDATE, dt_u=ops.F32, seed=_seed(opt, group, 0), **base, **mars_kw, **peer_in)  # fmt: skip
         ops.fused_chain(p=params_v, pe=pe, u=scratch, masked=masked, algo=ops.IDENTITY, u_is_input=1, caution_apply=1,
                         out_mode=ops.OUT_PARAM, dt_u=ops.F32, dt_p=base["dt_p"], dt_g=ops.NONE, dt_s=ops.NONE,
-                        seed=_seed(opt, group, 1), **epilogue)  # fmt: skip
+                        seed=_seed(opt, group, 1), **epilogue, **peer_out)  # fmt: skip
         return True
 
     # ---- orthogonal program: momentum -> Newton–Schulz per shape bucket -> parameter update
@@ -521,10 +536,10 @@ def _run(opt, prog, states, group, grads, params, on_gpu, check_only) -> bool:
         masked = torch.zeros(len(params_v), dtype=torch.int32, device=params[0].device)
         ops.fused_chain(g=grads_v, u=final, masked=masked, algo=ops.IDENTITY, u_is_input=1, count_caution=1,
                         out_mode=ops.OUT_UPDATE, dt_u=ops.F32, dt_g=base["dt_g"], dt_s=ops.NONE, dt_p=ops.NONE,
-                        seed=_seed(opt, group, 1))  # fmt: skip
+                        seed=_seed(opt, group, 1), **peer_in)  # fmt: skip
         ops.fused_chain(p=params_v, pe=pe, u=final, masked=masked, algo=ops.IDENTITY, u_is_input=1, caution_apply=1,
                         out_mode=ops.OUT_PARAM, dt_u=ops.F32, dt_p=base["dt_p"], dt_g=ops.NONE, dt_s=ops.NONE,
-                        seed=_seed(opt, group, 3), **epilogue)  # fmt: skip
+                        seed=_seed(opt, group, 3), **epilogue, **peer_out)  # fmt: skip
     else:
         ops.fused_chain(p=params_v, pe=pe, u=final, algo=ops.IDENTITY, u_is_input=1, out_mode=ops.OUT_PARAM, dt_u=ops.F32,
                         dt_p=base["dt_p"], dt_g=ops.NONE, dt_s=ops.NONE, seed=_seed(opt, group, 3), **epilogue,
@@ -586,11 +601,26 @@ def _group_key(group):
     return id(group)
 
 
+def _prime_owned_state(opt, peer, plan, states, group, grads, params):
+    """First step of a group whose second-order state is partitioned over the ranks of a data-parallel job.  That state
+    is initialised from the gradient (eigenbases of its outer products, the scale of the Kronecker factors), so this one
+    step averages the group's gradients with a collective and runs the PyTorch definitions on every rank; afterwards
+    the parameters are made identical again and every rank keeps only the state of the matrices it owns."""
+    peer.average_gradients(group)
+    C.chain(states, group, grads, params, *opt.fns)
+    peer.broadcast_parameters(group)
+    owned = {j for j, _ in plan["sel"]}
+    for j, p in enumerate(group["params"]):
+        if j not in owned:
+            opt.state.pop(p, None)
+    plan["primed"] = True
+
+
 def _precond_unsupported(opt, prog, group, params) -> bool:
     """Options the staged programs do not cover (the PyTorch definitions handle them)."""
     if group.get("storage_dtype", "float32") != "float32" or group.get("precond_grad_accum", False):
         return True
-    if getattr(opt, "hessian_approx", False) or group.get("sqrt", False) or group.get("param_ecc"):
+    if getattr(opt, "hessian_approx", False) or group.get("sqrt", False) or group.get("param_ecc") or group.get("split", False):
         return True
     if prog.kind == "soap" and group.get("ecc"):
         return True
@@ -604,8 +634,28 @@ def _precond_unsupported(opt, prog, group, params) -> bool:
 def _run_precond(opt, prog: _Program, states, group, grads, params, on_gpu: bool, check_only: bool = False) -> bool:
     if _precond_unsupported(opt, prog, group, params):
         return False
-    if getattr(opt, "_peer", None) is not None and opt._peer.plan_for(group) is not None:
-        return False
+    peer = getattr(opt, "_peer", None)
+    plan = peer.plan_for(group) if peer is not None else None
+    peer_in, peer_out = {}, {}
+    if plan is not None:
+        if check_only or not on_gpu:
+            return False
+        if not plan["primed"]:
+            _prime_owned_state(opt, peer, plan, states, group, grads, params)
+            return True
+        # this rank's matrices only: it reduces their gradients on load, runs their matrix stage, and stores the new
+        # values into every rank's parameter slab
+        pos_of = {p.data_ptr(): j for j, p in enumerate(group["params"])}
+        owned = {j for j, _ in plan["sel"]}
+        keep = [i for i, p in enumerate(params) if pos_of.get(p.data_ptr()) in owned]
+        for i in keep:
+            peer.validate(group["params"][pos_of[params[i].data_ptr()]], None, params[i], grads[i])
+        states, grads, params = ([xs[i] for i in keep] for xs in (states, grads, params))
+        if not params:
+            return True
+        args = peer.peer_args(params[0].dtype)
+        peer_in = {"g_delta": args["g_delta"], "g_scale": args["g_scale"]}
+        peer_out = {"p_delta": args["p_delta"]}
     stage = prog.stage
     ecc_mode = group.get("ecc")
     if not _state_ready(stage, states, False):
@@ -649,7 +699,7 @@ def _run_precond(opt, prog: _Program, states, group, grads, params, on_gpu: bool
                 kw["dt_s"] = ops.dtype_code(states[0][mkey], ecc_mode)
             kw.update(mars=[st[mkey] for st in states], marse=[st[mkey + "::ecc"] for st in states] if ecc_mode else [],
                       mars_a=-gamma * beta1 / (1 - beta1))  # fmt: skip
-        ops.fused_chain(g=grads, u=u_views, **kw)
+        ops.fused_chain(g=grads, u=u_views, **kw, **peer_in)
     else:
         upd = [g.float().clone() for g in grads]
         for tr in (prog.mars, prog.rule):
@@ -711,13 +761,14 @@ def _run_precond(opt, prog: _Program, states, group, grads, params, on_gpu: bool
         if caution:
             ref = fused_caution_ref if fused_caution_ref is not None else grads
             masked = torch.zeros(len(params), dtype=torch.int32, device=params[0].device)
+            ref_in = peer_in if ref is grads else {}  # gradients are reduced over the ranks on load, local buffers are not
             ops.fused_chain(g=ref, u=out_views, masked=masked, count_caution=1, out_mode=ops.OUT_UPDATE, dt_g=ops.dtype_code(ref[0]),
-                            dt_p=ops.NONE, u_op=prog.u_op, seed=_seed(opt, group, 2), **common)  # fmt: skip
+                            dt_p=ops.NONE, u_op=prog.u_op, seed=_seed(opt, group, 2), **common, **ref_in)  # fmt: skip
             ops.fused_chain(p=params, u=out_views, masked=masked, caution_apply=1, out_mode=ops.OUT_PARAM, dt_g=ops.NONE,
-                            dt_p=ops.dtype_code(params[0]), seed=_seed(opt, group, 3), **common, **epilogue)  # fmt: skip
+                            dt_p=ops.dtype_code(params[0]), seed=_seed(opt, group, 3), **common, **epilogue, **peer_out)  # fmt: skip
         else:
             ops.fused_chain(p=params, u=out_views, out_mode=ops.OUT_PARAM, dt_g=ops.NONE, dt_p=ops.dtype_code(params[0]),
-                            u_op=prog.u_op, seed=_seed(opt, group, 3), **common, **epilogue)  # fmt: skip
+                            u_op=prog.u_op, seed=_seed(opt, group, 3), **common, **epilogue, **peer_out)  # fmt: skip
     else:
         final = [o.clone().view(p.shape) for o, p in zip(out_views, params)]
         if prog.u_op:

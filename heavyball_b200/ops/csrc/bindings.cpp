@@ -107,9 +107,6 @@ void fused_chain(const TList& p, const TList& pe, const TList& g, const TList& u
     if (gsq.has_value())
       TORCH_CHECK(gsq->is_cuda() && gsq->is_contiguous() && gsq->scalar_type() == at::kFloat &&
                       (gsq->numel() == 1 || (size_t)gsq->numel() >= n), "fused_chain: gsq needs one fp32 entry, or one per tensor");
-    if (cfg.contains("g_delta") || cfg.contains("p_delta"))
-      TORCH_CHECK(pe.empty() && s0e.empty() && s1e.empty() && s2e.empty() && marse.empty(),
-                  "fused_chain: peer sources / destinations cannot be combined with ECC residual buffers");
   }
   std::vector<hb::TensorMeta> metas(n);
   for (size_t i = 0; i < n; ++i) {

@@ -193,6 +193,7 @@ __device__ inline void store4(void* p, void* c, int dt, int64_t i, int n_valid, 
     corr[k] = ecc_residual(x.v[k], h[k], bf, smax, u32_to_unit(rr[k]));
   }
   pack_h4((uint16_t*)p + i, n_valid, fast, h);
+  if (c == nullptr) return;  // primary-only copy (a peer's replica of a parameter whose residual lives with its owner)
   if (ecc_wide(dt)) {
     uint16_t w[4];
 #pragma unroll

@@ -238,8 +238,8 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
     }
     const uint4 prnd = draw(P.dt_p, rng, ctr, ctr_hi, (uint32_t)t, 3u);
     if (P.n_dst > 0) {  // single writer per element: every replica receives bit-identical parameters
-      for (int r = 0; r < P.n_dst; ++r)
-        store4((char*)M.p + P.p_delta[r], nullptr, P.dt_p, i, nv, vec_ok, p, prnd);
+      for (int r = 0; r < P.n_dst; ++r)  // the residual of an error-corrected parameter stays with this rank (its only reader)
+        store4((char*)M.p + P.p_delta[r], P.p_delta[r] == 0 ? M.pe : nullptr, P.dt_p, i, nv, vec_ok, p, prnd);
     } else {
       store4(M.p, M.pe, P.dt_p, i, nv, vec_ok, p, prnd);
     }

@@ -87,18 +87,12 @@ class PeerContext:
         if not params:
             raise ValueError("model has no trainable parameters")
         self.device = params[0].device
-        self.dtype = params[0].dtype
-        if any(p.dtype != self.dtype or p.device != self.device for p in params):
-            raise ValueError("peer data parallelism needs all parameters on one device with one dtype")
+        if any(p.device != self.device for p in params):
+            raise ValueError("peer data parallelism needs all parameters on one device")
         self.params = params
 
-        # ---- slab layout: 16-element aligned segments, identical on every rank
-        self.offsets: Dict[int, int] = {}
-        total = 0
-        for p in params:
-            self.offsets[id(p)] = total
-            total += (p.numel() + 15) // 16 * 16
-        self.total = total
+        # ---- slab layout: one parameter slab and one gradient slab per dtype (error-corrected parameters are 16-bit next
+        # to fp32 ones), 16-element aligned segments, identical on every rank
         import warnings
 
         with warnings.catch_warnings():
@@ -107,46 +101,65 @@ class PeerContext:
                 symm_mem.enable_symm_mem_for_group(self.group.group_name)
             except Exception:  # noqa: BLE001
                 pass
-        self.P = symm_mem.empty(total, dtype=self.dtype, device=self.device)
-        self.G = symm_mem.empty(total, dtype=self.dtype, device=self.device)
+        self.offsets: Dict[int, int] = {}
+        self.slabs: Dict[torch.dtype, dict] = {}
+        totals: Dict[torch.dtype, int] = {}
+        for p in params:
+            self.offsets[id(p)] = totals.get(p.dtype, 0)
+            totals[p.dtype] = self.offsets[id(p)] + (p.numel() + 15) // 16 * 16
         self.flags = symm_mem.empty(4 * ops.load().MAX_WORLD, dtype=torch.int32, device=self.device)
-        self.P.zero_()
-        self.G.zero_()
         self.flags.zero_()
-        self._hdl = [symm_mem.rendezvous(t, self.group) for t in (self.P, self.G, self.flags)]
-        self.p_ptrs, self.g_ptrs, self.f_ptrs = (list(h.buffer_ptrs) for h in self._hdl)
-        self.p_delta = [ptr - self.p_ptrs[self.rank] for ptr in self.p_ptrs]
-        self.g_delta = [ptr - self.g_ptrs[self.rank] for ptr in self.g_ptrs]
+        self._hdl = [symm_mem.rendezvous(self.flags, self.group)]
+        self.f_ptrs = list(self._hdl[0].buffer_ptrs)
+        for dtype in sorted(totals, key=str):  # same creation order on every rank
+            P = symm_mem.empty(totals[dtype], dtype=dtype, device=self.device)
+            G = symm_mem.empty(totals[dtype], dtype=dtype, device=self.device)
+            P.zero_()
+            G.zero_()
+            hp, hg = symm_mem.rendezvous(P, self.group), symm_mem.rendezvous(G, self.group)
+            self._hdl += [hp, hg]
+            p_ptrs, g_ptrs = list(hp.buffer_ptrs), list(hg.buffer_ptrs)
+            self.slabs[dtype] = {
+                "P": P, "G": G,
+                "p_delta": [ptr - p_ptrs[self.rank] for ptr in p_ptrs],
+                "g_delta": [ptr - g_ptrs[self.rank] for ptr in g_ptrs],
+            }  # fmt: skip
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
 
         with torch.no_grad():
             for p in params:
-                view = self.P[self.offsets[id(p)] : self.offsets[id(p)] + p.numel()].view(p.shape)
+                P = self.slabs[p.dtype]["P"]
+                view = P[self.offsets[id(p)] : self.offsets[id(p)] + p.numel()].view(p.shape)
                 view.copy_(p.data)
                 p.data = view
-            dist.broadcast(self.P, src=dist.get_global_rank(self.group, 0), group=self.group)
+            for slab in self.slabs.values():
+                dist.broadcast(slab["P"], src=dist.get_global_rank(self.group, 0), group=self.group)
         self._attach_grads()
 
         # ---- which parameters are handled by peer kernels, which by the all-reduce fallback
         self.plans: Dict[int, dict] = {}
-        self.fallback_ranges: List[Tuple[int, int]] = []
+        self.fallback_ranges: List[Tuple[torch.dtype, int, int]] = []
         self._optimizers = list(_inner_optimizers(optimizer))
         self.consolidations = 0
         self.stale_state = False  # True between an optimizer step and the next consolidate_state()
         for opt in self._optimizers:
             prog = lowering._program(opt) if hasattr(opt, "_lowered") else None
-            supported = prog is not None and opt.__class__.__name__ != "ADOPT"
+            kind = None if prog is None else prog.kind
             for g in getattr(opt, "param_groups", []):
-                if g.get("ecc") or g.get("param_ecc") or g.get("caution"):
-                    supported_here = False
-                else:
-                    supported_here = supported and all(id(p) in self.offsets for p in g["params"])
-                if supported_here:
-                    self.plans[id(g)] = self._plan_group(g, prog.kind)
+                ok = kind in ("elementwise", "orthogonal", "soap", "psgd") and all(id(p) in self.offsets for p in g["params"])
+                if ok and (prog.gclip is not None or prog.post is not None):
+                    ok = False  # need the norm of the reduced gradient / a second parameter-sized state written everywhere
+                if ok and kind in ("soap", "psgd") and lowering._precond_unsupported(opt, prog, g, g["params"]):
+                    ok = False
+                if ok:
+                    # a caution mask is counted per tensor, and a matrix stage needs its whole matrix: whole-tensor
+                    # ownership; everything else is cut by element
+                    whole = kind != "elementwise" or bool(g.get("caution"))
+                    self.plans[id(g)] = self._plan_group(g, kind, whole)
                 else:
                     for p in g["params"]:
                         if id(p) in self.offsets:
-                            self.fallback_ranges.append((self.offsets[id(p)], p.numel()))
+                            self.fallback_ranges.append((p.dtype, self.offsets[id(p)], p.numel()))
             if hasattr(opt, "consume_grad"):
                 opt.consume_grad = False  # gradients live in the slab for the whole run
             opt._peer = self
@@ -158,17 +171,17 @@ class PeerContext:
     def _attach_grads(self):
         for p in self.params:
             off = self.offsets[id(p)]
-            p.grad = self.G[off : off + p.numel()].view(p.shape)
+            p.grad = self.slabs[p.dtype]["G"][off : off + p.numel()].view(p.shape)
 
     def _check_grads_in_slab(self):
         """Backward must have accumulated into the slab views.  A gradient that was set to ``None`` and re-created by
         autograd lives elsewhere; publishing the (zero) slab for it would silently drop that gradient."""
-        lo, es = self.G.data_ptr(), self.G.element_size()
         for p in self.params:
             g = p.grad
             if g is None:
                 continue  # parameter unused in this step: its slab range is zero
-            if g.dtype != self.dtype or g.data_ptr() != lo + self.offsets[id(p)] * es:
+            G = self.slabs[p.dtype]["G"]
+            if g.dtype != p.dtype or g.data_ptr() != G.data_ptr() + self.offsets[id(p)] * G.element_size():
                 raise RuntimeError(
                     "peer data parallelism: a parameter's .grad is no longer the symmetric-slab view (it was set to "
                     "None and re-created, cast or replaced).  Use `optimizer.zero_grad()` / `model.zero_grad()` of the "
@@ -177,28 +190,30 @@ class PeerContext:
 
     @staticmethod
     def _coalesce(ranges):
+        """Merges ``(dtype, offset, length)`` ranges of one slab that touch (up to the alignment padding between them)."""
         out = []
-        for off, n in sorted(ranges):
-            if out and out[-1][0] + out[-1][1] + 15 >= off:
-                out[-1] = (out[-1][0], off + n - out[-1][0])
+        for dtype, off, n in sorted(ranges, key=lambda r: (str(r[0]), r[1])):
+            if out and out[-1][0] == dtype and out[-1][1] + out[-1][2] + 15 >= off:
+                out[-1] = (dtype, out[-1][1], off + n - out[-1][1])
             else:
-                out.append((off, n))
+                out.append((dtype, off, n))
         return out
 
-    def _plan_group(self, group, kind):
+    def _plan_group(self, group, kind, whole):
         ps = group["params"]
-        if kind == "orthogonal":  # whole tensors, balanced by matrix-stage cost
+        if whole:  # whole tensors, balanced by matrix-stage cost (element count for element-wise chains)
             loads, owned = [0.0] * self.world, []
             order = sorted(range(len(ps)), key=lambda i: -ps[i].numel())
             owner_of = {}
             for i in order:
                 p = ps[i]
-                cost = p.numel() * (min(p.shape[0], p[0].numel()) if p.ndim >= 2 else 1)
+                side = min(p.shape[0], p[0].numel()) if (p.ndim >= 2 and kind != "elementwise") else 1
+                cost = p.numel() * side
                 r = min(range(self.world), key=loads.__getitem__)
                 loads[r] += cost
                 owner_of[i] = r
             owned = [(i, None) for i in range(len(ps)) if owner_of[i] == self.rank]
-            return {"kind": kind, "sel": owned}
+            return {"kind": kind, "sel": owned, "owner_of": owner_of, "primed": False}
         # flat element partition
         starts, total = [], 0
         for p in ps:
@@ -210,9 +225,10 @@ class PeerContext:
         for i, p in enumerate(ps):
             a = max(lo, starts[i]) - starts[i]
             b = min(hi, starts[i] + p.numel()) - starts[i]
-            # keep segment starts 16-byte aligned relative to the tensor: boundaries move down to a multiple of 8
-            a = a // 8 * 8 if a > 0 else 0
-            b = b // 8 * 8 if b < p.numel() else p.numel()
+            # keep segment starts 16-byte aligned relative to the tensor for every buffer down to the one-byte residuals
+            # of error-corrected state: boundaries move down to a multiple of 16 elements
+            a = a // 16 * 16 if a > 0 else 0
+            b = b // 16 * 16 if b < p.numel() else p.numel()
             if b > a:
                 sel.append((i, (a, b)))
         return {"kind": kind, "sel": sel}
@@ -230,14 +246,15 @@ class PeerContext:
         self.stale_state = True
         self._check_grads_in_slab()
         self._barrier(0)
-        for off, n in self.fallback_ranges:
-            dist.all_reduce(self.G[off : off + n], op=dist.ReduceOp.AVG, group=self.group)
+        for dtype, off, n in self.fallback_ranges:
+            dist.all_reduce(self.slabs[dtype]["G"][off : off + n], op=dist.ReduceOp.AVG, group=self.group)
 
     def end_step(self):
         """After the last optimizer kernel: wait until every peer has finished reading this rank's
         gradients and writing this rank's parameters, then clear the gradient slab."""
         self._barrier(1)
-        self.G.zero_()
+        for slab in self.slabs.values():
+            slab["G"].zero_()
         self._attach_grads()
 
     def consolidate_state(self):
@@ -250,23 +267,40 @@ class PeerContext:
         complete state (and a checkpoint written by one rank resumes correctly under any world size)."""
         self.consolidations += 1
         self.stale_state = False
+        pieces = []  # (tensor, owned ranges): everything this rank must contribute / receive
         for opt in self._optimizers:
             for group in getattr(opt, "param_groups", []):
                 plan = self.plans.get(id(group))
                 if plan is None:
                     continue  # fallback groups are updated on every rank already
+                if plan["kind"] in ("soap", "psgd"):
+                    continue  # preconditioner state exists on the owner only (as under sharded training)
                 owned = {}
                 for i, rng in plan["sel"]:
                     owned.setdefault(i, []).append(rng)
                 for i, p in enumerate(group["params"]):
                     for t in self._state_tensors(opt, p):
-                        flat = t.view(-1)
-                        scratch = torch.zeros_like(flat)
-                        for rng in owned.get(i, []):
-                            a, b = (0, flat.numel()) if rng is None else rng
-                            scratch[a:b] = flat[a:b]
-                        dist.all_reduce(scratch, group=self.group)
-                        flat.copy_(scratch)
+                        pieces.append((t, owned.get(i, [])))
+        by_dtype = {}
+        for t, ranges in pieces:
+            by_dtype.setdefault(t.dtype, []).append((t, ranges))
+        for dtype, items in by_dtype.items():  # one collective per dtype instead of one per state tensor
+            flat = torch.zeros(sum(t.numel() for t, _ in items), dtype=dtype, device=self.device)
+            off = 0
+            for t, ranges in items:
+                src = t.reshape(-1)
+                for rng in ranges:
+                    a, b = (0, src.numel()) if rng is None else rng
+                    flat[off + a : off + b] = src[a:b]
+                off += t.numel()
+            wire = flat if dtype != torch.bfloat16 else flat.float()  # exact: every element has one non-zero contributor
+            dist.all_reduce(wire, group=self.group)
+            if wire is not flat:
+                flat.copy_(wire)
+            off = 0
+            for t, _ in items:
+                t.reshape(-1).copy_(flat[off : off + t.numel()])
+                off += t.numel()
 
     @staticmethod
     def _state_tensors(opt, p):
@@ -278,7 +312,9 @@ class PeerContext:
                 stack.extend(node.values())
             elif isinstance(node, (list, tuple)):
                 stack.extend(node)
-            elif isinstance(node, torch.Tensor) and node.numel() == p.numel() and node.numel() > 1 and node.is_floating_point():
+            elif isinstance(node, torch.Tensor) and node.numel() == p.numel() and node.numel() > 1 and (
+                node.is_floating_point() or node.dtype in (torch.int8, torch.int16)
+            ):  # moments, momentum buffers, and the integer residuals of error-corrected state
                 found.append(node)
         return found
 
@@ -292,22 +328,39 @@ class PeerContext:
     def plan_for(self, group) -> Optional[dict]:
         return self.plans.get(id(group))
 
+    def group_ranges(self, group):
+        return self._coalesce([(p.dtype, self.offsets[id(p)], p.numel()) for p in group["params"] if id(p) in self.offsets])
+
+    def average_gradients(self, group):
+        """Plain collective average of one group's gradient ranges (used for the one step that creates second-order
+        state from the reduced gradient with the PyTorch definitions)."""
+        for dtype, off, n in self.group_ranges(group):
+            dist.all_reduce(self.slabs[dtype]["G"][off : off + n], op=dist.ReduceOp.AVG, group=self.group)
+
+    def broadcast_parameters(self, group, src: int = 0):
+        for dtype, off, n in self.group_ranges(group):
+            dist.broadcast(self.slabs[dtype]["P"][off : off + n], src=dist.get_global_rank(self.group, src), group=self.group)
+
     def validate(self, param, seg, p_view, g_view):
         """Checks, on the host and before any launch, that the slices handed to a peer kernel are the slab views
         this context created (same dtype, inside the slab, at the parameter's slab offset plus the slice start)."""
         off = self.offsets.get(id(param))
         if off is None:
             raise RuntimeError("peer data parallelism: parameter is not part of the wrapped model")
-        es = self.P.element_size()
+        slabs = self.slabs.get(param.dtype)
+        if slabs is None:
+            raise RuntimeError(f"peer data parallelism: no symmetric slab holds {param.dtype} parameters (dtype changed after wrapping?)")
         start = 0 if seg is None else seg[0]
-        for what, view, slab in (("parameter", p_view, self.P), ("gradient", g_view, self.G)):
+        for what, view, slab in (("parameter", p_view, slabs["P"]), ("gradient", g_view, slabs["G"])):
+            es = slab.element_size()
             check_slab_view(
                 what, view.data_ptr(), view.numel() * view.element_size(), view.dtype, slab.data_ptr(),
                 slab.numel() * es, slab.dtype, (off + start) * es,
             )  # fmt: skip
 
-    def peer_args(self):
-        return {"g_delta": self.g_delta, "g_scale": 1.0 / self.world, "p_delta": self.p_delta}
+    def peer_args(self, dtype):
+        slab = self.slabs[dtype]
+        return {"g_delta": slab["g_delta"], "g_scale": 1.0 / self.world, "p_delta": slab["p_delta"]}
 
 
 class _PeerModule(torch.nn.Module):

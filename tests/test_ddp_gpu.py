@@ -50,3 +50,18 @@ def test_fully_shard_matches_single_process(name, width, tol):
         capture_output=True, text=True, timeout=600, env=env,
     )  # fmt: skip
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_data_parallel_covers_flags_and_second_order_chains():
+    """caution, error-corrected state and parameters, ADOPT's warm-up, and owner-partitioned PSGD / SOAP state all run
+    through the peer kernels (no collective fallback) with bit-identical replicas."""
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ddp_variants_worker.py")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    proc = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+         "--master-port", "29547", worker],
+        capture_output=True, text=True, timeout=900, env=env,
+    )  # fmt: skip
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert proc.stdout.count("ok=True") == 5, proc.stdout[-2000:]

@@ -511,40 +511,48 @@ class SplitOpt(utils.StatefulOptimizer):
             {'params': matrices, 'optimizer': Muon, 'lr': 0.02},
             {'params': vectors, 'optimizer': AdamW, 'lr': 0.001},
         ])
+
+    Every spec is ``{"params": ..., "optimizer": class, **constructor arguments}``; specs without parameters are
+    dropped.  The checkpoint is ``{"optimizers": [state_dict of each member, in order]}``.
     """
 
     def __init__(self, specs):
-        self.optimizers, everything = [], []
+        members, covered = [], []
         for spec in specs:
-            spec = dict(spec)
-            params = list(spec.pop("params"))
-            if params:
-                self.optimizers.append(spec.pop("optimizer")(params, **spec))
-                everything.extend(params)
-        if not self.optimizers:
+            options = {k: v for k, v in spec.items() if k not in ("params", "optimizer")}
+            own = list(spec["params"])
+            if own:
+                members.append(spec["optimizer"](own, **options))
+                covered += own
+        if not members:
             raise ValueError("No optimizers created")
-        super().__init__(everything, {"multi_tensor": True})
+        self.optimizers = members
+        super().__init__(covered, {"multi_tensor": True})
 
     def _handle_closure(self, closure):
+        # one evaluation serves every member: the first member owns closure handling (and curvature probes)
         return self.optimizers[0]._handle_closure(closure)
 
     @torch.no_grad()
     def step(self, closure=None):
-        loss = self._handle_closure(closure) if closure else None
-        for opt in self.optimizers:
-            opt.step()
+        loss = None if closure is None else self._handle_closure(closure)
+        for member in self.optimizers:
+            member.step()
         return loss
 
     def zero_grad(self, set_to_none: bool = True):
-        for opt in self.optimizers:
-            opt.zero_grad(set_to_none=set_to_none)
+        for member in self.optimizers:
+            member.zero_grad(set_to_none=set_to_none)
 
     def state_dict(self):
-        return {"optimizers": [opt.state_dict() for opt in self.optimizers]}
+        return {"optimizers": [member.state_dict() for member in self.optimizers]}
 
     def load_state_dict(self, state_dict):
-        for opt, sd in zip(self.optimizers, state_dict["optimizers"], strict=True):
-            opt.load_state_dict(sd)
+        saved = state_dict["optimizers"]
+        if len(saved) != len(self.optimizers):
+            raise ValueError(f"checkpoint holds {len(saved)} optimizers, this SplitOpt has {len(self.optimizers)}")
+        for member, part in zip(self.optimizers, saved):
+            member.load_state_dict(part)
 
 
 class SAMWrapper(torch.optim.Optimizer):
@@ -556,46 +564,46 @@ class SAMWrapper(torch.optim.Optimizer):
                  ball: float = 0.1):  # fmt: skip
         params = list(params)
         super().__init__(params, {"ball": ball})
-        if isinstance(wrapped_optimizer, type):
-            if not issubclass(wrapped_optimizer, utils.StatefulOptimizer):
-                raise ValueError(f"{wrapped_optimizer.__name__} is not a HeavyBall optimizer")
-            wrapped_optimizer = wrapped_optimizer(params)
-        elif not isinstance(wrapped_optimizer, utils.StatefulOptimizer):
-            raise ValueError(f"{wrapped_optimizer.__class__.__name__} is not a HeavyBall optimizer")
-        self.wrapped_optimizer = wrapped_optimizer
+        kind = wrapped_optimizer if isinstance(wrapped_optimizer, type) else type(wrapped_optimizer)
+        if not issubclass(kind, utils.StatefulOptimizer):
+            raise ValueError(f"{kind.__name__} is not a HeavyBall optimizer")
+        self.wrapped_optimizer = wrapped_optimizer(params) if isinstance(wrapped_optimizer, type) else wrapped_optimizer
 
     @torch.no_grad()
     def step(self, closure=None):
         if closure is None:
             raise ValueError("SAM requires closure")
         with torch.enable_grad():
-            closure()
-        saved = [utils.sam_step(group["params"], group["ball"]) for group in self.param_groups]
-        inner = self.wrapped_optimizer._handle_closure
+            closure()  # gradient at the current point, used for the ascent direction only
+        originals = [(group["params"], utils.sam_step(group["params"], group["ball"])) for group in self.param_groups]
+        inner = self.wrapped_optimizer
+        evaluate = inner._handle_closure
 
-        def restoring_closure(c):
+        def at_ascent_point_then_restore(c):
+            """The wrapped optimizer's closure evaluation happens at the perturbed parameters; they are put back before
+            its update runs."""
             try:
-                return inner(c)
+                return evaluate(c)
             finally:
-                for group, old in zip(self.param_groups, saved):
-                    utils.copy_stochastic_list_(group["params"], old)
+                for live, held in originals:
+                    utils.copy_stochastic_list_(live, held)
 
+        inner._handle_closure = at_ascent_point_then_restore
         try:
-            self.wrapped_optimizer._handle_closure = restoring_closure
-            return self.wrapped_optimizer.step(closure)
+            return inner.step(closure)
         finally:
-            self.wrapped_optimizer._handle_closure = inner
+            inner._handle_closure = evaluate
 
     def zero_grad(self, set_to_none: bool = True):
         self.wrapped_optimizer.zero_grad(set_to_none=set_to_none)
 
     def state_dict(self):
-        return {"wrapped": self.wrapped_optimizer.state_dict(), "ball": [g["ball"] for g in self.param_groups]}
+        return {"wrapped": self.wrapped_optimizer.state_dict(), "ball": [group["ball"] for group in self.param_groups]}
 
     def load_state_dict(self, state_dict):
         self.wrapped_optimizer.load_state_dict(state_dict["wrapped"])
-        for g, b in zip(self.param_groups, state_dict["ball"]):
-            g["ball"] = b
+        for group, ball in zip(self.param_groups, state_dict["ball"]):
+            group["ball"] = ball
 
     def train(self, mode: bool = True):
         self.wrapped_optimizer.train(mode)

@@ -1627,7 +1627,7 @@ class ChainOpt(utils.StatefulOptimizer):
             param_group = shards.localize([param_group])[0]
             self._orig_shapes = {**(self._orig_shapes or {}), **shards.infos}
         super().add_param_group(param_group)
-        if hasattr(self, "mapping"):
+        if getattr(self, "_fns", None) is not None:  # groups added after construction; the constructor does all of its own at once
             self._init_param_ecc_group(self.param_groups[-1])
 
     def zero_grad(self, set_to_none: bool = True):

@@ -86,15 +86,17 @@ def _triu_index(d0: int, d1: int, device) -> Tuple[Tensor, Tensor]:
     return rows, cols
 
 
+def _pack_upper(q: Tensor):
+    """``(shape, packed)``: the row-major upper triangle of a dense factor; vectors (diagonal factors) pass through
+    with ``shape=None``."""
+    if q.dim() < 3:
+        return None, q
+    rows, cols = _triu_index(q.shape[-2], q.shape[-1], q.device)
+    return tuple(q.shape), q[..., rows, cols]
+
+
 def triu_to_line(Q_list: List[Tensor]):
-    out = []
-    for q in Q_list:
-        if q.dim() < 3:
-            out.append((None, q))
-        else:
-            rows, cols = _triu_index(q.shape[-2], q.shape[-1], q.device)
-            out.append((tuple(q.shape), q[..., rows, cols]))
-    return out
+    return [_pack_upper(q) for q in Q_list]
 
 
 def line_to_triu(Q_list):
@@ -135,47 +137,52 @@ class PrecondInitError(ValueError):
     pass
 
 
-def precond_init_scale(scale, scale_scale, scale_power, grad, hessian_vector, vector, scale_max: float = 100):
-    hint = " Set it manually using `precond_init_scale=0.1`"
-    scale_scale = 1 if scale_scale is None else scale_scale
-    automatic = scale is None
-    if not automatic:
-        warn_once("It's recommended to use precond_init_scale=None (default since 1.7.x), which uses advanced heuristics.")
-        if scale_scale != 1:
-            warn_once(
-                "precond_init_scale_scale multiplies the precond_init_scale by a constant factor. "
-                "With a fixed precond_init_scale, you should explicitly fuse it."
-            )
-        if scale_power is not None:
-            warn_once(
-                "precond_init_scale_power is used to compute precond_init_scale ** precond_init_scale_power. "
-                "With a fixed precond_init_scale, you should explicitly fuse it."
-            )
-    elif hessian_vector is None:
-        scale = mean_root(grad, 4) * scale_scale
-    else:
-        scale = divided_root(vector, hessian_vector, 2, 4) * scale_scale
-    if automatic:
-        scale = scale ** (0.5 if scale_power is None else scale_power)
-    if isinstance(scale, Tensor):
-        scale = scale.item()
+_SCALE_HINT = " Set it manually using `precond_init_scale=0.1`"
 
-    if np.isfinite(scale):
-        if scale <= scale_max:
-            return scale
-        warn_once(f"The computed precond_init_scale {scale} is outside of the expected range.{hint}")
-    if not automatic:
-        raise PrecondInitError("The manually set precond_init_scale is not finite")
-    for x in (grad, hessian_vector, vector):
-        if x is None:
+
+def _explain_bad_scale(tensors):
+    """Raises with the reason an automatic initial scale came out unusable, if the inputs show one."""
+    for t in tensors:
+        if t is None:
             continue
-        if torch.allclose(x, torch.zeros_like(x)):
-            raise PrecondInitError(f"Grad or HVP is all 0s, causing NaNs in precond_init_scale computation.{hint}")
-        if not torch.isfinite(x).all().item():
+        if torch.allclose(t, torch.zeros_like(t)):
+            raise PrecondInitError(f"Grad or HVP is all 0s, causing NaNs in precond_init_scale computation.{_SCALE_HINT}")
+        if not bool(torch.isfinite(t).all()):
             raise PrecondInitError("Grad or HVP is not finite")
-    if np.isfinite(scale):
-        return scale
-    raise PrecondInitError(f"Computed precond_init_scale is not finite.{hint}")
+
+
+def precond_init_scale(scale, scale_scale, scale_power, grad, hessian_vector, vector, scale_max: float = 100):
+    """Initial scale of the preconditioner.  A user-given ``scale`` is taken as it is (with advice against combining it
+    with the multiplier / exponent knobs).  Otherwise it is estimated in log space: from the fourth-moment root of the
+    gradient, or, when a probe / Hessian-vector pair is at hand, from their ratio; multiplied by ``scale_scale`` and
+    raised to ``scale_power`` (default 1/2)."""
+    multiplier = 1 if scale_scale is None else scale_scale
+    given = scale is not None
+    if given:
+        warn_once("It's recommended to use precond_init_scale=None (default since 1.7.x), which uses advanced heuristics.")
+        for knob, text in (
+            (multiplier != 1, "precond_init_scale_scale multiplies the precond_init_scale by a constant factor. "),
+            (scale_power is not None, "precond_init_scale_power is used to compute precond_init_scale ** precond_init_scale_power. "),
+        ):
+            if knob:
+                warn_once(text + "With a fixed precond_init_scale, you should explicitly fuse it.")
+        value = scale
+    else:
+        root = mean_root(grad, 4) if hessian_vector is None else divided_root(vector, hessian_vector, 2, 4)
+        value = (root * multiplier) ** (0.5 if scale_power is None else scale_power)
+    value = value.item() if isinstance(value, Tensor) else value
+
+    finite = bool(np.isfinite(value))
+    if finite and value <= scale_max:
+        return value
+    if finite:
+        warn_once(f"The computed precond_init_scale {value} is outside of the expected range.{_SCALE_HINT}")
+    if given:
+        raise PrecondInitError("The manually set precond_init_scale is not finite")
+    _explain_bad_scale((grad, hessian_vector, vector))
+    if finite:
+        return value
+    raise PrecondInitError(f"Computed precond_init_scale is not finite.{_SCALE_HINT}")
 
 
 def _max_idx(x):
@@ -222,12 +229,13 @@ def init_Q_exprs(grad, scale, scale_scale, scale_power, max_size, min_ndim_trian
 
 
 def init_lra(grad, param_count, scale, scale_scale, scale_power, rank, hessian_vector, vector, dtype=None, eps: float = 10):
-    scale = precond_init_scale(scale, scale_scale, scale_power, grad, hessian_vector, vector)
-    uv = (param_count * (rank + eps)) ** -0.5
-    U = torch.randn((*grad.shape, rank), dtype=dtype, device=grad.device) * uv
-    V = torch.randn((*grad.shape, rank), dtype=dtype, device=grad.device) * uv
-    d = torch.full_like(grad, scale, dtype=dtype, device=grad.device)
-    return U, V, d
+    """Low-rank preconditioner ``(I + U V^T) diag(d)`` at its start: ``d`` constant at the initial scale, ``U`` and ``V``
+    Gaussian with standard deviation ``(param_count (rank + eps))^-1/2``, so ``U V^T`` starts as a small perturbation."""
+    d0 = precond_init_scale(scale, scale_scale, scale_power, grad, hessian_vector, vector)
+    spread = 1.0 / math.sqrt(param_count * (rank + eps))
+    like = dict(dtype=dtype, device=grad.device)
+    U, V = (torch.randn((*grad.shape, rank), **like) * spread for _ in range(2))
+    return U, V, torch.full_like(grad, d0, **like)
 
 
 # ---------------------------------------------------------------------------------------- spectral estimators
@@ -281,13 +289,15 @@ def max_singular_value_cholesky(A: Tensor, max_abs: Optional[Tensor] = None):
 
 
 def max_singular_value(A: Tensor, max_svd: int = 0, use_cholesky: bool = False, power_iter: int = 16) -> Tensor:
+    """Spectral norm estimate.  Dispatch: vectors -> largest magnitude; matrices no larger than ``max_svd`` -> exact;
+    ``use_cholesky`` (or a negative iteration count) -> the top-k sketch; otherwise power iteration."""
     if A.ndim < 2:
         return A.abs().max()
-    if min(A.shape[-2:]) <= max_svd:
+    small = min(A.shape[-2:]) <= max_svd
+    if small:
         return max_singular_value_exact(A)
-    if use_cholesky or power_iter < 0:
-        return max_singular_value_cholesky(A)
-    return max_singular_value_power_iter(A, iterations=power_iter)
+    sketch = use_cholesky or power_iter < 0
+    return max_singular_value_cholesky(A) if sketch else max_singular_value_power_iter(A, iterations=power_iter)
 
 
 def clamped_max_singular_value(A: Tensor, min: float, max_svd: int = 0, use_cholesky: bool = False, power_iter: int = 16):
@@ -435,11 +445,11 @@ def psgd_balance_Q(Q):
 
 
 def _balance_to_triu(Q):
-    if isinstance(Q[0], tuple):
-        psgd_balance_Q([o[1] for o in Q])
-        return line_to_triu(Q)
-    psgd_balance_Q(Q)
-    return Q
+    """Balances the factors in whatever form they are stored (the packed triangle scales like the dense factor) and
+    returns them dense."""
+    packed = isinstance(Q[0], tuple)
+    psgd_balance_Q([entry[1] for entry in Q] if packed else Q)
+    return line_to_triu(Q) if packed else Q
 
 
 def dampen_grad(g: Tensor, damp: float = 1e-9):
@@ -600,12 +610,14 @@ def lra_precond(U: Tensor, V: Tensor, d: Tensor, g: Tensor):
 
 
 def _lra_flatten_and_balance(U, V, d):
-    un = sum(u.square().sum().double() for u in U)
-    vn = sum(v.square().sum().double() for v in V)
-    scale = (un / vn) ** 0.25
-    scale = torch.where(torch.logical_and(torch.isfinite(scale), scale > 1e-6), scale, 1.0)
-    stochastic_multiply_(U, [1 / scale] * len(U))
-    stochastic_multiply_(V, [scale] * len(V))
+    """Equalises ``|U|_F`` and ``|V|_F`` (their product is what matters) by ``(|U| / |V|)^1/2`` and returns the flat
+    ``[numel, rank]`` / ``[numel]`` views of the three parts."""
+    sq = [sum(t.square().sum().double() for t in side) for side in (U, V)]
+    ratio = (sq[0] / sq[1]) ** 0.25
+    usable = torch.isfinite(ratio) & (ratio > 1e-6)
+    ratio = torch.where(usable, ratio, torch.ones_like(ratio))
+    stochastic_multiply_(U, [ratio.reciprocal()] * len(U))
+    stochastic_multiply_(V, [ratio] * len(V))
     return multi_flatten((U, 1), (V, 1), (d, 0))
 
 

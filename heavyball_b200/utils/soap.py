@@ -111,35 +111,39 @@ def get_soap_precond_schedule(precond_scheduler):
 # ---------------------------------------------------------------------------------------- eigen decompositions
 
 
+def _is_device_failure(err: RuntimeError, m: Tensor) -> bool:
+    return m.is_cuda and ("CUDA" in str(err) or "illegal memory access" in str(err))
+
+
 def _stable_symmetric_basis(m: Tensor, max_eps: float = 1e-3, min_eps: float = 1e-30, *, out_device=None, out_dtype=None):
-    """Eigenvectors (descending eigenvalue order) of a symmetric matrix with a retry ladder:
-    device OOM / CUDA solver failure -> CPU; fp32 failure -> fp64; then growing diagonal jitter."""
-    out_device = m.device if out_device is None else out_device
-    out_dtype = m.dtype if out_dtype is None else out_dtype
-    m = promote(m.data)
-    eps = min_eps
+    """Eigenvectors of a symmetric matrix, largest eigenvalue first.  ``eigh`` is retried down a ladder until it succeeds:
+    out of device memory or a device-side solver failure -> the same problem on the CPU; a failure in fp32 -> fp64; a
+    failure in fp64 -> more diagonal jitter (``eps <- eps^(2/3)``, starting at ``min_eps``) up to ``max_eps``."""
+    target = dict(device=m.device if out_device is None else out_device, dtype=m.dtype if out_dtype is None else out_dtype)
+    work, jitter = promote(m.data), min_eps
     while True:
+        to_cpu = False
         try:
-            eye = torch.eye(m.shape[-1], device=m.device, dtype=m.dtype)
-            _, vec = torch.linalg.eigh(m + eps * eye)
-            return torch.flip(vec, [-1]).contiguous().to(device=out_device, dtype=out_dtype)
+            shifted = work + jitter * torch.eye(work.shape[-1], device=work.device, dtype=work.dtype)
+            vectors = torch.linalg.eigh(shifted)[1]
+            return vectors.flip(-1).contiguous().to(**target)
         except torch.OutOfMemoryError:
-            if m.device.type == "cpu":
+            if not work.is_cuda:
                 raise
-            torch.cuda.synchronize(m.device)
-            clean()
-            m = m.cpu()
+            to_cpu = True
         except RuntimeError as err:
-            if m.is_cuda and ("CUDA" in str(err) or "illegal memory access" in str(err)):
-                torch.cuda.synchronize(m.device)
-                clean()
-                m = m.cpu()
-            elif m.dtype != torch.double:
-                m = m.double()
-            elif eps < max_eps:
-                eps = eps ** (2 / 3)
+            if _is_device_failure(err, work):
+                to_cpu = True
+            elif work.dtype != torch.float64:
+                work = work.double()
+            elif jitter < max_eps:
+                jitter = jitter ** (2 / 3)
             else:
                 raise
+        if to_cpu:
+            torch.cuda.synchronize(work.device)
+            clean()
+            work = work.cpu()
         clean()
 
 
@@ -390,14 +394,15 @@ def get_orthogonal_matrix_QR(GG, Q, *exp_avg, exp_avg_sq=None, heavy: bool = Fal
 
 
 def init_psgd_eigenbasis(Q: List[Tensor]):
-    out = []
-    for q in Q:
+    """Per dense factor the eigenbasis of ``Q^T Q`` (``None`` for diagonal factors, whose basis is the identity)."""
+
+    def basis(q):
         if q.ndim < 3:
-            out.append(None)
-            continue
-        q32 = promote(q)
-        out.append(_stable_symmetric_basis(q32.mT @ q32, out_device=q.device, out_dtype=q.dtype))
-    return out
+            return None
+        wide = promote(q)
+        return _stable_symmetric_basis(wide.mT @ wide, out_device=q.device, out_dtype=q.dtype)
+
+    return [basis(q) for q in Q]
 
 
 def get_psgd_eigenbasis(Q: List[Tensor], prev: List[Optional[Tensor]]):

@@ -70,8 +70,8 @@ def _states_of(state, param):
 
 def _mark(st, idx):
     done = st.get("is_initialized")
-    if done is None:
-        done = st["is_initialized"] = set()
+    if not isinstance(done, set):  # absent, or a list written by an older checkpoint
+        done = st["is_initialized"] = set(done or ())
     done.add(idx)
 
 

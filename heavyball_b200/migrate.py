@@ -88,11 +88,18 @@ def _detect_version(sd: Dict[str, Any]) -> int:
 
 
 def _first_tensor_meta(entry: Dict[str, Any]) -> Tuple[Tuple[int, ...], torch.dtype]:
+    """Shape and dtype for a placeholder parameter: taken from the first floating-point buffer of the saved state
+    (step counters and other integer entries say nothing about the parameter)."""
+    fallback = None
     for v in entry.values():
         t = v if isinstance(v, torch.Tensor) else (v[0] if isinstance(v, (list, tuple)) and v and isinstance(v[0], torch.Tensor) else None)
-        if t is not None:
-            return tuple(t.shape) or (1,), t.dtype
-    return (1,), torch.float32
+        if t is None:
+            continue
+        if t.is_floating_point() and t.ndim > 0:
+            return tuple(t.shape), t.dtype
+        if fallback is None and t.is_floating_point():
+            fallback = ((1,), t.dtype)
+    return fallback or ((1,), torch.float32)
 
 
 def _instantiate(opt_cls, sd: Dict[str, Any]):

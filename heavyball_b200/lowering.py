@@ -37,6 +37,7 @@ import torch
 
 from . import chainable as C
 from . import matrix_stage, ops, utils
+from .utils.tracing import stage as _stage
 
 enabled = os.environ.get("HB200_DISABLE_LOWERING") != "1"
 
@@ -494,8 +495,9 @@ def _run(opt, prog, states, group, grads, params, on_gpu, check_only) -> bool:
     layout, scratch, _ = _bucket_layout(prog, params_v)
     dev = params[0].device
     sq = torch.zeros(len(scratch), dtype=torch.float32, device=dev)  # squared norms, accumulated by the momentum kernel
-    launch(g=grads_v, u=scratch, s0=s0, s0e=s0e, s1=s1, s1e=s1e, s2=s2, s2e=s2e, out_mode=ops.OUT_UPDATE, dt_u=ops.F32,
-           scale=sq, accum_sumsq=1, seed=_seed(opt, group, 0), **base, **mars_kw, **peer_in)  # fmt: skip
+    with _stage("momentum"):
+        launch(g=grads_v, u=scratch, s0=s0, s0e=s0e, s1=s1, s1e=s1e, s2=s2, s2e=s2e, out_mode=ops.OUT_UPDATE, dt_u=ops.F32,
+               scale=sq, accum_sumsq=1, seed=_seed(opt, group, 0), **base, **mars_kw, **peer_in)  # fmt: skip
     scale_mode = "scale"
     final = list(scratch)
     buckets = [(shape, idx, U) for shape, idx, U, _ in layout if len(shape) >= 2]
@@ -522,7 +524,7 @@ def _run(opt, prog, states, group, grads, params, on_gpu, check_only) -> bool:
             side.wait_event(ready)
             used.append(side)
         chunk = max(1, _NS_WORKSPACE_BYTES // (R * Cc * 8))  # four bf16 work copies per matrix
-        with torch.cuda.stream(side):
+        with torch.cuda.stream(side), _stage(f"ns/{R}x{Cc}"):
             norms = sq.index_select(0, sel_idx)
             for c0 in range(0, len(idx), chunk):
                 c1 = min(len(idx), c0 + chunk)
@@ -532,8 +534,14 @@ def _run(opt, prog, states, group, grads, params, on_gpu, check_only) -> bool:
                 )
     for side in used:
         main.wait_stream(side)
+    with _stage("update"):
+        _orthogonal_update(opt, group, caution, params_v, grads_v, final, pe, base, epilogue, peer_in, peer_out)
+    return True
+
+
+def _orthogonal_update(opt, group, caution, params_v, grads_v, final, pe, base, epilogue, peer_in, peer_out):
     if caution:
-        masked = torch.zeros(len(params_v), dtype=torch.int32, device=params[0].device)
+        masked = torch.zeros(len(params_v), dtype=torch.int32, device=params_v[0].device)
         ops.fused_chain(g=grads_v, u=final, masked=masked, algo=ops.IDENTITY, u_is_input=1, count_caution=1,
                         out_mode=ops.OUT_UPDATE, dt_u=ops.F32, dt_g=base["dt_g"], dt_s=ops.NONE, dt_p=ops.NONE,
                         seed=_seed(opt, group, 1), **peer_in)  # fmt: skip
@@ -544,7 +552,6 @@ def _run(opt, prog, states, group, grads, params, on_gpu, check_only) -> bool:
         ops.fused_chain(p=params_v, pe=pe, u=final, algo=ops.IDENTITY, u_is_input=1, out_mode=ops.OUT_PARAM, dt_u=ops.F32,
                         dt_p=base["dt_p"], dt_g=ops.NONE, dt_s=ops.NONE, seed=_seed(opt, group, 3), **epilogue,
                         **peer_out)  # fmt: skip
-    return True
 
 
 def _scratch(prog: _Program, params) -> List[torch.Tensor]:
@@ -721,8 +728,9 @@ def _run_precond(opt, prog: _Program, states, group, grads, params, on_gpu: bool
                 continue
             U3, O3 = (U, O) if U.ndim == 3 else (U.unsqueeze(1), O.unsqueeze(1))
             bucket = _stage_bucket(prog, group, shape, len(idx), lambda: matrix_stage.SoapBucket(keys, _SOAP_INNER[stage.fn_name]))
-            bucket.run(members, U3, O3, group, b1=b1, b2=b2, eps=group["eps"], stat_w=stat_w,
-                       refresh=bool(group["is_preconditioning"]))  # fmt: skip
+            with _stage("soap.refresh" if group["is_preconditioning"] else "soap.project"):
+                bucket.run(members, U3, O3, group, b1=b1, b2=b2, eps=group["eps"], stat_w=stat_w,
+                           refresh=bool(group["is_preconditioning"]))  # fmt: skip
         if vec:
             m = [states[i][keys["exp_avg"]] for i in vec]
             v = [states[i][keys["exp_avg_sq"]] for i in vec]
@@ -748,7 +756,8 @@ def _run_precond(opt, prog: _Program, states, group, grads, params, on_gpu: bool
             members = [states[i] for i in idx]
             bucket = _stage_bucket(prog, group, shape, len(idx), lambda: matrix_stage.PsgdBucket(keys, line))
             inner = [len(idx), *(d for d in shape if d != 1)]  # the transform sees size-1 dims squeezed away
-            bucket.run(members, U.view(inner), O.view(inner), group, fit=fit, delayed=delayed)
+            with _stage("psgd.fit" if fit else "psgd.apply"):
+                bucket.run(members, U.view(inner), O.view(inner), group, fit=fit, delayed=delayed)
         # the fused form masks against the incoming update, the unfused one against the gradient
         fused_caution_ref = u_views if fused else None
 

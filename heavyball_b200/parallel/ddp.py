@@ -38,6 +38,7 @@ import torch
 import torch.distributed as dist
 
 from .. import ops
+from ..utils.tracing import stage as _stage
 
 
 def _world():
@@ -245,14 +246,16 @@ class PeerContext:
         self.epoch += 1
         self.stale_state = True
         self._check_grads_in_slab()
-        self._barrier(0)
+        with _stage("peer.begin"):
+            self._barrier(0)
         for dtype, off, n in self.fallback_ranges:
             dist.all_reduce(self.slabs[dtype]["G"][off : off + n], op=dist.ReduceOp.AVG, group=self.group)
 
     def end_step(self):
         """After the last optimizer kernel: wait until every peer has finished reading this rank's
         gradients and writing this rank's parameters, then clear the gradient slab."""
-        self._barrier(1)
+        with _stage("peer.end"):
+            self._barrier(1)
         for slab in self.slabs.values():
             slab["G"].zero_()
         self._attach_grads()

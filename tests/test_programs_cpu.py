@@ -78,3 +78,19 @@ def test_reloaded_checkpoint_continues_identically(name, kwargs):
     resumed, _ = _run(name, kwargs, 6, lowered=True, reload_at=4)
     for s, r in zip(straight, resumed):
         torch.testing.assert_close(r, s, rtol=1e-6, atol=1e-7)
+
+
+def test_stage_ranges_are_opened_when_tracing_is_on():
+    from heavyball_b200.utils import tracing
+
+    tracing.enable(True, record=True)
+    tracing.seen.clear()
+    try:
+        _run("SOAP", CASES[0][1], 4, lowered=True)
+        _run("PSGDKron", CASES[3][1], 3, lowered=True)
+    finally:
+        tracing.enable(False)
+    assert {"soap.project", "soap.refresh", "psgd.fit"} <= set(tracing.seen)
+    tracing.seen.clear()
+    _run("SOAP", CASES[0][1], 3, lowered=True)
+    assert not tracing.seen  # off again: nothing recorded, nothing pushed

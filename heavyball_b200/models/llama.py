@@ -32,8 +32,7 @@ class RMSNorm(nn.Module):
         self.eps = eps
 
     def forward(self, x):
-        x32 = x.float()
-        return (x32 * torch.rsqrt(x32.pow(2).mean(-1, keepdim=True) + self.eps)).type_as(x) * self.weight
+        return F.rms_norm(x, (x.shape[-1],), self.weight.to(x.dtype), self.eps)  # one fused kernel each way
 
 
 def _rope(x, cos, sin):

@@ -105,6 +105,9 @@ def load():
             raise RuntimeError("heavyball_b200.ops: extension unavailable") from _load_error
         try:
             _ext = _import_prebuilt() or build()
+            tile = os.environ.get("HB200_NS_TILE")  # tuning aid: force the 128 or 256 output tile of the Newton-Schulz GEMMs
+            if tile:
+                _ext.set_ns_gemm_tile(int(tile))
         except BaseException as err:  # noqa: BLE001
             _load_error = err
             raise RuntimeError(

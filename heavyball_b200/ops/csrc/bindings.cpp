@@ -524,5 +524,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("segmented_reduce", &segmented_reduce);
   m.def("ns_prepare", &ns_prepare);
   m.def("ns_gemm", &ns_gemm);
+  m.def("set_ns_gemm_tile", &hb::set_ns_gemm_tile_override);
   m.def("chunk_elems", &hb::chain_chunk_elems);
 }

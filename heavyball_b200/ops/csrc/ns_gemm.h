@@ -28,6 +28,10 @@ struct GemmParams {
   int* status;              // set to 1 if a bounded wait expired
 };
 
+// Tile choice of launch_ns_gemm: 0 = by problem size (default), 128 / 256 = force that output tile (tests, tuning).
+int ns_gemm_tile_override();
+void set_ns_gemm_tile_override(int tile);
+
 cudaError_t launch_ns_gemm(const void* A, int64_t lda, int64_t strideA, const void* B, int64_t ldb, int64_t strideB,
                            const GemmParams& P, cudaStream_t stream);
 cudaError_t launch_ns_prepare(const void* const* srcs, int src_dt, int R, int C, int batch, const float* sumsq, float eps,

@@ -9,7 +9,7 @@ import heavyball_b200 as hb
 pytestmark = pytest.mark.gpu
 
 
-def _model(width=1024, depth=4):
+def _model(width=2048, depth=8):  # 134 MB of parameters: library workspaces (tens of MB) stay small beside it
     torch.manual_seed(0)
     layers = []
     for _ in range(depth):
@@ -21,7 +21,7 @@ def test_adamw_peak_memory_envelope():
     model = _model()
     model_bytes = sum(p.numel() * p.element_size() for p in model.parameters())
     opt = hb.AdamW(model.parameters(), lr=1e-3)
-    x = torch.randn(8, 1024, device="cuda")
+    x = torch.randn(8, 2048, device="cuda")
     for step in range(6):
         if step == 2:  # state exists, the allocator is warm
             torch.cuda.synchronize()

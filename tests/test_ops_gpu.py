@@ -177,10 +177,20 @@ def test_newton_schulz_kernel_vs_fp32(shape, batch):
         assert abs(sv.median().item() - sv_want.median().item()) < 0.05
 
 
-def test_ns_gemm_modes_vs_matmul():
+@pytest.mark.parametrize("tile,m,n", [(128, 256, 384), (256, 256, 384), (256, 520, 712), (256, 1024, 1280)])
+def test_ns_gemm_modes_vs_matmul(tile, m, n):
+    """The three products of one polynomial step, with the 128x128-tile kernel and with the 256x256-tile one (forced:
+    by default it is only chosen for large problems), ragged sizes included."""
     ext = ops.load()
+    ext.set_ns_gemm_tile(tile)
+    try:
+        _ns_gemm_modes(ext, 2, m, n)
+    finally:
+        ext.set_ns_gemm_tile(0)
+
+
+def _ns_gemm_modes(ext, B, m, n):
     torch.manual_seed(1)
-    B, m, n = 2, 256, 384
     x = (torch.randn(B, m, n, device=DEV) / n**0.5).bfloat16()
     xt = x.mT.contiguous()
     S = torch.empty(B, m, m, device=DEV, dtype=torch.bfloat16)
@@ -205,6 +215,40 @@ def test_ns_gemm_modes_vs_matmul():
     assert torch.equal(nxt, nx.mT.contiguous())
     torch.testing.assert_close(F, nx.float() * 0.5, rtol=0, atol=0)
     assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("table", ["polar_express", "legacy"])
+def test_other_coefficient_tables_through_the_kernel(table):
+    """The 10-step Polar-Express table (8 triples) and the fixed legacy triple run through the same GEMM chain."""
+    from heavyball_b200.utils import orthogonal as O
+
+    torch.manual_seed(0)
+    coeffs = [O.ABC_LIST_STABLE[min(i, len(O.ABC_LIST_STABLE) - 1)] for i in range(10)] if table == "polar_express" \
+        else [O.LEGACY_COEFFS] * 5
+    mats = [torch.randn(256, 640, device=DEV) for _ in range(2)]
+    out = ops.newton_schulz_batched(mats, coeffs, out_scale=1.0)
+    torch.cuda.synchronize()
+    ops.check_status()
+    for m, o in zip(mats, out):
+        want = _ns_reference(m, coeffs)
+        assert ((o - want).norm() / want.norm()).item() < 6e-2
+        if table == "polar_express":  # ten steps reach the polar factor: singular values at 1
+            sv = torch.linalg.svdvals(o.float())
+            assert 0.9 < sv.min().item() and sv.max().item() < 1.1
+
+
+@pytest.mark.parametrize("shape,batch", [((1024, 4096), 2), ((2048, 2048), 3), ((256, 512), 160)], ids=str)
+def test_newton_schulz_large_and_many(shape, batch):
+    """A 4096-wide operand, square 2048 matrices (the 256x256-tile kernel by default) and a batch of more than one
+    wave of tiles."""
+    torch.manual_seed(0)
+    mats = [torch.randn(*shape, device=DEV) for _ in range(batch)]
+    out = ops.newton_schulz_batched(mats, utils.NS5_COEFFS, out_scale=1.0)
+    torch.cuda.synchronize()
+    ops.check_status()
+    for i in (0, batch - 1):
+        want = _ns_reference(mats[i], utils.NS5_COEFFS)
+        assert ((out[i] - want).norm() / want.norm()).item() < 4e-2, shape
 
 
 def test_muon_lowered_matches_pytorch():

@@ -257,10 +257,11 @@ class _Plan:
     ``assemble`` lists, for each owned parameter, where every rank's slice lands in the full tensor.
     """
 
-    __slots__ = ("items", "dtype", "device", "send_order", "send_splits", "recv_splits", "assemble", "half_recv")
+    __slots__ = ("items", "dtype", "device", "send_order", "send_splits", "recv_splits", "assemble", "half_recv", "mover")
 
     def __init__(self, items, rank, ws):
         self.items = items  # [(param, info)], same order on every rank
+        self.mover = None  # PeerMover once built; False when the collective path is to be used
         self.dtype = items[0][0].dtype
         self.device = items[0][0].device
         self.send_order = [[] for _ in range(ws)]  # per destination: indices into items with a local slice
@@ -302,15 +303,182 @@ def _build_plans(gathers, rank, ws):
     return [_Plan(items, rank, ws) for items in by_key.values()]
 
 
+# ---------------------------------------------------------------------------------------- peer-memory mover
+
+
+def _peer_mover_possible(plan) -> bool:
+    import os
+
+    if os.environ.get("HB200_FSDP_PEER", "1") == "0" or plan.device.type != "cuda":
+        return False
+    if plan.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+        return False
+    try:
+        from .. import ops
+
+        return ops.available() and dist.get_backend() == "nccl" and _world() <= ops.load().MAX_WORLD
+    except Exception:  # noqa: BLE001 - no extension, no symmetric memory: the collective path is always there
+        return False
+
+
+class PeerMover:
+    """Moves the shards of one plan between ranks with this library's own kernels over NVLink peer memory instead of
+    collectives.
+
+    Every rank keeps its local parameter and gradient slices in two *staging* buffers of symmetric memory (one layout,
+    known to all ranks from the shard-size table).  Gather: after a flag barrier the owner of a matrix runs ONE
+    multi-tensor copy launch whose sources are the slices in its peers' staging buffers (peer loads) and whose
+    destinations are the pieces of the full parameter / gradient in local memory - no collective, no concatenation, no
+    per-slice copies.  Scatter: one launch stores the pieces of the updated full parameters into the staging buffers
+    of the ranks that hold those rows (peer stores); after a second barrier every rank copies its staging slices back
+    into its shards.  Waits on the flags are bounded; an expired wait is reported by :meth:`check`.
+    """
+
+    def __init__(self, plan, rank: int, ws: int):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from .. import ops
+
+        self.plan, self.rank, self.ws = plan, rank, ws
+        self.ext = ops.load()
+        # layout of every rank's staging buffer: its slices in plan order, 16-element aligned
+        self.offset = [[None] * len(plan.items) for _ in range(ws)]
+        totals = []
+        for r in range(ws):
+            at = 0
+            for k, (_, info) in enumerate(plan.items):
+                n = info.sizes[r]
+                if n:
+                    self.offset[r][k] = at
+                    at += (n + 15) // 16 * 16
+            totals.append(at)
+        size = max(max(totals), 16)
+        group = dist.group.WORLD
+        import warnings
+
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            try:
+                symm_mem.enable_symm_mem_for_group(group.group_name)
+            except Exception:  # noqa: BLE001 - a deprecated no-op in newer releases
+                pass
+        self.P = symm_mem.empty(size, dtype=plan.dtype, device=plan.device)
+        self.G = symm_mem.empty(size, dtype=plan.dtype, device=plan.device)
+        self.flags = symm_mem.empty(4 * self.ext.MAX_WORLD, dtype=torch.int32, device=plan.device)
+        self.P.zero_()
+        self.G.zero_()
+        self.flags.zero_()
+        self.hp, self.hg, hf = (symm_mem.rendezvous(t, group) for t in (self.P, self.G, self.flags))
+        self.f_ptrs = list(hf.buffer_ptrs)
+        self._hf = hf
+        self.status = torch.zeros(1, dtype=torch.int32, device=plan.device)
+        self.epoch = 0
+        self.timeout_s = 10.0
+        # views that never change: this rank's staging slices, and its peers' slices of the matrices it owns
+        self.mine = [k for k, (_, info) in enumerate(plan.items) if info.sizes[rank]]
+        self.stage_p = [self.P[self.offset[rank][k] : self.offset[rank][k] + plan.items[k][1].sizes[rank]] for k in self.mine]
+        self.stage_g = [self.G[self.offset[rank][k] : self.offset[rank][k] + plan.items[k][1].sizes[rank]] for k in self.mine]
+        self.remote_p, self.remote_g = {}, {}
+        for k, pieces in plan.assemble.items():
+            for src, _, length, _ in pieces:
+                shape, off = (length,), self.offset[src][k]
+                self.remote_p[(k, src)] = self.hp.get_buffer(src, shape, plan.dtype, off)
+                self.remote_g[(k, src)] = self.hg.get_buffer(src, shape, plan.dtype, off)
+        torch.cuda.synchronize(plan.device)
+        dist.barrier()
+
+    def _barrier(self, slot):
+        from .. import ops
+
+        self.ext.peer_signal(self.f_ptrs, slot, self.rank, self.epoch)
+        self.ext.peer_wait(self.flags, slot, self.ws, self.epoch, self.timeout_s, self.status)
+        ops.launch_counter.count += 2
+
+    def _copy(self, srcs, dsts):
+        """One multi-tensor launch: ``dst[i] <- src[i]`` (sources and destinations may be peer memory)."""
+        from .. import ops
+
+        if srcs:
+            code = ops.dtype_code(srcs[0])
+            ops.fused_chain(g=srcs, u=dsts, algo=ops.IDENTITY, out_mode=ops.OUT_UPDATE, n_state=0, dt_g=code, dt_u=code,
+                            dt_p=ops.NONE, dt_s=ops.NONE, seed=0)  # fmt: skip
+
+    def gather(self):
+        plan = self.plan
+        self.epoch += 1
+        local_p = [plan.items[k][0].data.reshape(-1) for k in self.mine]
+        local_g = []
+        for k in self.mine:
+            p = plan.items[k][0]
+            if p.grad is None:
+                local_g.append(torch.zeros_like(p.data).reshape(-1))
+            else:
+                if p.grad.dtype != plan.dtype:
+                    raise RuntimeError(f"gradient dtype {p.grad.dtype} differs from parameter dtype {plan.dtype}")
+                local_g.append(p.grad.reshape(-1))
+        self._copy(local_p + local_g, self.stage_p + self.stage_g)
+        self._barrier(0)  # every rank's slices are in its staging buffers
+        shards, srcs, dsts = {}, [], []
+        for k, (p, info) in enumerate(plan.items):
+            shards[id(p)] = p.data
+            p.grad = None
+            pieces = plan.assemble.get(k)
+            if pieces is None:
+                continue
+            full_p, full_g = p.data.new_empty(info.total), p.data.new_empty(info.total)
+            for src, off, length, _ in pieces:
+                srcs += [self.remote_p[(k, src)], self.remote_g[(k, src)]]
+                dsts += [full_p[off : off + length], full_g[off : off + length]]
+            p.data, p.grad = full_p.view(info.orig_shape), full_g.view(info.orig_shape)
+        self._copy(srcs, dsts)
+        return shards
+
+    def scatter(self, shards):
+        plan = self.plan
+        srcs, dsts = [], []
+        for k, (p, info) in enumerate(plan.items):
+            pieces = plan.assemble.get(k)
+            if pieces is None:
+                continue
+            flat = p.data.reshape(-1)
+            if flat.numel() != info.total:
+                raise RuntimeError(f"return path expects full parameter {info.param_idx}, got {flat.numel()} elements")
+            for src, off, length, _ in pieces:
+                srcs.append(flat[off : off + length])
+                dsts.append(self.remote_p[(k, src)])
+        self._copy(srcs, dsts)
+        self._barrier(1)  # every owner has stored the rows this rank holds (and has read this rank's gradients)
+        for k, (p, _) in enumerate(plan.items):
+            p.data = shards[id(p)]
+            p.grad = None
+        self._copy(self.stage_p, [plan.items[k][0].data.reshape(-1) for k in self.mine])
+
+    def check(self):
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            raise RuntimeError(f"shard exchange timed out waiting for rank {code - 2} (epoch {self.epoch})")
+
+
 def _all_to_all(send, recv_splits, send_splits):
     recv = send.new_empty(sum(recv_splits))
     dist.all_to_all_single(recv, send, output_split_sizes=recv_splits, input_split_sizes=send_splits)
     return recv
 
 
+def _mover_of(plan, rank):
+    if plan.mover is None:
+        plan.mover = PeerMover(plan, rank, _world()) if _peer_mover_possible(plan) else False
+    return plan.mover or None
+
+
 def _gather_to_owners(plans, rank):
     shards = {}
     for plan in plans:
+        mover = _mover_of(plan, rank)
+        if mover is not None:
+            shards.update(mover.gather())
+            continue
         payload = []
         for dst_items in plan.send_order:
             ps = [plan.items[k][0] for k in dst_items]
@@ -350,6 +518,9 @@ def _gather_to_owners(plans, rank):
 
 def _scatter_from_owners(exchange: _Exchange, rank):
     for plan in exchange.plans:
+        if plan.mover:
+            plan.mover.scatter(exchange.shards)
+            continue
         out = [[] for _ in plan.recv_splits]
         for k, (p, info) in enumerate(plan.items):
             pieces = plan.assemble.get(k)

@@ -77,6 +77,13 @@ def main():
         train(fsdp, opt, steps, x, y)
         with FSDP.summon_full_params(fsdp):
             got = torch.cat([p.detach().flatten() for p in fsdp.parameters()])
+    movers = [pl.mover for plans in getattr(opt, "_fsdp_plans", {}).values() for pl in plans if pl.mover]
+    for mover in movers:
+        mover.check()  # no bounded wait of the peer-memory exchange expired
+    want_peer = use_cuda and os.environ.get("HB200_FSDP_PEER", "1") != "0" and getattr(opt, "_needs_gather", False)
+    if want_peer and not movers:
+        print("RESULT peer-memory exchange was expected but the collective path ran")
+        sys.exit(1)
     err = (got - want).abs().max().item()
     ok = err <= tol * max(1.0, want.abs().max().item())
     if rank == 0:

@@ -101,7 +101,7 @@ def parse(argv=None):
                          "(auto = only for the default configuration)")
     ap.add_argument("--secondary-steps", type=int, default=4)
     ap.add_argument("--secondary-timeout", type=float, default=420.0, help="seconds per child process")
-    ap.add_argument("--secondary-budget", type=float, default=1500.0, help="seconds for all child processes together")
+    ap.add_argument("--secondary-budget", type=float, default=1000.0, help="seconds for all child processes together")
     ap.add_argument("--reference-compile-mode", default=None,
                     help="reference arm: value for heavyball.utils.compile_mode ('none' = eager); default = stock")
     return ap.parse_args(argv)

@@ -416,8 +416,8 @@ def _run(opt, prog, states, group, grads, params, on_gpu, check_only) -> bool:
             raise RuntimeError("peer data parallelism: the step's parameters do not match the partition plan of their group")
         sel = [(pos_to_local[j], seg) for j, seg in plan["sel"] if j in pos_to_local]
         args = peer.peer_args(params[0].dtype)
-        peer_in = {"g_delta": args["g_delta"], "g_scale": args["g_scale"]}
-        peer_out = {"p_delta": args["p_delta"]}
+        peer_in = {"g_delta": args["g_delta"], "g_scale": args["g_scale"], "g_mc_delta": args["g_mc_delta"]}
+        peer_out = {"p_delta": args["p_delta"], "p_mc_delta": args["p_mc_delta"]}
     else:
         sel = [(i, None) for i in range(len(params))]
     pick = lambda xs: [_cut(xs[i], seg) for i, seg in sel] if len(xs) else []  # noqa: E731
@@ -661,8 +661,8 @@ def _run_precond(opt, prog: _Program, states, group, grads, params, on_gpu: bool
         if not params:
             return True
         args = peer.peer_args(params[0].dtype)
-        peer_in = {"g_delta": args["g_delta"], "g_scale": args["g_scale"]}
-        peer_out = {"p_delta": args["p_delta"]}
+        peer_in = {"g_delta": args["g_delta"], "g_scale": args["g_scale"], "g_mc_delta": args["g_mc_delta"]}
+        peer_out = {"p_delta": args["p_delta"], "p_mc_delta": args["p_mc_delta"]}
     stage = prog.stage
     ecc_mode = group.get("ecc")
     if not _state_ready(stage, states, False):

@@ -153,6 +153,8 @@ void fused_chain(const TList& p, const TList& pe, const TList& g, const TList& u
     P.n_dst = (int)d.size();
     for (size_t i = 0; i < d.size(); ++i) P.p_delta[i] = d[i];
   }
+  P.g_mc_delta = cfg.contains("g_mc_delta") ? cfg["g_mc_delta"].cast<int64_t>() : 0;
+  P.p_mc_delta = cfg.contains("p_mc_delta") ? cfg["p_mc_delta"].cast<int64_t>() : 0;
   check(hb::launch_fused_chain(t.metas, t.prefix, t.total_chunks, P, geti("count_caution") != 0,
                                at::cuda::getCurrentCUDAStream()), "fused_chain launch");
 }

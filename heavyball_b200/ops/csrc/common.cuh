@@ -214,4 +214,71 @@ __device__ inline void store4(void* p, void* c, int dt, int64_t i, int n_valid, 
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// NVSwitch multicast accesses (multimem): one instruction acts on the same address of every GPU bound to the
+// multicast object.  Addresses must be 16-byte (v4.f32) / 8-byte (v2) aligned.
+// ---------------------------------------------------------------------------------------------
+__device__ inline F4 mc_ld_reduce4(const void* mc, int dt, int64_t i) {
+  F4 r;
+  if (dt == kF32) {
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3])
+                 : "l"((const float*)mc + i)
+                 : "memory");
+  } else {  // four 16-bit values, accumulated in fp32 inside the switch
+    uint32_t a, b;
+    if (dt == kBF16)
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v2.bf16x2 {%0, %1}, [%2];"
+                   : "=r"(a), "=r"(b) : "l"((const uint16_t*)mc + i) : "memory");
+    else
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v2.f16x2 {%0, %1}, [%2];"
+                   : "=r"(a), "=r"(b) : "l"((const uint16_t*)mc + i) : "memory");
+    const uint16_t h[4] = {(uint16_t)(a & 0xFFFF), (uint16_t)(a >> 16), (uint16_t)(b & 0xFFFF), (uint16_t)(b >> 16)};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) r.v[k] = dt == kBF16 ? bf16_bits_to_float(h[k]) : f16_bits_to_float(h[k]);
+  }
+  return r;
+}
+
+// Stores the primary of four elements to every GPU through the multicast address `mc`; the residual of an
+// error-corrected value (if any) goes to the local buffer `c`.  Same rounding as store4.
+__device__ inline void mc_store4(void* mc, void* c, int dt, int64_t i, const F4& x, uint4 rnd) {
+  if (dt == kF32) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"l"((float*)mc + i), "f"(x.v[0]), "f"(x.v[1]), "f"(x.v[2]), "f"(x.v[3])
+                 : "memory");
+    return;
+  }
+  const uint32_t rr[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+  const bool bf = is_bf16_like(dt);
+  uint16_t h[4];
+  int corr[4] = {0, 0, 0, 0};
+  const float smax = ecc_wide(dt) ? 32767.0f : 127.0f;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    if (is_ecc(dt)) {
+      h[k] = bf ? rne_bf16_bits(x.v[k]) : rne_f16_bits(x.v[k]);
+      corr[k] = ecc_residual(x.v[k], h[k], bf, smax, u32_to_unit(rr[k]));
+    } else {
+      h[k] = bf ? sr_bf16_bits(x.v[k], rr[k]) : rne_f16_bits(x.v[k]);
+    }
+  }
+  const float lo = __uint_as_float((uint32_t)h[0] | ((uint32_t)h[1] << 16));
+  const float hi = __uint_as_float((uint32_t)h[2] | ((uint32_t)h[3] << 16));
+  asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"((uint16_t*)mc + i), "f"(lo), "f"(hi) : "memory");
+  if (is_ecc(dt) && c != nullptr) {
+    if (ecc_wide(dt)) {
+      uint16_t w[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) w[k] = (uint16_t)(int16_t)corr[k];
+      pack_h4((uint16_t*)c + i, 4, true, w);
+    } else {
+      uint32_t t = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) t |= ((uint32_t)(uint8_t)(int8_t)corr[k]) << (8 * k);
+      *(uint32_t*)((int8_t*)c + i) = t;
+    }
+  }
+}
+
 }  // namespace hb

@@ -72,7 +72,12 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
     F4 s1 = load4(M.s1, M.s1e, P.dt_s, i, nv, vec_ok);
     F4 s2 = load4(M.s2, M.s2e, P.dt_s, i, nv, vec_ok);
     F4 g;
-    if (P.n_src > 0) {  // reduce the same element over every rank's gradient slab (peer loads over NVLink)
+    if (P.n_src > 0 && P.g_mc_delta != 0 && vec_ok && nv == 4 && (P.dt_g == kF32 || P.dt_g == kBF16 || P.dt_g == kF16)) {
+      // one load, summed over all ranks inside the NVSwitch
+      g = mc_ld_reduce4((const char*)M.g + P.g_mc_delta, P.dt_g, i);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) g.v[k] *= P.g_scale;
+    } else if (P.n_src > 0) {  // reduce the same element over every rank's gradient slab (peer loads over NVLink)
 #pragma unroll
       for (int k = 0; k < 4; ++k) g.v[k] = 0.f;
       for (int r0 = 0; r0 < P.n_src; r0 += 4) {  // four sources in flight at a time, summed in rank order
@@ -237,7 +242,9 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
       p.v[k] = p.v[k] * (1.0f - d * P.lr) + uu * -P.lr;
     }
     const uint4 prnd = draw(P.dt_p, rng, ctr, ctr_hi, (uint32_t)t, 3u);
-    if (P.n_dst > 0) {  // single writer per element: every replica receives bit-identical parameters
+    if (P.n_dst > 0 && P.p_mc_delta != 0 && vec_ok && nv == 4) {  // one store, replicated to every rank by the NVSwitch
+      mc_store4((char*)M.p + P.p_mc_delta, M.pe, P.dt_p, i, p, prnd);
+    } else if (P.n_dst > 0) {  // single writer per element: every replica receives bit-identical parameters
       for (int r = 0; r < P.n_dst; ++r)  // the residual of an error-corrected parameter stays with this rank (its only reader)
         store4((char*)M.p + P.p_delta[r], P.p_delta[r] == 0 ? M.pe : nullptr, P.dt_p, i, nv, vec_ok, p, prnd);
     } else {

@@ -69,6 +69,12 @@ struct ChainParams {
   float g_scale;
   int64_t g_delta[kMaxPeers];
   int64_t p_delta[kMaxPeers];
+  // NVSwitch multicast (0 = off): byte offsets from this rank's address to the multicast address of the same element.
+  // With g_mc_delta the gradient of all ranks is summed inside the switch by one multimem.ld_reduce per 16 bytes instead
+  // of one peer load per rank; with p_mc_delta one multimem.st replaces the per-rank parameter stores.  Both need
+  // 16-byte aligned, full 4-element accesses; ragged edges take the per-rank path.
+  int64_t g_mc_delta;
+  int64_t p_mc_delta;
 };
 
 int chain_chunk_elems();

@@ -32,6 +32,7 @@ the ``state_dict`` of any one rank is the whole optimizer state.
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -120,10 +121,17 @@ class PeerContext:
             hp, hg = symm_mem.rendezvous(P, self.group), symm_mem.rendezvous(G, self.group)
             self._hdl += [hp, hg]
             p_ptrs, g_ptrs = list(hp.buffer_ptrs), list(hg.buffer_ptrs)
+            # NVSwitch multicast addresses of the two slabs (0 where the fabric has none): reductions and broadcasts then
+            # happen inside the switch
+            use_mc = os.environ.get("HB200_PEER_MULTIMEM", "1") != "0"
+            mc_p = int(getattr(hp, "multicast_ptr", 0) or 0) if use_mc else 0
+            mc_g = int(getattr(hg, "multicast_ptr", 0) or 0) if use_mc else 0
             self.slabs[dtype] = {
                 "P": P, "G": G,
                 "p_delta": [ptr - p_ptrs[self.rank] for ptr in p_ptrs],
                 "g_delta": [ptr - g_ptrs[self.rank] for ptr in g_ptrs],
+                "p_mc_delta": (mc_p - p_ptrs[self.rank]) if mc_p else 0,
+                "g_mc_delta": (mc_g - g_ptrs[self.rank]) if mc_g else 0,
             }  # fmt: skip
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
 
@@ -257,8 +265,7 @@ class PeerContext:
         with _stage("peer.end"):
             self._barrier(1)
         for slab in self.slabs.values():
-            slab["G"].zero_()
-        self._attach_grads()
+            slab["G"].zero_()  # gradients stay the slab views they were (checked again at the next begin_step)
 
     def consolidate_state(self):
         """Makes the optimizer state complete on every rank.  Collective: call it on all ranks, e.g. before rank 0
@@ -363,7 +370,13 @@ class PeerContext:
 
     def peer_args(self, dtype):
         slab = self.slabs[dtype]
-        return {"g_delta": slab["g_delta"], "g_scale": 1.0 / self.world, "p_delta": slab["p_delta"]}
+        return {"g_delta": slab["g_delta"], "g_scale": 1.0 / self.world, "p_delta": slab["p_delta"],
+                "g_mc_delta": slab["g_mc_delta"], "p_mc_delta": slab["p_mc_delta"]}  # fmt: skip
+
+    @property
+    def multicast(self) -> bool:
+        """True when gradient reduction and parameter broadcast go through NVSwitch multicast addresses."""
+        return any(slab["g_mc_delta"] or slab["p_mc_delta"] for slab in self.slabs.values())
 
 
 class _PeerModule(torch.nn.Module):

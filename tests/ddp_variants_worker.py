@@ -41,6 +41,8 @@ def run(variant, mode, steps, rank, device):
     opt = make(mats, rest)
     wrapped = ddp.wrap(model, opt, mode=mode)
     planned = len(wrapped.peer.plans) if hasattr(wrapped, "peer") else 0
+    if hasattr(wrapped, "peer") and rank == 0:
+        print(f"INFO {variant}: NVSwitch multicast in use = {wrapped.peer.multicast}")
     gen = torch.Generator().manual_seed(100 + rank)
     for _ in range(steps):
         tokens = torch.randint(0, 512, (4, 65), generator=gen).to(device)

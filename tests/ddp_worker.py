@@ -81,6 +81,7 @@ def main():
     scale = nccl_flat.abs().max().item()
     rms = ((peer_flat - nccl_flat).square().mean().sqrt() / nccl_flat.square().mean().sqrt()).item()
     if rank == 0:
+        print(f"multimem={os.environ.get('HB200_PEER_MULTIMEM', '1')} ", end="")
         print(f"RESULT identical={identical} max_abs_diff={diff:.3e} max_abs={scale:.3e} rel_rms={rms:.3e} "
               f"loss_peer={peer_loss.tolist()} loss_nccl={nccl_loss.tolist()} graph_rel_rms={graph_rms:.3e} "
               f"loss_amp={amp_loss.tolist()} loss_graph={graph_loss.tolist()} state_identical={state_identical} "

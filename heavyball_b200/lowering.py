@@ -170,6 +170,30 @@ def _program(opt) -> Optional[_Program]:
     return cached or None
 
 
+def describe(opt) -> str:
+    """One line on what runs the chain of ``opt``: the lowered program (kernel launches) or the PyTorch definitions.
+
+    ``"elementwise(update_by_adam)"``, ``"orthogonal(heavyball_momentum)"``, ``"soap(adam)"``, ``"psgd(update_by_psgd)"``,
+    ``"route[orthogonal(nesterov_ema) | elementwise(update_by_adam)]"``, or ``"not lowered"``.
+    """
+
+    def one(prog):
+        if prog.kind == "route":
+            return "route[" + " | ".join(one(sub) for _, sub in prog.routes) + "]"
+        if prog.kind == "soap":
+            inner = _SOAP_INNER[prog.stage.fn_name]
+        elif prog.kind == "psgd":
+            inner = prog.stage.fn_name if prog.rule is None else f"{prog.rule.fn_name} -> {prog.stage.fn_name}"
+        else:
+            inner = prog.rule.fn_name
+        extra = [name for name, on in (("mars", prog.mars), ("palm", prog.palm), ("grad_clip", prog.gclip),
+                                       ("trust_region", prog.u_op), ("schedule_free", prog.post)) if on]  # fmt: skip
+        return f"{prog.kind}({inner})" + ("".join(f" +{e}" for e in extra))
+
+    prog = _program(opt)
+    return "not lowered" if prog is None else one(prog)
+
+
 def _mark_initialized(tr: C.FunctionTransform, st: dict):
     for layer in tr.layers:
         if isinstance(layer, (C.ZeroSlots, C.CopySlots, C.InitSlots, C.Tag, C.PerTensor, C.Warmup)):

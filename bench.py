@@ -358,6 +358,9 @@ def run_config(args):
 
                 train_model = hb_ddp.wrap(model, opt, mode=args.ddp_mode)
                 parallel_note = f"data parallel, gradient path {args.ddp_mode}"
+                ctx = getattr(opt, "_peer", None) or next((getattr(o, "_peer", None) for o in getattr(opt, "optimizers", [])), None)
+                if ctx is not None:
+                    parallel_note += ", NVSwitch multimem reduce / broadcast" if ctx.multicast else ", per-rank peer loads / stores"
             else:
                 from torch.nn.parallel import DistributedDataParallel
 
@@ -608,6 +611,10 @@ def run_child(cmd, timeout):
     import signal
 
     env = {k: v for k, v in os.environ.items() if k not in _SCRUB}
+    if "torch.distributed.run" in cmd:
+        # a child that runs into its time limit is killed as a group; its ranks' memory is then never bound to an
+        # NVSwitch multicast object (plain peer loads / stores and NCCL without in-switch reduction instead)
+        env.update(NCCL_NVLS_ENABLE="0", HB200_PEER_MULTIMEM="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     t0 = time.time()
     try:
         proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env, cwd=ROOT,

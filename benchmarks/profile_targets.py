@@ -8,6 +8,9 @@
     python benchmarks/profile_targets.py gelu_small      # GELU fwd, and bwd + bias gradient, 16384 x 3072 bf16 (100 MB per tensor)
     python benchmarks/profile_targets.py tf32_small      # split-tf32 GEMM, 4 x (2048 x 2048 x 2048)
     python benchmarks/profile_targets.py qr_small        # panel-wise Cholesky QR of 8 x (1024 x 1024), eager launches
+    python benchmarks/profile_targets.py ns_big          # Newton-Schulz on 4 x (4096 x 4096): the 256 x 256-tile kernel
+    python benchmarks/profile_targets.py soap_small      # one plain SOAP step on 8 x 1024^2 (tf32 GEMMs with fused epilogues)
+    python benchmarks/profile_targets.py psgd_small      # one plain PSGDKron step on 8 x 1024^2 (cached P = Q^T Q operands)
 
 Each case holds well under a few GB on the device and launches only a handful of kernels.
 """
@@ -189,6 +192,64 @@ def qr_small():
     torch.cuda.profiler.stop()
 
 
+def ns_big():
+    mats = [torch.randn(4096, 4096, device="cuda") for _ in range(4)]
+    out = ops.newton_schulz_batched(mats, utils.NS5_COEFFS)
+    us = _timed(lambda: ops.newton_schulz_batched(mats, utils.NS5_COEFFS), reps=3)
+    # per iteration: Gram (upper tiles count half), polynomial (same), apply; 5 iterations
+    dense = 5 * 3 * 2 * 4 * 4096**3
+    print(f"newton_schulz 4x4096^2: {us:.0f} us, {dense / us / 1e6:.0f} dense-equivalent TFLOP/s, "
+          f"{dense * (2 / 3) / us / 1e6:.0f} TFLOP/s counting symmetric products once")
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    out = ops.newton_schulz_batched(mats, utils.NS5_COEFFS)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    ops.check_status()
+    print(float(out.abs().mean()))
+
+
+def _second_order(cls, **kw):
+    params = [torch.nn.Parameter(torch.randn(1024, 1024, device="cuda")) for _ in range(8)]
+    opt = cls(params, lr=1e-3, **kw)
+    grads = [torch.randn_like(p) for p in params]
+
+    def one_step():
+        for p, g in zip(params, grads):
+            p.grad = g
+        opt.step()
+
+    return opt, one_step
+
+
+def soap_small():
+    opt, one_step = _second_order(hb.SOAP, precondition_frequency=100)
+    for _ in range(4):
+        one_step()
+    us = _timed(one_step)
+    print(f"SOAP plain step 8x1024^2: {us:.0f} us")
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    one_step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    ops.check_status()
+
+
+def psgd_small():
+    opt, one_step = _second_order(hb.PSGDKron, preconditioner_update_probability=1e-9)
+    for _ in range(4):
+        one_step()
+    us = _timed(one_step)
+    print(f"PSGDKron plain step 8x1024^2: {us:.0f} us")
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    one_step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    ops.check_status()
+
+
 if __name__ == "__main__":
-    {"qr_small": qr_small, "opt_step_gpt2": opt_step_gpt2, "ns_small": ns_small, "adam_small": adam_small, "ce_small": ce_small,
+    {"ns_big": ns_big, "soap_small": soap_small, "psgd_small": psgd_small, "qr_small": qr_small, "opt_step_gpt2": opt_step_gpt2, "ns_small": ns_small, "adam_small": adam_small, "ce_small": ce_small,
      "ln_small": ln_small, "tf32_small": tf32_small, "gelu_small": gelu_small}[sys.argv[1]]()

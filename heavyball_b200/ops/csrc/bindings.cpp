@@ -326,6 +326,10 @@ at::Tensor tf32_gemm(const at::Tensor& a2, const at::Tensor& b2, int64_t K, int 
     E.m = m->data_ptr<float>(); E.v = v->data_ptr<float>();
   }
   TORCH_CHECK(E.C != nullptr || E.S != nullptr, "tf32_gemm: no output requested");
+  // X X^T (one buffer as both operands): upper tiles only, mirrored on store.  An in-place lerp target is then
+  // symmetric by construction (it only ever receives symmetric increments).
+  E.symmetric = (a2.data_ptr() == b2.data_ptr() && M == N && E.C != nullptr && E.S == nullptr &&
+                 (mode == hb::kEpiStore || mode == hb::kEpiLerp)) ? 1 : 0;
   check(hb::launch_tf32_gemm(a2.data_ptr<float>(), b2.data_ptr<float>(), (int)M, (int)N, (int)K, (int)batch, E,
                              status.data_ptr<int>(), at::cuda::getCurrentCUDAStream()), "tf32 gemm");
   return s;

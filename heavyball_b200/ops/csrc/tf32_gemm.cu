@@ -48,134 +48,162 @@ __device__ __forceinline__ float tf32_hi(float x) {
 
 __device__ __forceinline__ float lerp_w(float s, float x, float w) { return s * (1.0f - w) + x * w; }
 
-// Fused epilogue of one thread: row `r` of the 128x128 tile, 32 accumulator columns at a time.  Values outside
-// [M, N] are never stored; the zero padding of a split output (columns [K, kp) of the operand being produced) is.
-__device__ __forceinline__ void epilogue_direct(uint32_t tmem_base, int quarter, int r, int tm, int tn, int batch, int M, int N,
-                                                const Tf32Epilogue& E) {
-  const int row = tm * TBM + r;
+constexpr int kStageLd = 36;                         // floats per staged row: rows stay 16-byte aligned and float4
+                                                     // accesses of a quarter-warp fall into distinct banks
+constexpr int kStageWarpBytes = 32 * kStageLd * 4;   // one warp's 32 rows x 32 columns
+
+// Fused epilogue of one warp: its 32 accumulator rows of the 128x128 tile, 32 columns at a time.  A thread reads
+// its own row from tensor memory; global memory wants the other orientation (consecutive lanes on consecutive
+// columns), so the block is turned through the warp's `stage` in shared memory (the idle operand ring):
+//   pass 1 (lane = row):                   accumulators * alpha -> stage
+//   pass 2 (8 lanes per row, 4 rows/step): moments, lerp, C store, split-operand store - every global access is a full
+//                                          128-byte line per row; the final values go back to the stage when needed
+//   pass 3 (lane = row):                   outputs that run along the rows: transposed split operand, mirror tile
+// Values outside [M, N] are never stored; the zero padding of a split output (columns [K, kp) of the operand being
+// produced) is.
+__device__ __forceinline__ void epilogue_direct(uint32_t tmem_base, int quarter, int lane, float* stage, int tm, int tn,
+                                                int batch, int M, int N, const Tf32Epilogue& E) {
+  const int row0 = tm * TBM + quarter * 32;
   const int64_t b64 = batch;
   const bool state_vec = (N & 3) == 0;
-  const bool c_vec = (E.ldc & 3) == 0 && ((E.strideC & 3) == 0);
+  const bool c_vec = (E.ldc & 3) == 0 && ((E.strideC & 3) == 0) && ((((uintptr_t)E.C) & 15) == 0);
+  const bool moments = E.mode == kEpiAdam || E.mode == kEpiLaProp;
+  const bool mirror = E.symmetric && tm != tn && E.C != nullptr;
+  const bool along_rows = mirror || (E.S != nullptr && E.s_transposed);
+  const bool s_rows = E.S != nullptr && !E.s_transposed;
+  const int sub = lane >> 3, cg = (lane & 7) * 4;
+  const float w1 = 1.0f - E.b1, w2 = 1.0f - E.b2;
+  float* mine = stage + lane * kStageLd;
 #pragma unroll 1
   for (int cb = 0; cb < TBN / 32; ++cb) {
-    uint32_t acc[32];
-    tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cb * 32), acc);
-    tmem_ld_wait();
     const int col0 = tn * TBN + cb * 32;
-    float v[32];
+    {
+      uint32_t acc[32];
+      tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cb * 32), acc);
+      tmem_ld_wait();
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]) * E.alpha;
+      for (int q = 0; q < 8; ++q)
+        *(float4*)(mine + q * 4) =
+            make_float4(__uint_as_float(acc[q * 4]) * E.alpha, __uint_as_float(acc[q * 4 + 1]) * E.alpha,
+                        __uint_as_float(acc[q * 4 + 2]) * E.alpha, __uint_as_float(acc[q * 4 + 3]) * E.alpha);
+    }
+    __syncwarp();
 
-    if (E.mode == kEpiAdam || E.mode == kEpiLaProp) {
-      if (row < M) {
-        float* mrow = E.m + (b64 * M + row) * (int64_t)N;
-        float* vrow = E.v + (b64 * M + row) * (int64_t)N;
-        const float w1 = 1.0f - E.b1, w2 = 1.0f - E.b2;
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const int col = col0 + q * 4;
-          if (col >= N) break;
-          float m4[4], s4[4];
+    const int col = col0 + cg;
+#pragma unroll 2
+    for (int it = 0; it < 8; ++it) {
+      const int lr = it * 4 + sub, row = row0 + lr;
+      float* sp = stage + lr * kStageLd + cg;
+      const float4 x4 = *(const float4*)sp;
+      float x[4] = {x4.x, x4.y, x4.z, x4.w};
+      if (row < M && col < N) {
+        if (moments) {
+          float* mp = E.m + (b64 * M + row) * (int64_t)N + col;
+          float* vp = E.v + (b64 * M + row) * (int64_t)N + col;
           const bool fast = state_vec && col + 3 < N;
+          float m4[4], s4[4];
           if (fast) {
-            const float4 a = *(const float4*)(mrow + col), c = *(const float4*)(vrow + col);
+            const float4 a = *(const float4*)mp, c = *(const float4*)vp;
             m4[0] = a.x; m4[1] = a.y; m4[2] = a.z; m4[3] = a.w;
             s4[0] = c.x; s4[1] = c.y; s4[2] = c.z; s4[3] = c.w;
           } else {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              m4[e] = col + e < N ? mrow[col + e] : 0.f;
-              s4[e] = col + e < N ? vrow[col + e] : 0.f;
+              m4[e] = col + e < N ? mp[e] : 0.f;
+              s4[e] = col + e < N ? vp[e] : 0.f;
             }
           }
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float x = v[q * 4 + e];
-            s4[e] = lerp_w(s4[e], x * x, w2);
+            s4[e] = lerp_w(s4[e], x[e] * x[e], w2);
             const float d = fmaxf(sqrtf(s4[e]), E.eps);
             if (E.mode == kEpiAdam) {
-              m4[e] = lerp_w(m4[e], x, w1);
-              v[q * 4 + e] = m4[e] / d;
+              m4[e] = lerp_w(m4[e], x[e], w1);
+              x[e] = m4[e] / d;
             } else {
-              m4[e] = lerp_w(m4[e], x / d, w1);
-              v[q * 4 + e] = m4[e];
+              m4[e] = lerp_w(m4[e], x[e] / d, w1);
+              x[e] = m4[e];
             }
           }
           if (fast) {
-            *(float4*)(mrow + col) = make_float4(m4[0], m4[1], m4[2], m4[3]);
-            *(float4*)(vrow + col) = make_float4(s4[0], s4[1], s4[2], s4[3]);
+            *(float4*)mp = make_float4(m4[0], m4[1], m4[2], m4[3]);
+            *(float4*)vp = make_float4(s4[0], s4[1], s4[2], s4[3]);
           } else {
 #pragma unroll
             for (int e = 0; e < 4; ++e)
-              if (col + e < N) { mrow[col + e] = m4[e]; vrow[col + e] = s4[e]; }
+              if (col + e < N) { mp[e] = m4[e]; vp[e] = s4[e]; }
+          }
+        }
+        if (E.C != nullptr) {
+          float* cp = E.C + b64 * E.strideC + (int64_t)row * E.ldc + col;
+          const bool fast = c_vec && col + 3 < N;
+          if (E.mode == kEpiLerp) {
+            if (fast) {
+              const float4 o = *(const float4*)cp;
+              x[0] = o.x + (x[0] - o.x) * E.w; x[1] = o.y + (x[1] - o.y) * E.w;
+              x[2] = o.z + (x[2] - o.z) * E.w; x[3] = o.w + (x[3] - o.w) * E.w;
+            } else {
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                if (col + e < N) { const float o = cp[e]; x[e] = o + (x[e] - o) * E.w; }
+            }
+          }
+          if (fast) {
+            *(float4*)cp = make_float4(x[0], x[1], x[2], x[3]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (col + e < N) cp[e] = x[e];
           }
         }
       }
+      if (s_rows && row < M && col < E.kpS) {  // operand rows = output rows, K over the output columns (zero from N to kp)
+        float* srow = E.S + b64 * E.strideS + (int64_t)row * (2 * E.kpS) + col;
+        float hi[4], lo[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float y = col + e < N ? x[e] : 0.f;
+          hi[e] = tf32_hi(y);
+          lo[e] = tf32_hi(y - hi[e]);
+        }
+        *(float4*)srow = make_float4(hi[0], hi[1], hi[2], hi[3]);
+        *(float4*)(srow + E.kpS) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+      }
+      if (along_rows) *(float4*)sp = make_float4(x[0], x[1], x[2], x[3]);
     }
 
-    if (E.C != nullptr && row < M) {
-      float* crow = E.C + b64 * E.strideC + (int64_t)row * E.ldc;
+    if (along_rows) {
+      __syncwarp();
+      const int row = row0 + lane;
+      float v[32];
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
-        const int col = col0 + q * 4;
-        if (col >= N) break;
-        const bool fast = c_vec && col + 3 < N;
-        if (E.mode == kEpiLerp) {
-          if (fast) {
-            const float4 o = *(const float4*)(crow + col);
-            v[q * 4] = o.x + (v[q * 4] - o.x) * E.w; v[q * 4 + 1] = o.y + (v[q * 4 + 1] - o.y) * E.w;
-            v[q * 4 + 2] = o.z + (v[q * 4 + 2] - o.z) * E.w; v[q * 4 + 3] = o.w + (v[q * 4 + 3] - o.w) * E.w;
-          } else {
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-              if (col + e < N) { const float o = crow[col + e]; v[q * 4 + e] = o + (v[q * 4 + e] - o) * E.w; }
-          }
-        }
-        if (fast) {
-          *(float4*)(crow + col) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-        } else {
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            if (col + e < N) crow[col + e] = v[q * 4 + e];
-        }
+        const float4 t = *(const float4*)(mine + q * 4);
+        v[q * 4] = t.x; v[q * 4 + 1] = t.y; v[q * 4 + 2] = t.z; v[q * 4 + 3] = t.w;
       }
-    }
-
-    if (E.S != nullptr) {
-      float* sb = E.S + b64 * E.strideS;
-      const int64_t ld = 2 * E.kpS;
-      if (!E.s_transposed) {  // operand rows = output rows, K runs over the output columns (zero from N up to kp)
-        if (row < M) {
-          float* srow = sb + (int64_t)row * ld;
+      if (mirror && row < M) {  // consecutive lanes hold consecutive rows: one accumulator column is one contiguous line
+        float* ccol = E.C + b64 * E.strideC + row;
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            const int col = col0 + q * 4;
-            if (col >= E.kpS) break;
-            float hi[4], lo[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float x = col + e < N ? v[q * 4 + e] : 0.f;
-              hi[e] = tf32_hi(x);
-              lo[e] = tf32_hi(x - hi[e]);
-            }
-            *(float4*)(srow + col) = make_float4(hi[0], hi[1], hi[2], hi[3]);
-            *(float4*)(srow + E.kpS + col) = make_float4(lo[0], lo[1], lo[2], lo[3]);
-          }
-        }
-      } else if (row < E.kpS) {  // operand rows = output columns, K runs over the output rows (zero from M up to kp)
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < N) ccol[(int64_t)(col0 + j) * E.ldc] = v[j];
+      }
+      if (E.S != nullptr && E.s_transposed && row < E.kpS) {
+        // operand rows = output columns, K over the output rows (zero from M up to kp)
+        float* sb = E.S + b64 * E.strideS + row;
+        const int64_t ld = 2 * E.kpS;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          const int col = col0 + j;
-          if (col < N) {
-            const float x = row < M ? v[j] : 0.f;
-            const float hi = tf32_hi(x);
-            float* dst = sb + (int64_t)col * ld + row;
+          if (col0 + j < N) {
+            const float y = row < M ? v[j] : 0.f;
+            const float hi = tf32_hi(y);
+            float* dst = sb + (int64_t)(col0 + j) * ld;
             dst[0] = hi;
-            dst[E.kpS] = tf32_hi(x - hi);
+            dst[E.kpS] = tf32_hi(y - hi);
           }
         }
       }
     }
+    __syncwarp();  // the stage is rewritten by the next block of columns
   }
 }
 
@@ -194,7 +222,14 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int tiles_n = (N + TBN - 1) / TBN;
-  const int tm = blockIdx.x / tiles_n, tn = blockIdx.x % tiles_n, batch = blockIdx.y;
+  int tm = blockIdx.x / tiles_n, tn = blockIdx.x % tiles_n;
+  if (E.symmetric) {  // blockIdx.x counts the tiles on or above the diagonal, row by row
+    int left = blockIdx.x;
+    tm = 0;
+    while (left >= tiles_n - tm) { left -= tiles_n - tm; ++tm; }
+    tn = tm + left;
+  }
+  const int batch = blockIdx.y;
   const int seg_kb = kp / TBK;      // K blocks per term of the split product
   const int num_kb = 3 * seg_kb;    // hi*hi, hi*lo, lo*hi
   const float alpha = E.alpha;
@@ -262,7 +297,7 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                           __uint_as_float(acc[q * 4 + 2]) * alpha, __uint_as_float(acc[q * 4 + 3]) * alpha);
       }
     } else if (have) {
-      epilogue_direct(tmem_base, quarter, r, tm, tn, batch, M, N, E);
+      epilogue_direct(tmem_base, quarter, lane, (float*)(tiles + quarter * kStageWarpBytes), tm, tn, batch, M, N, E);
     }
     tc_fence_before();
     if (bulk_store) {
@@ -395,16 +430,19 @@ cudaError_t launch_tf32_gemm(const float* A2, const float* B2, int M, int N, int
   if (M == 0 || N == 0 || batch == 0) return cudaSuccess;
   if ((E.mode == kEpiAdam || E.mode == kEpiLaProp) && (E.m == nullptr || E.v == nullptr)) return cudaErrorInvalidValue;
   if (E.mode == kEpiLerp && E.C == nullptr) return cudaErrorInvalidValue;
+  if (E.symmetric && (A2 != B2 || M != N || E.C == nullptr || E.S != nullptr || (E.mode != kEpiStore && E.mode != kEpiLerp)))
+    return cudaErrorInvalidValue;
   const int64_t kp = tf32_split_kp(K), ld = 2 * kp;
   // plain products leave through the bulk-store path; everything else is written by the epilogue threads themselves
-  const int bulk = (E.mode == kEpiStore && E.S == nullptr && E.C != nullptr && (E.ldc & 3) == 0 && (E.strideC & 3) == 0 &&
+  const int bulk = (!E.symmetric && E.mode == kEpiStore && E.S == nullptr && E.C != nullptr && (E.ldc & 3) == 0 && (E.strideC & 3) == 0 &&
                     (((uintptr_t)E.C) & 15) == 0) ? 1 : 0;
   CUtensorMap ma, mb, mc;
   if (!make_f32_map(&ma, A2, M, ld, ld, (int64_t)M * ld, batch) || !make_f32_map(&mb, B2, N, ld, ld, (int64_t)N * ld, batch))
     return cudaErrorInvalidValue;
   mc = ma;  // placeholder when the bulk-store path is not taken (never dereferenced then)
   if (bulk && !make_f32_map(&mc, E.C, M, N, E.ldc, E.strideC, batch)) return cudaErrorInvalidValue;
-  dim3 grid(((M + TBM - 1) / TBM) * ((N + TBN - 1) / TBN), batch);
+  const int tiles_m = (M + TBM - 1) / TBM, tiles_n = (N + TBN - 1) / TBN;
+  dim3 grid(E.symmetric ? tiles_n * (tiles_n + 1) / 2 : tiles_m * tiles_n, batch);
   tf32_gemm_kernel<<<grid, kTThreads, kTSmemBytes, stream>>>(ma, mb, mc, M, N, (int)kp, E, bulk, status);
   return cudaGetLastError();
 }

@@ -37,6 +37,8 @@ struct Tf32Epilogue {
   int s_transposed;        // 0: operand rows = output rows, K = N; 1: operand rows = output columns, K = M
   float* m;                // kEpiAdam / kEpiLaProp state, fp32 [batch, M, N] contiguous
   float* v;
+  int symmetric;           // A2 == B2 (so M == N and the product is symmetric): only tiles on or above the diagonal are
+                           // computed and each is also stored transposed.  kEpiStore / kEpiLerp with C set and S null.
 };
 
 // out[b] = epilogue(A[b] * B[b]^T) over split operands A2: [batch, M, 2 * kp(K)], B2: [batch, N, 2 * kp(K)].

@@ -70,16 +70,49 @@ def test_split_outputs_feed_the_next_product(B, M, N, K):
     assert float((out.double() - want2).abs().max()) < 3e-5 * float((want.abs() @ c.double().abs().transpose(1, 2)).max())
 
 
-@pytest.mark.parametrize("B,M,N,K", [(2, 256, 256, 128), (2, 136, 136, 200)])
-def test_lerp_epilogue(B, M, N, K):
+@pytest.mark.parametrize("B,M,K", [(2, 256, 128), (2, 136, 200), (3, 520, 96), (1, 1024, 160)])
+def test_lerp_epilogue_on_a_symmetric_product(B, M, K):
+    """``GG <- lerp(GG, X X^T)`` with one buffer as both operands: only the tiles on or above the diagonal are computed,
+    each is stored mirrored as well, and the statistics stay exactly symmetric."""
     x = _rand(B, M, K, seed=6)
     x_s, _ = ops.tf32_split(x, True, False)
     gg = _rand(B, M, M, seed=7)
+    gg = (gg + gg.transpose(1, 2)) / 2
     want = gg.double() + (x.double() @ x.double().transpose(1, 2) - gg.double()) * 0.25
     ops.tf32_gemm(x_s, x_s, K, mode=ops.EPI_LERP, w=0.25, out=gg)
     torch.cuda.synchronize()
     ops.check_status()
     assert float((gg.double() - want).abs().max()) < _tol(x.double(), x.double())
+    assert torch.equal(gg, gg.transpose(1, 2))
+
+
+def test_lerp_epilogue_with_distinct_operands_updates_every_tile():
+    B, M, K = 2, 264, 128
+    a, b = _rand(B, M, K, seed=12), _rand(B, M, K, seed=13)
+    a_s, _ = ops.tf32_split(a, True, False)
+    b_s, _ = ops.tf32_split(b, True, False)
+    c = _rand(B, M, M, seed=14)
+    want = c.double() + (a.double() @ b.double().transpose(1, 2) - c.double()) * 0.5
+    ops.tf32_gemm(a_s, b_s, K, mode=ops.EPI_LERP, w=0.5, out=c)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert float((c.double() - want).abs().max()) < _tol(a.double(), b.double())
+
+
+@pytest.mark.parametrize("B,M,K,pad", [(2, 384, 256, 0), (2, 200, 136, 8)])
+def test_symmetric_store(B, M, K, pad):
+    x = _rand(B, M, K, seed=15)
+    x_s, _ = ops.tf32_split(x, True, False)
+    buf = torch.full((B, M, M + pad), 7.0, device="cuda")
+    out = buf[:, :, :M]
+    ops.tf32_gemm(x_s, x_s, K, out=out, alpha=2.0)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = 2.0 * (x.double() @ x.double().transpose(1, 2))
+    assert float((out.double() - want).abs().max()) < 2 * _tol(x.double(), x.double())
+    assert torch.equal(out, out.transpose(1, 2))
+    if pad:
+        assert float((buf[:, :, M:] - 7.0).abs().max()) == 0
 
 
 @pytest.mark.parametrize("mode", ["adam", "laprop"])

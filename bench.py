@@ -100,8 +100,8 @@ def parse(argv=None):
                     help="also run the plain-model measurement and the other configurations as child processes "
                          "(auto = only for the default configuration)")
     ap.add_argument("--secondary-steps", type=int, default=4)
-    ap.add_argument("--secondary-timeout", type=float, default=420.0, help="seconds per child process")
-    ap.add_argument("--secondary-budget", type=float, default=1000.0, help="seconds for all child processes together")
+    ap.add_argument("--secondary-timeout", type=float, default=600.0, help="seconds per child process")
+    ap.add_argument("--secondary-budget", type=float, default=1300.0, help="seconds for all child processes together")
     ap.add_argument("--reference-compile-mode", default=None,
                     help="reference arm: value for heavyball.utils.compile_mode ('none' = eager); default = stock")
     return ap.parse_args(argv)
@@ -356,8 +356,21 @@ def run_config(args):
             if ours:
                 from heavyball_b200.parallel import ddp as hb_ddp
 
-                train_model = hb_ddp.wrap(model, opt, mode=args.ddp_mode)
-                parallel_note = f"data parallel, gradient path {args.ddp_mode}"
+                mode, why = args.ddp_mode, ""
+                try:
+                    train_model = hb_ddp.wrap(model, opt, mode=mode)
+                except Exception as err:  # noqa: BLE001  (e.g. no symmetric memory between these GPUs)
+                    if mode != "peer":
+                        raise
+                    train_model, why = None, f"{type(err).__name__}: {str(err)[:200]}"
+                agreed = torch.tensor([0 if train_model is None else 1], device=device)
+                dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+                if int(agreed.item()) == 0:
+                    if train_model is not None:
+                        raise RuntimeError("peer data parallelism came up on this rank but not on all ranks")
+                    mode = "nccl"
+                    train_model = hb_ddp.wrap(model, opt, mode=mode)
+                parallel_note = f"data parallel, gradient path {mode}" + (f" (peer path unavailable: {why})" if why else "")
                 ctx = getattr(opt, "_peer", None) or next((getattr(o, "_peer", None) for o in getattr(opt, "optimizers", [])), None)
                 if ctx is not None:
                     parallel_note += ", NVSwitch multimem reduce / broadcast" if ctx.multicast else ", per-rank peer loads / stores"
@@ -559,15 +572,18 @@ def run_config(args):
             "config": {
                 "model": args.config, "global_batch": B * world, "seq_len": T,
                 "parallelism": f"{cfg['parallelism']}{world}",
-                "parallel_impl": parallel_note,
                 "optimizer": OPTIMIZER_TEXT[cfg["optimizer"]],
                 "precision": ("bf16 autocast, fp32 master weights" if autocast else "bf16 parameters and compute"),
                 "vocab_rows": vocab_rows(cfg),
                 "parameters": n_params,
+                "l2": "per-step working set (activations, parameters, optimizer state) exceeds the 126 MB L2",
+            },
+            # how this arm runs the workload above (the workload itself is identical in both arms)
+            "implementation": {
+                "parallel_impl": parallel_note,
                 "model_impl": ("heavyball_b200.models (own LayerNorm / GELU / head+loss kernels)" if model_kind == "native"
                                else "baseline/ref_model.py (plain torch.nn)"),
                 "cuda_graphs": "forward and backward replayed from CUDA graphs, optimizer launched eagerly" if graphed else "none",
-                "l2": "per-step working set (activations, parameters, optimizer state) exceeds the 126 MB L2",
                 "reference_compile": compile_note,
             },
             "clocks": clocks,
@@ -647,7 +663,7 @@ def _brief(rec):
     """The fields of a child's line that the parent's line keeps."""
     keep = ("impl", "value", "unit", "n_gpus", "steps", "warmup", "windows", "ms_per_step", "optimizer_step_ms",
             "optimizer_step_max_ms", "fwd_bwd_ms", "clocks", "e2e", "gpu_launches", "final_loss", "unavailable",
-            "seconds", "config", "roofline", "note")  # fmt: skip
+            "seconds", "config", "implementation", "roofline", "note")  # fmt: skip
     return {k: rec[k] for k in keep if k in rec}
 
 

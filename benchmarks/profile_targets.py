@@ -11,6 +11,8 @@
     python benchmarks/profile_targets.py ns_big          # Newton-Schulz on 4 x (4096 x 4096): the 256 x 256-tile kernel
     python benchmarks/profile_targets.py soap_small      # one plain SOAP step on 8 x 1024^2 (tf32 GEMMs with fused epilogues)
     python benchmarks/profile_targets.py psgd_small      # one plain PSGDKron step on 8 x 1024^2 (cached P = Q^T Q operands)
+    python benchmarks/profile_targets.py psgd_fit        # one PSGDKron step with a preconditioner fit, 8 x (1024 x 4096)
+    python benchmarks/profile_targets.py soap_refresh    # one SOAP step with an eigenbasis refresh, 4 x (2048 x 5504)
 
 Each case holds well under a few GB on the device and launches only a handful of kernels.
 """
@@ -209,8 +211,8 @@ def ns_big():
     print(float(out.abs().mean()))
 
 
-def _second_order(cls, **kw):
-    params = [torch.nn.Parameter(torch.randn(1024, 1024, device="cuda")) for _ in range(8)]
+def _second_order(cls, shape=(1024, 1024), count=8, **kw):
+    params = [torch.nn.Parameter(torch.randn(*shape, device="cuda")) for _ in range(count)]
     opt = cls(params, lr=1e-3, **kw)
     grads = [torch.randn_like(p) for p in params]
 
@@ -250,6 +252,31 @@ def psgd_small():
     ops.check_status()
 
 
+def _periodic(cls, shape, count, label, **kw):
+    """Times and exposes one step that includes the periodic stage (fit / refresh): the schedule is set so that every
+    step does it; the first two run eagerly / are captured, the profiled one is the steady state."""
+    opt, one_step = _second_order(cls, shape, count, **kw)
+    for _ in range(4):
+        one_step()
+    us = _timed(one_step, reps=3)
+    print(f"{label} {count}x{shape[0]}x{shape[1]}: {us:.0f} us")
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    one_step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    ops.check_status()
+
+
+def psgd_fit():
+    _periodic(hb.PSGDKron, (1024, 4096), 8, "PSGDKron step with fit", preconditioner_update_probability=1.0,
+              max_size_triangular=8192)
+
+
+def soap_refresh():
+    _periodic(hb.SOAP, (2048, 5504), 4, "SOAP step with refresh", precondition_frequency=1, max_precond_dim=8192)
+
+
 if __name__ == "__main__":
-    {"ns_big": ns_big, "soap_small": soap_small, "psgd_small": psgd_small, "qr_small": qr_small, "opt_step_gpt2": opt_step_gpt2, "ns_small": ns_small, "adam_small": adam_small, "ce_small": ce_small,
+    {"psgd_fit": psgd_fit, "soap_refresh": soap_refresh, "ns_big": ns_big, "soap_small": soap_small, "psgd_small": psgd_small, "qr_small": qr_small, "opt_step_gpt2": opt_step_gpt2, "ns_small": ns_small, "adam_small": adam_small, "ce_small": ce_small,
      "ln_small": ln_small, "tf32_small": tf32_small, "gelu_small": gelu_small}[sys.argv[1]]()

@@ -108,6 +108,9 @@ def load():
             tile = os.environ.get("HB200_NS_TILE")  # tuning aid: force the 128 or 256 output tile of the Newton-Schulz GEMMs
             if tile:
                 _ext.set_ns_gemm_tile(int(tile))
+            tile = os.environ.get("HB200_TF32_TILE")  # same for the split-tf32 GEMM
+            if tile:
+                _ext.set_tf32_gemm_tile(int(tile))
         except BaseException as err:  # noqa: BLE001
             _load_error = err
             raise RuntimeError(

@@ -531,5 +531,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ns_prepare", &ns_prepare);
   m.def("ns_gemm", &ns_gemm);
   m.def("set_ns_gemm_tile", &hb::set_ns_gemm_tile_override);
+  m.def("set_tf32_gemm_tile", &hb::set_tf32_gemm_tile_override);
   m.def("chunk_elems", &hb::chain_chunk_elems);
 }

@@ -61,25 +61,26 @@ constexpr int kStageWarpBytes = 32 * kStageLd * 4;   // one warp's 32 rows x 32 
 //   pass 3 (lane = row):                   outputs that run along the rows: transposed split operand, mirror tile
 // Values outside [M, N] are never stored; the zero padding of a split output (columns [K, kp) of the operand being
 // produced) is.
-__device__ __forceinline__ void epilogue_direct(uint32_t tmem_base, int quarter, int lane, float* stage, int tm, int tn,
-                                                int batch, int M, int N, const Tf32Epilogue& E) {
-  const int row0 = tm * TBM + quarter * 32;
+// `tmem_warp`: tensor-memory address of the warp's first row and the tile's first column; `row0` / `col_base`: their
+// global indices; `n_cb`: 32-column blocks in the tile; `off_diagonal`: the tile is not on the diagonal (mirror stores).
+__device__ __forceinline__ void epilogue_direct(uint32_t tmem_warp, int lane, float* stage, int row0, int col_base, int n_cb,
+                                                bool off_diagonal, int batch, int M, int N, const Tf32Epilogue& E) {
   const int64_t b64 = batch;
   const bool state_vec = (N & 3) == 0;
   const bool c_vec = (E.ldc & 3) == 0 && ((E.strideC & 3) == 0) && ((((uintptr_t)E.C) & 15) == 0);
   const bool moments = E.mode == kEpiAdam || E.mode == kEpiLaProp;
-  const bool mirror = E.symmetric && tm != tn && E.C != nullptr;
+  const bool mirror = E.symmetric && off_diagonal && E.C != nullptr;
   const bool along_rows = mirror || (E.S != nullptr && E.s_transposed);
   const bool s_rows = E.S != nullptr && !E.s_transposed;
   const int sub = lane >> 3, cg = (lane & 7) * 4;
   const float w1 = 1.0f - E.b1, w2 = 1.0f - E.b2;
   float* mine = stage + lane * kStageLd;
 #pragma unroll 1
-  for (int cb = 0; cb < TBN / 32; ++cb) {
-    const int col0 = tn * TBN + cb * 32;
+  for (int cb = 0; cb < n_cb; ++cb) {
+    const int col0 = col_base + cb * 32;
     {
       uint32_t acc[32];
-      tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cb * 32), acc);
+      tmem_ld32(tmem_warp + (uint32_t)(cb * 32), acc);
       tmem_ld_wait();
 #pragma unroll
       for (int q = 0; q < 8; ++q)
@@ -297,7 +298,8 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                           __uint_as_float(acc[q * 4 + 2]) * alpha, __uint_as_float(acc[q * 4 + 3]) * alpha);
       }
     } else if (have) {
-      epilogue_direct(tmem_base, quarter, lane, (float*)(tiles + quarter * kStageWarpBytes), tm, tn, batch, M, N, E);
+      epilogue_direct(tmem_base + ((uint32_t)(quarter * 32) << 16), lane, (float*)(tiles + quarter * kStageWarpBytes),
+                      tm * TBM + quarter * 32, tn * TBN, TBN / 32, tm != tn, batch, M, N, E);
     }
     tc_fence_before();
     if (bulk_store) {
@@ -323,6 +325,119 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   __syncthreads();
   if (threadIdx.x == 0 && abort_flag && status != nullptr) atomicExch(status, 1);
   if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, kTTmemCols); }
+}
+
+// ------------------------------------------------------------------------------------------ 256 x 256 tiles
+// A 128 x 128 tile asks the L2 for 32 KiB of operands per 256 tensor-core cycles (tf32 runs at half the bf16 rate on
+// operands twice as wide), which is more than the L2 delivers to 148 SMs at once; a 256 x 256 tile needs half of that
+// per FLOP.  One CTA per SM: four 128 x 128 fp32 accumulators = all 512 columns of tensor memory, 64 KiB ring stages
+// (two 128-row boxes per operand), two 128 x 256 x 8 instructions per 8 of K sharing the B rows.  Eight epilogue
+// warps: two per 32-lane quarter of tensor memory, one for each 128-row half of the tile.
+constexpr int TBM2 = 256, TBN2 = 256;
+constexpr int kTStageBytes2 = 4 * kTTileBytes;                  // 64 KiB
+constexpr int kTSmemBytes2 = kTStages * kTStageBytes2 + 1024;
+constexpr int kTThreads2 = 320;                                 // producer, MMA, 8 epilogue warps
+constexpr uint32_t kTTmemCols2 = 512;
+constexpr uint32_t kTf32InstrDesc256 =
+    (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(TBN2 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+
+__global__ void __launch_bounds__(kTThreads2, 1)
+tf32_gemm256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, int M, int N, int kp,
+                    const Tf32Epilogue E, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kTStages];
+  __shared__ __align__(8) uint64_t empty_bar[kTStages];
+  __shared__ __align__(8) uint64_t accum_bar;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  if (status != nullptr && *(volatile const int*)status != 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int tiles_n = (N + TBN2 - 1) / TBN2;
+  int tm = blockIdx.x / tiles_n, tn = blockIdx.x % tiles_n;
+  if (E.symmetric) {
+    int left = blockIdx.x;
+    tm = 0;
+    while (left >= tiles_n - tm) { left -= tiles_n - tm; ++tm; }
+    tn = tm + left;
+  }
+  const int batch = blockIdx.y;
+  const int seg_kb = kp / TBK;
+  const int num_kb = 3 * seg_kb;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kTStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(&accum_bar, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) { tmem_alloc(&tmem_base_slot, kTTmemCols2); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  int issued = 0;
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % kTStages, round = kb / kTStages;
+        if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &abort_flag)) break;
+        uint8_t* dst = tiles + s * kTStageBytes2;
+        const int seg = kb / seg_kb, k0 = (kb - seg * seg_kb) * TBK;
+        const int ka = k0 + (seg == 2 ? kp : 0), kb_col = k0 + (seg == 1 ? kp : 0);   // A: hi, hi, lo   B: hi, lo, hi
+        mbar_expect_tx(&full_bar[s], kTStageBytes2);   // rows past the operand's end arrive as zeros and count as bytes
+        tma_load_3d(dst, &map_a, &full_bar[s], ka, tm * TBM2, batch);
+        tma_load_3d(dst + kTTileBytes, &map_a, &full_bar[s], ka, tm * TBM2 + 128, batch);
+        tma_load_3d(dst + 2 * kTTileBytes, &map_b, &full_bar[s], kb_col, tn * TBN2, batch);
+        tma_load_3d(dst + 3 * kTTileBytes, &map_b, &full_bar[s], kb_col, tn * TBN2 + 128, batch);
+        issued = kb + 1;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % kTStages, round = kb / kTStages;
+        ok = mbar_wait(&full_bar[s], round & 1, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t base = smem_u32(tiles + s * kTStageBytes2);
+        const uint64_t a_top = make_smem_desc(base), a_bot = make_smem_desc(base + kTTileBytes);
+        // 256 B rows = 32 eight-row groups, 1 KiB apart: the two 128-row boxes are contiguous
+        const uint64_t b_desc = make_smem_desc(base + 2 * kTTileBytes);
+#pragma unroll
+        for (int k = 0; k < TBK / 8; ++k) {
+          const uint32_t acc = (kb | k) ? 1u : 0u;
+          tc_mma_tf32(tmem_base, a_top + 2 * k, b_desc + 2 * k, kTf32InstrDesc256, acc);
+          tc_mma_tf32(tmem_base + 256u, a_bot + 2 * k, b_desc + 2 * k, kTf32InstrDesc256, acc);
+        }
+        tc_commit(&empty_bar[s]);
+      }
+      if (ok) tc_commit(&accum_bar);
+    }
+  } else {
+    const int quarter = warp & 3, half = (warp - 2) >> 2;   // warps 2..5: rows 0..127 of the tile, warps 6..9: rows 128..255
+    const bool have = (num_kb == 0) || mbar_wait(&accum_bar, 0, &abort_flag);
+    tc_fence_after();
+    const int row0 = tm * TBM2 + half * 128 + quarter * 32;
+    if (have && row0 < M)
+      epilogue_direct(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 256), lane,
+                      (float*)(tiles + (warp - 2) * kStageWarpBytes), row0, tn * TBN2, TBN2 / 32, tm != tn, batch, M, N, E);
+    tc_fence_before();
+  }
+
+  if (warp == 0 && lane == 0 && abort_flag) {
+    for (int kb = max(0, issued - kTStages); kb < issued; ++kb) {
+      const int s = kb % kTStages, round = kb / kTStages;
+      for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+        if (mbar_try_wait(&full_bar[s], round & 1)) break;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && abort_flag && status != nullptr) atomicExch(status, 1);
+  if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, kTTmemCols2); }
 }
 
 // One block moves a 64 x 64 tile of the source through shared memory and writes the [hi | lo] rows it covers of either
@@ -419,11 +534,17 @@ cudaError_t launch_tf32_split(const float* src, int64_t ld_src, int64_t stride_s
   return cudaGetLastError();
 }
 
+static int g_tf32_tile_override = 0;  // 0 = by size, 128 / 256 = forced (tests and measurements)
+int tf32_gemm_tile_override() { return g_tf32_tile_override; }
+void set_tf32_gemm_tile_override(int tile) { g_tf32_tile_override = (tile == 128 || tile == 256) ? tile : 0; }
+
 cudaError_t launch_tf32_gemm(const float* A2, const float* B2, int M, int N, int K, int batch, const Tf32Epilogue& E,
                              int* status, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(tf32_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTSmemBytes);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(tf32_gemm256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTSmemBytes2);
     if (e != cudaSuccess) return e;
     configured = true;
   }
@@ -433,12 +554,26 @@ cudaError_t launch_tf32_gemm(const float* A2, const float* B2, int M, int N, int
   if (E.symmetric && (A2 != B2 || M != N || E.C == nullptr || E.S != nullptr || (E.mode != kEpiStore && E.mode != kEpiLerp)))
     return cudaErrorInvalidValue;
   const int64_t kp = tf32_split_kp(K), ld = 2 * kp;
-  // plain products leave through the bulk-store path; everything else is written by the epilogue threads themselves
-  const int bulk = (!E.symmetric && E.mode == kEpiStore && E.S == nullptr && E.C != nullptr && (E.ldc & 3) == 0 && (E.strideC & 3) == 0 &&
-                    (((uintptr_t)E.C) & 15) == 0) ? 1 : 0;
   CUtensorMap ma, mb, mc;
   if (!make_f32_map(&ma, A2, M, ld, ld, (int64_t)M * ld, batch) || !make_f32_map(&mb, B2, N, ld, ld, (int64_t)N * ld, batch))
     return cudaErrorInvalidValue;
+
+  // big tiles once there are enough of them to fill the machine (one CTA per SM) and K is long enough to pay for a
+  // serial epilogue; small problems keep 128 x 128 tiles, two CTAs per SM
+  const int big_m = (M + TBM2 - 1) / TBM2, big_n = (N + TBN2 - 1) / TBN2;
+  const int64_t big_tiles = (int64_t)(E.symmetric ? big_n * (big_n + 1) / 2 : big_m * big_n) * batch;
+  bool big = M >= TBM2 && N >= TBN2 && K >= 512 && big_tiles >= 96;
+  if (g_tf32_tile_override == 128) big = false;
+  if (g_tf32_tile_override == 256) big = true;
+  if (big) {
+    dim3 grid(E.symmetric ? big_n * (big_n + 1) / 2 : big_m * big_n, batch);
+    tf32_gemm256_kernel<<<grid, kTThreads2, kTSmemBytes2, stream>>>(ma, mb, M, N, (int)kp, E, status);
+    return cudaGetLastError();
+  }
+
+  // plain products leave through the bulk-store path; everything else is written by the epilogue threads themselves
+  const int bulk = (!E.symmetric && E.mode == kEpiStore && E.S == nullptr && E.C != nullptr && (E.ldc & 3) == 0 &&
+                    (E.strideC & 3) == 0 && (((uintptr_t)E.C) & 15) == 0) ? 1 : 0;
   mc = ma;  // placeholder when the bulk-store path is not taken (never dereferenced then)
   if (bulk && !make_f32_map(&mc, E.C, M, N, E.ldc, E.strideC, batch)) return cudaErrorInvalidValue;
   const int tiles_m = (M + TBM - 1) / TBM, tiles_n = (N + TBN - 1) / TBN;

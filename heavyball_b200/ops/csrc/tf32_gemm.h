@@ -46,4 +46,8 @@ struct Tf32Epilogue {
 cudaError_t launch_tf32_gemm(const float* A2, const float* B2, int M, int N, int K, int batch, const Tf32Epilogue& E,
                              int* status, cudaStream_t stream);
 
+// Tile choice of launch_tf32_gemm: 0 = by problem size, 128 or 256 = forced.
+int tf32_gemm_tile_override();
+void set_tf32_gemm_tile_override(int tile);
+
 }  // namespace hb

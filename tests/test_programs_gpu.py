@@ -9,6 +9,15 @@ from heavyball_b200 import lowering, ops
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=[0, 128, 256], ids=["tile-auto", "tile-128", "tile-256"])
+def tile(request):
+    """Runs a GEMM-level test with the tile size chosen by problem size and with each tile size forced."""
+    ext = ops.load()
+    ext.set_tf32_gemm_tile(request.param)
+    yield request.param
+    ext.set_tf32_gemm_tile(0)
+
+
 def _rand(*shape, seed):
     g = torch.Generator(device="cuda").manual_seed(seed)
     return torch.randn(*shape, device="cuda", generator=g)
@@ -25,7 +34,7 @@ def _tol(a, b):
 
 
 @pytest.mark.parametrize("B,M,N,K", [(2, 256, 128, 384), (3, 200, 136, 160), (1, 129, 300, 130)])
-def test_split_and_plain_product(B, M, N, K):
+def test_split_and_plain_product(B, M, N, K, tile):
     a, b = _rand(B, M, K, seed=1), _rand(B, N, K, seed=2)
     a_s, a_t = ops.tf32_split(a, True, True)
     assert torch.allclose(_unsplit(a_s, K), a.double(), atol=1e-6)
@@ -42,7 +51,7 @@ def test_split_and_plain_product(B, M, N, K):
 
 
 @pytest.mark.parametrize("B,M,N,K", [(2, 256, 128, 256), (2, 200, 136, 160)])
-def test_split_outputs_feed_the_next_product(B, M, N, K):
+def test_split_outputs_feed_the_next_product(B, M, N, K, tile):
     a, b = _rand(B, M, K, seed=3), _rand(B, N, K, seed=4)
     a_s, _ = ops.tf32_split(a, True, False)
     b_s, _ = ops.tf32_split(b, True, False)
@@ -71,7 +80,7 @@ def test_split_outputs_feed_the_next_product(B, M, N, K):
 
 
 @pytest.mark.parametrize("B,M,K", [(2, 256, 128), (2, 136, 200), (3, 520, 96), (1, 1024, 160)])
-def test_lerp_epilogue_on_a_symmetric_product(B, M, K):
+def test_lerp_epilogue_on_a_symmetric_product(B, M, K, tile):
     """``GG <- lerp(GG, X X^T)`` with one buffer as both operands: only the tiles on or above the diagonal are computed,
     each is stored mirrored as well, and the statistics stay exactly symmetric."""
     x = _rand(B, M, K, seed=6)
@@ -86,7 +95,7 @@ def test_lerp_epilogue_on_a_symmetric_product(B, M, K):
     assert torch.equal(gg, gg.transpose(1, 2))
 
 
-def test_lerp_epilogue_with_distinct_operands_updates_every_tile():
+def test_lerp_epilogue_with_distinct_operands_updates_every_tile(tile):
     B, M, K = 2, 264, 128
     a, b = _rand(B, M, K, seed=12), _rand(B, M, K, seed=13)
     a_s, _ = ops.tf32_split(a, True, False)
@@ -100,7 +109,7 @@ def test_lerp_epilogue_with_distinct_operands_updates_every_tile():
 
 
 @pytest.mark.parametrize("B,M,K,pad", [(2, 384, 256, 0), (2, 200, 136, 8)])
-def test_symmetric_store(B, M, K, pad):
+def test_symmetric_store(B, M, K, pad, tile):
     x = _rand(B, M, K, seed=15)
     x_s, _ = ops.tf32_split(x, True, False)
     buf = torch.full((B, M, M + pad), 7.0, device="cuda")
@@ -117,7 +126,7 @@ def test_symmetric_store(B, M, K, pad):
 
 @pytest.mark.parametrize("mode", ["adam", "laprop"])
 @pytest.mark.parametrize("B,M,N,K", [(2, 256, 128, 256), (2, 200, 138, 160)])
-def test_moment_epilogues(mode, B, M, N, K):
+def test_moment_epilogues(mode, B, M, N, K, tile):
     a, b = _rand(B, M, K, seed=8), _rand(B, N, K, seed=9)
     a_s, _ = ops.tf32_split(a, True, False)
     b_s, _ = ops.tf32_split(b, True, False)

@@ -311,18 +311,17 @@ class SOAPBase(C.BaseOpt):
     use_precond_schedule: bool = False
 
     def _build_soap_defaults(self, locals_dict, fns):
-        scheduled = C.default(locals_dict["use_precond_schedule"], self.use_precond_schedule)
+        """Turns the constructor's arguments into group defaults and picks how often the eigenbases are refreshed:
+        a fixed period (``precondition_frequency``) or the decaying schedule (``precond_scheduler``); the option that
+        is not in use is dropped from the defaults."""
         params, defaults = C._build_defaults(locals_dict)
-        if scheduled:
-            del defaults["precondition_frequency"]
-            self.precond_schedule = utils.get_soap_precond_schedule(defaults.pop("precond_scheduler"))
+        period, scheduler = defaults.pop("precondition_frequency"), defaults.pop("precond_scheduler")
+        if C.default(locals_dict["use_precond_schedule"], self.use_precond_schedule):
+            self.precond_schedule = utils.get_soap_precond_schedule(scheduler)
         else:
-            del defaults["precond_scheduler"]
-            self.precond_schedule = 1 / defaults.pop("precondition_frequency")
-        C.BaseOpt.__init__(
-            self, params, defaults, locals_dict["gradient_clipping"], locals_dict["update_clipping"],
-            locals_dict.get("palm", False), fns=fns,
-        )  # fmt: skip
+            self.precond_schedule = 1 / period
+        clips = (locals_dict["gradient_clipping"], locals_dict["update_clipping"])
+        C.BaseOpt.__init__(self, params, defaults, *clips, locals_dict.get("palm", False), fns=fns)
 
 
 def _soap_body(self, L):
@@ -395,21 +394,20 @@ class PSGDBase(C.BaseOpt):
 
     def _build_psgd_defaults(self, locals_dict, fns, *, default_update_clipping=utils.trust_region_clip_,
                              extra_defaults=None):  # fmt: skip
-        exp_avg_input = C.default(locals_dict.get("exp_avg_input", D), self.exp_avg_input)
-        update_clipping = C.default(locals_dict["update_clipping"], default_update_clipping)
-        locals_dict = {**locals_dict, "exp_avg_input": exp_avg_input, "update_clipping": update_clipping}
-        params, defaults = C._build_defaults(locals_dict)
-        self.precond_schedule = C.default(
-            defaults.pop("preconditioner_update_probability"), utils.precond_update_prob_schedule()
-        )
-        if extra_defaults:
-            defaults.update(extra_defaults)
+        """Group defaults of the PSGD family.  Class attributes supply what the caller left at ``use_default``
+        (momentum in front of the preconditioner, trust-region clipping of the update); the fitting probability is
+        taken out of the defaults and kept as the schedule."""
+        resolved = dict(locals_dict)
+        resolved["exp_avg_input"] = C.default(locals_dict.get("exp_avg_input", D), self.exp_avg_input)
+        resolved["update_clipping"] = C.default(locals_dict["update_clipping"], default_update_clipping)
+        params, defaults = C._build_defaults(resolved)
+        probability = defaults.pop("preconditioner_update_probability")
+        self.precond_schedule = C.default(probability, utils.precond_update_prob_schedule())
+        defaults.update(extra_defaults or {})
         if self.sqrt:
-            defaults["sqrt"] = self.sqrt
-        C.BaseOpt.__init__(
-            self, params, defaults, locals_dict["gradient_clipping"], update_clipping, False,
-            fns=(*(C.exp_avg,) * exp_avg_input, *fns),
-        )  # fmt: skip
+            defaults["sqrt"] = True
+        chain = ((C.exp_avg,) if resolved["exp_avg_input"] else ()) + tuple(fns)
+        C.BaseOpt.__init__(self, params, defaults, resolved["gradient_clipping"], resolved["update_clipping"], False, fns=chain)
 
 
 def _kron_body(self, L):

@@ -592,6 +592,10 @@ def run_config(args):
             "roofline": roof,
             "final_loss": float(last.detach()),
         }  # fmt: skip
+    if ours and out is not None and cfg["optimizer"] == "soap":
+        from heavyball_b200.utils import orthogonal
+
+        out["implementation"]["eigenbasis_qr"] = dict(orthogonal.qr_stats)  # fast factorisation taken / refused
     if world > 1:
         dist.destroy_process_group()
     return out

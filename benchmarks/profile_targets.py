@@ -12,7 +12,7 @@
     python benchmarks/profile_targets.py soap_small      # one plain SOAP step on 8 x 1024^2 (tf32 GEMMs with fused epilogues)
     python benchmarks/profile_targets.py psgd_small      # one plain PSGDKron step on 8 x 1024^2 (cached P = Q^T Q operands)
     python benchmarks/profile_targets.py psgd_fit        # one PSGDKron step with a preconditioner fit, 8 x (1024 x 4096)
-    python benchmarks/profile_targets.py soap_refresh    # one SOAP step with an eigenbasis refresh, 4 x (2048 x 5504)
+    python benchmarks/profile_targets.py soap_refresh    # one SOAP step with an eigenbasis refresh, 8 x (2048 x 2048)
 
 Each case holds well under a few GB on the device and launches only a handful of kernels.
 """
@@ -211,13 +211,15 @@ def ns_big():
     print(float(out.abs().mean()))
 
 
-def _second_order(cls, shape=(1024, 1024), count=8, **kw):
+def _second_order(cls, shape=(1024, 1024), count=8, fresh_grads=False, **kw):
     params = [torch.nn.Parameter(torch.randn(*shape, device="cuda")) for _ in range(count)]
     opt = cls(params, lr=1e-3, **kw)
     grads = [torch.randn_like(p) for p in params]
 
     def one_step():
         for p, g in zip(params, grads):
+            if fresh_grads:  # statistics accumulated over different gradients are full rank, as in training
+                g.normal_()
             p.grad = g
         opt.step()
 
@@ -255,8 +257,8 @@ def psgd_small():
 def _periodic(cls, shape, count, label, **kw):
     """Times and exposes one step that includes the periodic stage (fit / refresh): the schedule is set so that every
     step does it; the first two run eagerly / are captured, the profiled one is the steady state."""
-    opt, one_step = _second_order(cls, shape, count, **kw)
-    for _ in range(4):
+    opt, one_step = _second_order(cls, shape, count, fresh_grads=True, **kw)
+    for _ in range(6):
         one_step()
     us = _timed(one_step, reps=3)
     print(f"{label} {count}x{shape[0]}x{shape[1]}: {us:.0f} us")
@@ -274,7 +276,10 @@ def psgd_fit():
 
 
 def soap_refresh():
-    _periodic(hb.SOAP, (2048, 5504), 4, "SOAP step with refresh", precondition_frequency=1, max_precond_dim=8192)
+    from heavyball_b200.utils import orthogonal
+
+    _periodic(hb.SOAP, (2048, 2048), 8, "SOAP step with refresh", precondition_frequency=1)
+    print("QR paths taken:", orthogonal.qr_stats)
 
 
 if __name__ == "__main__":

@@ -321,15 +321,18 @@ def tf32_gemm(a2: torch.Tensor, b2: torch.Tensor, K: int, *, mode: int = EPI_STO
     return s if split_out else None
 
 
-def matmul3(a: torch.Tensor, b: torch.Tensor, trans_a: bool = False, trans_b: bool = False, alpha: float = 1.0) -> torch.Tensor:
+def matmul3(a: torch.Tensor, b: torch.Tensor, trans_a: bool = False, trans_b: bool = False, alpha: float = 1.0,
+            upper_upper: bool = False) -> torch.Tensor:
     """``alpha * op(a) @ op(b)`` for fp32 matrices (optionally batched, equal leading shapes) on the tf32 tensor
-    cores with the 3-term split (measured error about 2^-18 of ``|a| @ |b|``; one tf32 pass gives 2^-11, fp32 SIMT 2^-21)."""
+    cores with the 3-term split (measured error about 2^-18 of ``|a| @ |b|``; one tf32 pass gives 2^-11, fp32 SIMT 2^-21).
+    ``upper_upper``: ``op(a)`` and ``op(b)`` are upper triangular matrices of one size (entries below their diagonals
+    ARE zero): a sixth of the tile products, and exact zeros below the diagonal of the result."""
     lead = a.shape[:-2]
     if b.shape[:-2] != lead:
         lead = torch.broadcast_shapes(a.shape[:-2], b.shape[:-2])
         a, b = a.expand(*lead, *a.shape[-2:]), b.expand(*lead, *b.shape[-2:])
     a3 = a.reshape(-1, *a.shape[-2:]).contiguous()
     b3 = b.reshape(-1, *b.shape[-2:]).contiguous()
-    out = load().tf32x3_matmul(a3, b3, trans_a, trans_b, alpha, _status(a.device))
+    out = load().tf32x3_matmul(a3, b3, trans_a, trans_b, alpha, _status(a.device), upper_upper)
     launch_counter.count += 3
     return out.reshape(*lead, *out.shape[-2:])

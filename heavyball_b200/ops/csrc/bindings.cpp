@@ -337,7 +337,10 @@ at::Tensor tf32_gemm(const at::Tensor& a2, const at::Tensor& b2, int64_t K, int 
 
 // op(a) @ op(b) for batched fp32 matrices on the split-tf32 tensor-core path.  a: [batch, R, C]; ta = 0 uses a as
 // [M, K], ta = 1 as [K, M]; likewise b is [K, N] for tb = 0 and [N, K] for tb = 1.  Returns [batch, M, N].
-at::Tensor tf32x3_matmul(const at::Tensor& a, const at::Tensor& b, bool ta, bool tb, double alpha, const at::Tensor& status) {
+// upper_upper: op(a) and op(b) are both upper triangular (square, same size): only the non-zero K range of every tile
+// is walked and the part below the diagonal comes back as zeros.
+at::Tensor tf32x3_matmul(const at::Tensor& a, const at::Tensor& b, bool ta, bool tb, double alpha, const at::Tensor& status,
+                         bool upper_upper) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == at::kFloat && b.scalar_type() == at::kFloat &&
                   a.dim() == 3 && b.dim() == 3 && a.is_contiguous() && b.is_contiguous() && a.size(0) == b.size(0),
               "tf32x3_matmul: contiguous fp32 [batch, rows, cols] CUDA tensors");
@@ -362,6 +365,11 @@ at::Tensor tf32x3_matmul(const at::Tensor& a, const at::Tensor& b, bool ta, bool
           "tf32 split B");
   hb::Tf32Epilogue E{};
   E.mode = hb::kEpiStore; E.alpha = (float)alpha; E.C = c.data_ptr<float>(); E.ldc = ldc; E.strideC = M * ldc;
+  E.symmetric = same_operand ? 1 : 0;  // X X^T / X^T X: upper tiles, mirrored on store
+  if (upper_upper) {
+    TORCH_CHECK(M == N && M == K && !same_operand, "tf32x3_matmul: upper_upper needs two square matrices of one size");
+    E.tri = 1;
+  }
   check(hb::launch_tf32_gemm(a2.data_ptr<float>(), b2.data_ptr<float>(), (int)M, (int)N, (int)K, (int)batch, E,
                              status.data_ptr<int>(), stream), "tf32 gemm");
   return ldc == N ? c : c.narrow(2, 0, N);

@@ -63,8 +63,10 @@ constexpr int kStageWarpBytes = 32 * kStageLd * 4;   // one warp's 32 rows x 32 
 // produced) is.
 // `tmem_warp`: tensor-memory address of the warp's first row and the tile's first column; `row0` / `col_base`: their
 // global indices; `n_cb`: 32-column blocks in the tile; `off_diagonal`: the tile is not on the diagonal (mirror stores).
+// `zero_acc`: the tile had no product (its accumulator was never written): the values are zeros.
 __device__ __forceinline__ void epilogue_direct(uint32_t tmem_warp, int lane, float* stage, int row0, int col_base, int n_cb,
-                                                bool off_diagonal, int batch, int M, int N, const Tf32Epilogue& E) {
+                                                bool off_diagonal, bool zero_acc, int batch, int M, int N,
+                                                const Tf32Epilogue& E) {
   const int64_t b64 = batch;
   const bool state_vec = (N & 3) == 0;
   const bool c_vec = (E.ldc & 3) == 0 && ((E.strideC & 3) == 0) && ((((uintptr_t)E.C) & 15) == 0);
@@ -80,8 +82,13 @@ __device__ __forceinline__ void epilogue_direct(uint32_t tmem_warp, int lane, fl
     const int col0 = col_base + cb * 32;
     {
       uint32_t acc[32];
-      tmem_ld32(tmem_warp + (uint32_t)(cb * 32), acc);
-      tmem_ld_wait();
+      if (!zero_acc) {
+        tmem_ld32(tmem_warp + (uint32_t)(cb * 32), acc);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] = 0u;
+      }
 #pragma unroll
       for (int q = 0; q < 8; ++q)
         *(float4*)(mine + q * 4) =
@@ -231,7 +238,12 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     tn = tm + left;
   }
   const int batch = blockIdx.y;
-  const int seg_kb = kp / TBK;      // K blocks per term of the split product
+  int kb_lo = 0, kb_hi = kp / TBK;  // K blocks of one term of the split product that this tile walks
+  if (E.tri) {
+    kb_lo = min(kb_hi, tm * (TBM / TBK));
+    kb_hi = tn < tm ? kb_lo : min(kb_hi, (tn + 1) * (TBN / TBK));
+  }
+  const int seg_kb = kb_hi - kb_lo;
   const int num_kb = 3 * seg_kb;    // hi*hi, hi*lo, lo*hi
   const float alpha = E.alpha;
 
@@ -254,7 +266,7 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int s = kb % kTStages, round = kb / kTStages;
         if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &abort_flag)) break;
         uint8_t* dst = tiles + s * kTStageBytes;
-        const int seg = kb / seg_kb, k0 = (kb - seg * seg_kb) * TBK;
+        const int seg = kb / seg_kb, k0 = (kb_lo + kb - seg * seg_kb) * TBK;
         mbar_expect_tx(&full_bar[s], kTStageBytes);
         tma_load_3d(dst, &map_a, &full_bar[s], k0 + (seg == 2 ? kp : 0), tm * TBM, batch);               // hi, hi, lo
         tma_load_3d(dst + kTTileBytes, &map_b, &full_bar[s], k0 + (seg == 1 ? kp : 0), tn * TBN, batch);  // hi, lo, hi
@@ -299,7 +311,7 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       }
     } else if (have) {
       epilogue_direct(tmem_base + ((uint32_t)(quarter * 32) << 16), lane, (float*)(tiles + quarter * kStageWarpBytes),
-                      tm * TBM + quarter * 32, tn * TBN, TBN / 32, tm != tn, batch, M, N, E);
+                      tm * TBM + quarter * 32, tn * TBN, TBN / 32, tm != tn, num_kb == 0, batch, M, N, E);
     }
     tc_fence_before();
     if (bulk_store) {
@@ -363,7 +375,12 @@ tf32_gemm256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tn = tm + left;
   }
   const int batch = blockIdx.y;
-  const int seg_kb = kp / TBK;
+  int kb_lo = 0, kb_hi = kp / TBK;
+  if (E.tri) {
+    kb_lo = min(kb_hi, tm * (TBM2 / TBK));
+    kb_hi = tn < tm ? kb_lo : min(kb_hi, (tn + 1) * (TBN2 / TBK));
+  }
+  const int seg_kb = kb_hi - kb_lo;
   const int num_kb = 3 * seg_kb;
 
   if (threadIdx.x == 0) {
@@ -385,7 +402,7 @@ tf32_gemm256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int s = kb % kTStages, round = kb / kTStages;
         if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &abort_flag)) break;
         uint8_t* dst = tiles + s * kTStageBytes2;
-        const int seg = kb / seg_kb, k0 = (kb - seg * seg_kb) * TBK;
+        const int seg = kb / seg_kb, k0 = (kb_lo + kb - seg * seg_kb) * TBK;
         const int ka = k0 + (seg == 2 ? kp : 0), kb_col = k0 + (seg == 1 ? kp : 0);   // A: hi, hi, lo   B: hi, lo, hi
         mbar_expect_tx(&full_bar[s], kTStageBytes2);   // rows past the operand's end arrive as zeros and count as bytes
         tma_load_3d(dst, &map_a, &full_bar[s], ka, tm * TBM2, batch);
@@ -424,7 +441,8 @@ tf32_gemm256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int row0 = tm * TBM2 + half * 128 + quarter * 32;
     if (have && row0 < M)
       epilogue_direct(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 256), lane,
-                      (float*)(tiles + (warp - 2) * kStageWarpBytes), row0, tn * TBN2, TBN2 / 32, tm != tn, batch, M, N, E);
+                      (float*)(tiles + (warp - 2) * kStageWarpBytes), row0, tn * TBN2, TBN2 / 32, tm != tn, num_kb == 0,
+                      batch, M, N, E);
     tc_fence_before();
   }
 
@@ -551,6 +569,7 @@ cudaError_t launch_tf32_gemm(const float* A2, const float* B2, int M, int N, int
   if (M == 0 || N == 0 || batch == 0) return cudaSuccess;
   if ((E.mode == kEpiAdam || E.mode == kEpiLaProp) && (E.m == nullptr || E.v == nullptr)) return cudaErrorInvalidValue;
   if (E.mode == kEpiLerp && E.C == nullptr) return cudaErrorInvalidValue;
+  if (E.tri && (M != N || M != K || E.symmetric)) return cudaErrorInvalidValue;
   if (E.symmetric && (A2 != B2 || M != N || E.C == nullptr || E.S != nullptr || (E.mode != kEpiStore && E.mode != kEpiLerp)))
     return cudaErrorInvalidValue;
   const int64_t kp = tf32_split_kp(K), ld = 2 * kp;
@@ -572,7 +591,7 @@ cudaError_t launch_tf32_gemm(const float* A2, const float* B2, int M, int N, int
   }
 
   // plain products leave through the bulk-store path; everything else is written by the epilogue threads themselves
-  const int bulk = (!E.symmetric && E.mode == kEpiStore && E.S == nullptr && E.C != nullptr && (E.ldc & 3) == 0 &&
+  const int bulk = (!E.symmetric && !E.tri && E.mode == kEpiStore && E.S == nullptr && E.C != nullptr && (E.ldc & 3) == 0 &&
                     (E.strideC & 3) == 0 && (((uintptr_t)E.C) & 15) == 0) ? 1 : 0;
   mc = ma;  // placeholder when the bulk-store path is not taken (never dereferenced then)
   if (bulk && !make_f32_map(&mc, E.C, M, N, E.ldc, E.strideC, batch)) return cudaErrorInvalidValue;

@@ -37,6 +37,9 @@ struct Tf32Epilogue {
   int s_transposed;        // 0: operand rows = output rows, K = N; 1: operand rows = output columns, K = M
   float* m;                // kEpiAdam / kEpiLaProp state, fp32 [batch, M, N] contiguous
   float* v;
+  int tri;                 // A[i, k] = 0 for k < i and B[j, k] = 0 for k > j (an upper-triangular matrix times an upper-
+                           // triangular matrix, M == N == K): a tile only walks the K range where both are non-zero,
+                           // tiles below the diagonal are stored as zeros without a product
   int symmetric;           // A2 == B2 (so M == N and the product is symmetric): only tiles on or above the diagonal are
                            // computed and each is also stored transposed.  kEpiStore / kEpiLerp with C set and S null.
 };

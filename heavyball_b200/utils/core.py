@@ -454,7 +454,7 @@ def apply_flat_add(params: List[Tensor], update: Tensor, alpha):
 # ---------------------------------------------------------------------------------------- tensor-core products
 
 
-def _tc_matmul(a: Tensor, b: Tensor, ta: bool = False, tb: bool = False):
+def _tc_matmul(a: Tensor, b: Tensor, ta: bool = False, tb: bool = False, upper_upper: bool = False):
     """``op(a) @ op(b)`` on the split-tf32 tensor-core kernel when it applies (fp32 CUDA matrices on sm_100a with
     every dimension >= 128 and ``utils.tensor_core_matmul`` on), else ``None``."""
     if not (a.is_cuda and getattr(_settings(), "tensor_core_matmul", True)):
@@ -463,12 +463,19 @@ def _tc_matmul(a: Tensor, b: Tensor, ta: bool = False, tb: bool = False):
 
     if not ops.matmul_supported(a, b):
         return None
-    return ops.matmul3(a, b, ta, tb)
+    return ops.matmul3(a, b, ta, tb, upper_upper=upper_upper)
 
 
 def _mm(a: Tensor, b: Tensor, ta: bool = False, tb: bool = False) -> Tensor:
     out = _tc_matmul(a, b, ta, tb)
     return out if out is not None else (a.mT if ta else a) @ (b.mT if tb else b)
+
+
+def _mm_upper(a: Tensor, b: Tensor) -> Tensor:
+    """``a @ b`` for upper-triangular ``a`` and ``b`` (entries below their diagonals are zero): the tensor-core kernel
+    walks only the K range where both are non-zero."""
+    out = _tc_matmul(a, b, upper_upper=True) if a.ndim == 3 and a.shape == b.shape and a.shape[-1] == a.shape[-2] else None
+    return out if out is not None else a @ b
 
 
 # ---------------------------------------------------------------------------------------- blocked triangular solve

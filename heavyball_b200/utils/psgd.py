@@ -39,7 +39,7 @@ from .core import (
     warn_once,
 )
 from . import core as _core
-from .core import _mm, _segmented_absmax_rows, _solve_right_upper, _tc_matmul
+from .core import _mm, _mm_upper, _segmented_absmax_rows, _solve_right_upper, _tc_matmul
 from .orthogonal import inplace_orthogonal_
 from .soap import compiled_einsum, einsum_base
 
@@ -524,7 +524,7 @@ def psgd_update_precond(G, precond_lr, oq, store_triu_as_line, beta2, V, running
             step = promote(q) * (t1 - t2)
         else:
             ell = _update_lb(max_eigenvalue_spd(t1 + t2, power_iter=power_iter), lb, lower_bount_beta)
-            step = _mm((t1 - t2).triu(), promote(q))
+            step = _mm_upper((t1 - t2).triu(), promote(q))  # q is upper triangular as well
             if store_triu_as_line:
                 step = triu_to_line([step])[0][1]
         target = oq_i[1] if isinstance(oq_i, tuple) else oq_i

@@ -403,6 +403,31 @@ at::Tensor tri_inv_blocks(const at::Tensor& q) {
   return x;
 }
 
+// Row-major upper triangles of contiguous [batch, n, n] matrices (2- or 4-byte elements) as [batch, n (n + 1) / 2].
+at::Tensor triu_pack(const at::Tensor& dense) {
+  TORCH_CHECK(dense.is_cuda() && dense.dim() == 3 && dense.size(1) == dense.size(2) && dense.is_contiguous() &&
+                  (dense.element_size() == 2 || dense.element_size() == 4) && dense.size(0) <= 65535,
+              "triu_pack: contiguous [batch <= 65535, n, n] CUDA tensor with 2- or 4-byte elements");
+  c10::cuda::CUDAGuard guard(dense.device());
+  const int64_t n = dense.size(1);
+  at::Tensor line = at::empty({dense.size(0), n * (n + 1) / 2}, dense.options());
+  check(hb::launch_triu_pack(dense.data_ptr(), line.data_ptr(), (int)dense.element_size(), (int)dense.size(0), (int)n,
+                             at::cuda::getCurrentCUDAStream()), "triu_pack launch");
+  return line;
+}
+
+// Inverse of triu_pack; entries below the diagonal are zero.
+at::Tensor triu_unpack(const at::Tensor& line, int64_t n) {
+  TORCH_CHECK(line.is_cuda() && line.dim() == 2 && line.size(1) == n * (n + 1) / 2 && line.is_contiguous() &&
+                  (line.element_size() == 2 || line.element_size() == 4) && line.size(0) <= 65535,
+              "triu_unpack: contiguous [batch <= 65535, n (n + 1) / 2] CUDA tensor with 2- or 4-byte elements");
+  c10::cuda::CUDAGuard guard(line.device());
+  at::Tensor dense = at::empty({line.size(0), n, n}, line.options());
+  check(hb::launch_triu_unpack(line.data_ptr(), dense.data_ptr(), (int)line.element_size(), (int)line.size(0), (int)n,
+                               at::cuda::getCurrentCUDAStream()), "triu_unpack launch");
+  return dense;
+}
+
 // fp32 column sums of a contiguous bf16 matrix [rows, cols] (cols % 8 == 0).
 at::Tensor colsum_bf16(const at::Tensor& x) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kBFloat16 && x.is_contiguous() &&
@@ -540,5 +565,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ns_gemm", &ns_gemm);
   m.def("set_ns_gemm_tile", &hb::set_ns_gemm_tile_override);
   m.def("set_tf32_gemm_tile", &hb::set_tf32_gemm_tile_override);
+  m.def("triu_pack", &triu_pack);
+  m.def("triu_unpack", &triu_unpack);
   m.def("chunk_elems", &hb::chain_chunk_elems);
 }

@@ -190,4 +190,50 @@ cudaError_t launch_tri_inv_blocks(const float* Q, long long ld, long long stride
   return cudaGetLastError();
 }
 
+
+// ------------------------------------------------------------------------------------------ packed upper triangles
+// PSGD stores a triangular factor as the row-major upper triangle ("line").  Row i of the triangle is the contiguous
+// piece dense[i, i:n] and sits at line offset i*n - i*(i-1)/2, so packing and unpacking are row copies: one block per
+// (row, matrix), no index tensors (index_put / index_select read an 8-byte index per element and first materialise
+// 16 n^2 bytes of indices).
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(256) triu_pack_kernel(const T* __restrict__ dense, T* __restrict__ line, int n) {
+  const long long i = blockIdx.x, b = blockIdx.y;
+  const long long len = (long long)n * (n + 1) / 2;
+  const T* src = dense + (b * n + i) * n + i;
+  T* dst = line + b * len + i * n - i * (i - 1) / 2;
+  for (int j = threadIdx.x; j < n - (int)i; j += blockDim.x) dst[j] = src[j];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) triu_unpack_kernel(const T* __restrict__ line, T* __restrict__ dense, int n) {
+  const long long i = blockIdx.x, b = blockIdx.y;
+  const long long len = (long long)n * (n + 1) / 2;
+  const T* src = line + b * len + i * n - i * (i - 1) / 2 - i;  // indexed by the dense column
+  T* dst = dense + (b * n + i) * n;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) dst[j] = j >= (int)i ? src[j] : T(0);
+}
+
+}  // namespace
+
+cudaError_t launch_triu_pack(const void* dense, void* line, int elem_bytes, int batch, int n, cudaStream_t stream) {
+  if (batch == 0 || n == 0) return cudaSuccess;
+  dim3 grid(n, batch);
+  if (elem_bytes == 4) triu_pack_kernel<uint32_t><<<grid, 256, 0, stream>>>((const uint32_t*)dense, (uint32_t*)line, n);
+  else if (elem_bytes == 2) triu_pack_kernel<uint16_t><<<grid, 256, 0, stream>>>((const uint16_t*)dense, (uint16_t*)line, n);
+  else return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_triu_unpack(const void* line, void* dense, int elem_bytes, int batch, int n, cudaStream_t stream) {
+  if (batch == 0 || n == 0) return cudaSuccess;
+  dim3 grid(n, batch);
+  if (elem_bytes == 4) triu_unpack_kernel<uint32_t><<<grid, 256, 0, stream>>>((const uint32_t*)line, (uint32_t*)dense, n);
+  else if (elem_bytes == 2) triu_unpack_kernel<uint16_t><<<grid, 256, 0, stream>>>((const uint16_t*)line, (uint16_t*)dense, n);
+  else return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+
 }  // namespace hb

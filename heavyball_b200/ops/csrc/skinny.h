@@ -18,4 +18,9 @@ constexpr int kTriBlock = 128;
 cudaError_t launch_tri_inv_blocks(const float* Q, long long ld, long long strideQ, int batch, int n, float* X,
                                   cudaStream_t stream);
 
+// Row-major upper triangle of square matrices, [batch, n, n] <-> [batch, n (n + 1) / 2]; elements of 2 or 4 bytes are
+// moved as bits.  Unpacking writes zeros below the diagonal.  blockIdx.y = batch (<= 65535).
+cudaError_t launch_triu_pack(const void* dense, void* line, int elem_bytes, int batch, int n, cudaStream_t stream);
+cudaError_t launch_triu_unpack(const void* line, void* dense, int elem_bytes, int batch, int n, cudaStream_t stream);
+
 }  // namespace hb

@@ -86,11 +86,23 @@ def _triu_index(d0: int, d1: int, device) -> Tuple[Tensor, Tensor]:
     return rows, cols
 
 
+def _triu_kernels(t: Tensor, square: bool):
+    """The extension when its packed-triangle kernels apply (batched square CUDA matrices, 2- or 4-byte elements)."""
+    if not (t.is_cuda and square and t.element_size() in (2, 4) and t.shape[0] <= 65535 and not t.is_complex()):
+        return None
+    from .. import ops
+
+    return ops.load() if ops.available() else None
+
+
 def _pack_upper(q: Tensor):
     """``(shape, packed)``: the row-major upper triangle of a dense factor; vectors (diagonal factors) pass through
     with ``shape=None``."""
     if q.dim() < 3:
         return None, q
+    ext = _triu_kernels(q, q.dim() == 3 and q.shape[-2] == q.shape[-1])
+    if ext is not None:
+        return tuple(q.shape), ext.triu_pack(q.contiguous())
     rows, cols = _triu_index(q.shape[-2], q.shape[-1], q.device)
     return tuple(q.shape), q[..., rows, cols]
 
@@ -104,10 +116,14 @@ def line_to_triu(Q_list):
     for shape, q in Q_list:
         if shape is not None:
             d0, d1 = shape[-2], shape[-1]
-            rows, cols = _triu_index(d0, d1, q.device)
-            dense = torch.zeros(q.shape[:-1] + (d0, d1), device=q.device, dtype=q.dtype)
-            dense[..., rows, cols] = q
-            q = dense
+            ext = _triu_kernels(q, q.dim() == 2 and d0 == d1)
+            if ext is not None:
+                q = ext.triu_unpack(q.contiguous(), d0)
+            else:
+                rows, cols = _triu_index(d0, d1, q.device)
+                dense = torch.zeros(q.shape[:-1] + (d0, d1), device=q.device, dtype=q.dtype)
+                dense[..., rows, cols] = q
+                q = dense
         out.append(q)
     return out
 

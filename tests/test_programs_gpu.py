@@ -231,6 +231,19 @@ def test_psgd_diagonal_factor_statistics_on_the_gpu():
     assert q[0][0] is None and q[0][1].shape == (1, 640)  # packed form: diagonal factor for the 640 side
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,n", [(3, 5), (2, 128), (1, 1000), (4, 257)])
+def test_packed_triangle_kernels_match_index_arithmetic(B, n, dtype):
+    from heavyball_b200.utils import psgd
+
+    q = _rand(B, n, n, seed=21).to(dtype)
+    rows, cols = torch.triu_indices(n, n, device="cuda")
+    (shape, line), = psgd.triu_to_line([q])
+    assert shape == (B, n, n) and torch.equal(line, q[:, rows, cols])
+    (dense,) = psgd.line_to_triu([(shape, line)])
+    assert torch.equal(dense, q.triu())
+
+
 @pytest.mark.parametrize("n", [128, 200, 1024])
 def test_block_inverse_triangular_solve(n):
     """``X q = b`` through the inverses of the 128-wide diagonal blocks against the library's triangular solve."""

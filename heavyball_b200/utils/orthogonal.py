@@ -230,12 +230,21 @@ def _chol_upper_blocked(G: Tensor, R: Tensor, bad: Tensor, lo: int, hi: int):
     _chol_upper_blocked(G, R, bad, mid, hi)
 
 
-def _cholesky_qr2(x: Tensor):
-    """Two rounds of Cholesky QR on the column-normalised input: ``G = A^T A = R^T R``, ``A <- A R^-1``.  Everything is
+_CHOLQR_SHIFT = 1e-5  # of the Gram matrix's trace bound; one shifted round lowers the condition number ~300-fold
+_CHOLQR_ACCEPT = 1e-4  # largest entry of Q^T Q - I that is accepted (a Householder factor reaches ~1e-6 in fp32)
+
+
+def _cholesky_qr2(x: Tensor, shifted_rounds: int = 0):
+    """Cholesky QR on the column-normalised input: ``G = A^T A = R^T R``, ``A <- A R^-1``, repeated.  Everything is
     matrix products plus 128-wide batched Cholesky leaves, so an ``n x n`` basis costs a few milliseconds instead of
-    the hundreds of dependent panel steps of :func:`_panel_cholesky_qr`.  It is only valid while the columns are far
-    from dependent (condition number below about ``eps^-1/2``), which is the usual case once an eigenbasis tracks its
-    statistics; the second round's Gram matrix tells: it must be close to the identity.  Returns ``(q, bad)`` with one
+    the hundreds of dependent panel steps of :func:`_panel_cholesky_qr`.
+
+    Two plain rounds are valid while the columns are far from dependent (condition number below about ``eps^-1/2``),
+    which is the usual case once an eigenbasis tracks its statistics.  Worse inputs get ``shifted_rounds`` rounds in
+    front that factor ``G + s I`` instead (always positive definite; the result is not yet orthonormal but its
+    condition number is lower by about ``sqrt(lambda_max / s)``); the product of all triangular factors is still THE
+    triangular factor of ``A``, so every variant returns the same ``Q``.  Whether the input was within reach is read off
+    the result: ``Q^T Q`` must be the identity to 1e-4 (one more symmetric product).  Returns ``(q, bad)`` with one
     failure count per matrix, nothing read on the host."""
     batch, (n, k) = x.shape[:-2], x.shape[-2:]
     a = x.reshape(-1, n, k)
@@ -243,45 +252,54 @@ def _cholesky_qr2(x: Tensor):
     a = a / a.norm(dim=-2, keepdim=True).clamp_(min=tiny)
     bad = torch.zeros(a.shape[0], dtype=torch.int32, device=a.device)
     eye = torch.eye(k, device=a.device, dtype=a.dtype)
-    for rnd in range(2):
+    rounds = shifted_rounds + 2
+    info = torch.zeros_like(bad)  # failed leaves are not a verdict: what counts is the orthogonality reached at the end
+    for rnd in range(rounds):
         gram = _mm(a, a, True, False)
-        if rnd == 1:
-            bad += (gram - eye).abs().amax(dim=(-2, -1)).gt(0.3)
+        if rnd < shifted_rounds:
+            # unit columns: the diagonal is 1 and lambda_max <= k
+            gram.diagonal(dim1=-2, dim2=-1).add_(_CHOLQR_SHIFT * k)
         r = torch.zeros_like(gram)
-        _chol_upper_blocked(gram, r, bad, 0, k)
+        _chol_upper_blocked(gram, r, info, 0, k)
         a = _solve_right_upper(r, a)
+        if rnd < shifted_rounds:  # columns shrank by different amounts: back to unit columns for the next round
+            a = a / a.norm(dim=-2, keepdim=True).clamp_(min=tiny)
+    bad += (_mm(a, a, True, False) - eye).abs().amax(dim=(-2, -1)).gt(_CHOLQR_ACCEPT)
     bad += (~torch.isfinite(a)).flatten(1).any(dim=1)
     return a.reshape(*batch, n, k), bad
 
 
 _cholqr_graphs = {}
-qr_stats = {"cholesky_qr2": 0, "cholesky_qr2_rejected": 0}  # how often the fast factorisation was taken / refused
+_CHOLQR_LADDER = (0, 1, 3)  # shifted rounds in front of the two plain ones, tried in this order
+_cholqr_level, _cholqr_wins = {}, {}  # (device, shape) -> where to start on the ladder / successes so far
+# how often each variant produced the basis, and how often all were refused (panel-wise route)
+qr_stats = {"cholesky_qr2": 0, "cholesky_qr_shifted_1": 0, "cholesky_qr_shifted_3": 0, "cholesky_qr2_rejected": 0}
 
 
-def _cholesky_qr2_replayed(x: Tensor):
-    """:func:`_cholesky_qr2` through a CUDA graph per (device, shape), like :func:`_panel_qr_replayed`."""
-    key = (x.device, tuple(x.shape))
+def _cholesky_qr2_replayed(x: Tensor, shifted_rounds: int = 0):
+    """:func:`_cholesky_qr2` through a CUDA graph per (device, shape, variant), like :func:`_panel_qr_replayed`."""
+    key = (x.device, tuple(x.shape), shifted_rounds)
     slot = _cholqr_graphs.get(key)
     if slot is None:
-        if len(_cholqr_graphs) >= _QR_GRAPH_LIMIT:
-            return _cholesky_qr2(x)
+        if len(_cholqr_graphs) >= 2 * _QR_GRAPH_LIMIT:
+            return _cholesky_qr2(x, shifted_rounds)
         slot = _cholqr_graphs[key] = [0, None]
     slot[0] += 1
     if slot[1] is False or slot[0] == 1 or not _settings().graph_qr:
-        return _cholesky_qr2(x)
+        return _cholesky_qr2(x, shifted_rounds)
     if slot[1] is None:
         try:
             static_in = x.clone()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                static_out, static_bad = _cholesky_qr2(static_in)
+                static_out, static_bad = _cholesky_qr2(static_in, shifted_rounds)
             slot[1] = (graph, static_in, static_out, static_bad)
         except Exception as err:  # noqa: BLE001 - any capture failure means "do not graph this shape"
             slot[1] = False
             import warnings
 
             warnings.warn(f"CUDA graph capture of the Cholesky QR failed ({type(err).__name__}); running it eagerly")
-            return _cholesky_qr2(x)
+            return _cholesky_qr2(x, shifted_rounds)
     graph, static_in, static_out, static_bad = slot[1]
     static_in.copy_(x)
     graph.replay()
@@ -345,10 +363,18 @@ def _qr_basis(x: Tensor, fallback: Tensor = None) -> Tensor:
     x32 = promote(x)
     if (x32.is_cuda and _settings().fast_qr and x32.shape[-2] >= x32.shape[-1] >= _CHOLQR_MIN
             and not torch.cuda.is_current_stream_capturing()):  # fmt: skip
-        q, bad = _cholesky_qr2_replayed(x32.contiguous())
-        if int(bad.sum()) == 0:  # one host read per refresh; a failure takes the robust panel-wise route below
-            qr_stats["cholesky_qr2"] += 1
-            return q.clone() if q.data_ptr() != x32.data_ptr() else q
+        xc = x32.contiguous()
+        key = (xc.device, tuple(xc.shape))
+        start = _cholqr_level.get(key, 0)
+        for level in range(start, len(_CHOLQR_LADDER)):
+            q, bad = _cholesky_qr2_replayed(xc, _CHOLQR_LADDER[level])
+            if int(bad.sum()) == 0:  # one host read per attempt; a failure climbs the ladder, then takes the panel-wise route
+                qr_stats["cholesky_qr2" if level == 0 else f"cholesky_qr_shifted_{_CHOLQR_LADDER[level]}"] += 1
+                # start where it worked next time, and try one step cheaper every eighth success
+                wins = _cholqr_wins[key] = _cholqr_wins.get(key, 0) + 1
+                _cholqr_level[key] = max(0, level - 1) if wins % 8 == 0 else level
+                return q.clone() if q.data_ptr() != x32.data_ptr() else q
+        _cholqr_level[key] = len(_CHOLQR_LADDER) - 1
         qr_stats["cholesky_qr2_rejected"] += 1
     if x32.is_cuda and _settings().fast_qr and x32.shape[-2] >= x32.shape[-1] >= 2 * _QR_PANEL:
         q = _panel_qr_replayed(x32.contiguous(), fallback) if _settings().graph_qr else _panel_cholesky_qr(x32)

@@ -110,7 +110,9 @@ def test_tall_skinny_products_match_matmul(n, k, m, p):
 
 def test_cholesky_qr2_fast_path_and_its_failure_flag():
     """Well-conditioned refresh inputs take two rounds of Cholesky QR (matrix products only); badly conditioned ones are
-    flagged on the device and ``_qr_basis`` then returns the panel-wise result."""
+    flagged on the device, and ``_qr_basis`` then climbs to the variants with shifted rounds in front (or, past those,
+    to the panel-wise method)."""
+    from heavyball_b200.utils import orthogonal
     from heavyball_b200.utils.orthogonal import _cholesky_qr2, _qr_basis
 
     eye = torch.eye(512, device="cuda")
@@ -123,8 +125,29 @@ def test_cholesky_qr2_fast_path_and_its_failure_flag():
     hard = _spd_power_iterate(512, 4, 20, 1.0)
     _, bad = _cholesky_qr2(hard)
     assert int(bad.sum()) > 0
+    before = dict(orthogonal.qr_stats)
     q = _qr_basis(hard)
-    assert (q.mT @ q - eye).abs().max().item() < 1e-5
+    assert (q.mT @ q - eye).abs().max().item() < 1e-4
+    assert orthogonal.qr_stats["cholesky_qr2"] == before["cholesky_qr2"]  # the plain variant was refused ...
+    assert sum(orthogonal.qr_stats.values()) == sum(before.values()) + 1  # ... and exactly one other route produced it
     for _ in range(3):  # replayed from its graph from the second call on
         q = _qr_basis(easy)
     assert (q.mT @ q - eye).abs().max().item() < 3e-5
+
+
+@pytest.mark.parametrize("decades,shifted", [(2, 0), (5, 1), (7, 3)])
+def test_shifted_cholesky_qr_reaches_worse_conditioning(decades, shifted):
+    """Every variant returns the Householder factor's Q (up to column signs) while the input is within its reach."""
+    from heavyball_b200.utils.orthogonal import _cholesky_qr2
+
+    torch.manual_seed(decades)
+    n = 512
+    u = torch.linalg.qr(torch.randn(2, n, n, device="cuda", dtype=torch.float64)).Q
+    v = torch.linalg.qr(torch.randn(2, n, n, device="cuda", dtype=torch.float64)).Q
+    a = (u * torch.logspace(0, -decades, n, device="cuda", dtype=torch.float64)) @ v.mT
+    q, bad = _cholesky_qr2(a.float(), shifted)
+    assert int(bad.sum()) == 0
+    assert (q.mT @ q - torch.eye(n, device="cuda")).abs().max().item() < 1e-4
+    if decades <= 5:  # beyond that the trailing columns of the fp32 input are rounding noise in any method
+        ref = torch.linalg.qr(a).Q
+        assert ((q.double() * ref).sum(-2).abs() - 1).abs().max().item() < 1e-2

@@ -403,6 +403,29 @@ at::Tensor tri_inv_blocks(const at::Tensor& q) {
   return x;
 }
 
+// Factors the diagonal leaf [lo, lo + size) of the batched symmetric positive definite fp32 matrices g ([batch, n, n], unit
+// inner stride) as R^T R: writes R's block into r (same layout as g) and the block's inverse into inv[:, lo / 128]
+// (inv: contiguous [batch, ceil(n / 128), 128, 128]); info: int32 [batch], incremented per matrix with a bad pivot.
+void chol_inv_leaf(const at::Tensor& g, at::Tensor& r, at::Tensor& inv, int64_t lo, int64_t size, at::Tensor& info) {
+  TORCH_CHECK(g.is_cuda() && g.scalar_type() == at::kFloat && g.dim() == 3 && g.size(1) == g.size(2) && g.stride(2) == 1 &&
+                  r.is_cuda() && r.scalar_type() == at::kFloat && r.sizes() == g.sizes() && r.stride(2) == 1 &&
+                  r.device() == g.device(), "chol_inv_leaf: fp32 [batch, n, n] CUDA tensors with unit inner stride");
+  const int64_t batch = g.size(0), n = g.size(1), nb = (n + hb::kTriBlock - 1) / hb::kTriBlock;
+  TORCH_CHECK(lo >= 0 && size >= 1 && size <= hb::kTriBlock && lo + size <= n && lo % hb::kTriBlock == 0,
+              "chol_inv_leaf: leaf [lo, lo + size) must start on a multiple of 128 and hold at most 128 rows");
+  TORCH_CHECK(inv.is_cuda() && inv.scalar_type() == at::kFloat && inv.is_contiguous() && inv.dim() == 4 && inv.size(0) == batch &&
+                  inv.size(1) == nb && inv.size(2) == hb::kTriBlock && inv.size(3) == hb::kTriBlock && inv.device() == g.device(),
+              "chol_inv_leaf: inv must be contiguous fp32 [batch, ceil(n / 128), 128, 128]");
+  TORCH_CHECK(info.is_cuda() && info.scalar_type() == at::kInt && info.is_contiguous() && info.numel() == batch &&
+                  info.device() == g.device(), "chol_inv_leaf: info must be int32 [batch]");
+  c10::cuda::CUDAGuard guard(g.device());
+  const int64_t blk = hb::kTriBlock * hb::kTriBlock;
+  check(hb::launch_chol_inv_leaf(g.data_ptr<float>() + lo * g.stride(1) + lo, g.stride(1), g.stride(0),
+                                 r.data_ptr<float>() + lo * r.stride(1) + lo, r.stride(1), r.stride(0),
+                                 inv.data_ptr<float>() + (lo / hb::kTriBlock) * blk, nb * blk, (int)batch, (int)size,
+                                 info.data_ptr<int>(), at::cuda::getCurrentCUDAStream()), "chol_inv_leaf launch");
+}
+
 // Row-major upper triangles of contiguous [batch, n, n] matrices (2- or 4-byte elements) as [batch, n (n + 1) / 2].
 at::Tensor triu_pack(const at::Tensor& dense) {
   TORCH_CHECK(dense.is_cuda() && dense.dim() == 3 && dense.size(1) == dense.size(2) && dense.is_contiguous() &&
@@ -565,6 +588,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ns_gemm", &ns_gemm);
   m.def("set_ns_gemm_tile", &hb::set_ns_gemm_tile_override);
   m.def("set_tf32_gemm_tile", &hb::set_tf32_gemm_tile_override);
+  m.def("chol_inv_leaf", &chol_inv_leaf);
   m.def("triu_pack", &triu_pack);
   m.def("triu_unpack", &triu_unpack);
   m.def("chunk_elems", &hb::chain_chunk_elems);

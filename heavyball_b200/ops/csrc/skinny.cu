@@ -191,6 +191,87 @@ cudaError_t launch_tri_inv_blocks(const float* Q, long long ld, long long stride
 }
 
 
+// ------------------------------------------------------------------------------------------ Cholesky leaf
+// One CTA factors one (up to) 128 x 128 symmetric positive definite block G = R^T R (R upper triangular) and inverts R,
+// both in shared memory.  Thread j owns column j.
+//   factor:  for k = 0 .. n-1:  r_kk = sqrt(g_kk);  r_kj = g_kj / r_kk (j > k);  g_ij -= r_ki r_kj (k < i <= j)
+//   invert:  x_jj = 1 / r_jj,   x_ij = -(sum_{k = i+1 .. j} r_ik x_kj) / r_ii   for i = j-1 .. 0
+// A non-positive or non-finite pivot is replaced by 1 and counted in info[b] (the result for that matrix is then
+// meaningless, the others are unaffected).  The batched library factorisation of the same leaf takes ~160 us per call
+// in ten launches, and the blocked solves around it each used to invert the leaves again.
+namespace {
+
+__global__ void __launch_bounds__(kTriBlock) chol_inv_leaf_kernel(const float* __restrict__ G, long long ldg, long long strideG,
+                                                                  float* __restrict__ R, long long ldr, long long strideR,
+                                                                  float* __restrict__ X, long long strideX, int size,
+                                                                  int* __restrict__ info) {
+  extern __shared__ float leaf_smem[];
+  float(*t)[kTriBlock + 1] = (float(*)[kTriBlock + 1])leaf_smem;
+  float(*x)[kTriBlock + 1] = (float(*)[kTriBlock + 1])(leaf_smem + kTriBlock * (kTriBlock + 1));
+  __shared__ int failed;
+  const int b = blockIdx.x, j = threadIdx.x;
+  const float* g = G + (long long)b * strideG;
+  if (j == 0) failed = 0;
+  for (int i = 0; i < kTriBlock; ++i) {  // upper part of the block; the rest of a short block is an identity
+    float v = (i == j) ? 1.f : 0.f;
+    if (i < size && j < size && j >= i) v = g[(long long)i * ldg + j];
+    t[i][j] = v;
+    x[i][j] = 0.f;
+  }
+  __syncthreads();
+  for (int k = 0; k < size; ++k) {
+    const float d = t[k][k];
+    const bool ok = d > 0.f && d < 3.0e38f;
+    const float piv = ok ? sqrtf(d) : 1.f;
+    __syncthreads();  // everyone has read the pivot before it is overwritten
+    if (j == k) {
+      t[k][k] = piv;
+      if (!ok) failed = 1;
+    } else if (j > k) {
+      t[k][j] = t[k][j] / piv;
+    }
+    __syncthreads();
+    if (j > k) {
+      const float rkj = t[k][j];
+      for (int i = k + 1; i <= j; ++i) t[i][j] = fmaf(-t[k][i], rkj, t[i][j]);
+    }
+    __syncthreads();
+  }
+  {
+    x[j][j] = 1.0f / t[j][j];
+    for (int i = j - 1; i >= 0; --i) {
+      float sum = 0.f;
+      for (int k = i + 1; k <= j; ++k) sum = fmaf(t[i][k], x[k][j], sum);
+      x[i][j] = -sum / t[i][i];
+    }
+  }
+  __syncthreads();
+  float* r = R + (long long)b * strideR;
+  float* out = X + (long long)b * strideX;
+  for (int i = 0; i < kTriBlock; ++i) {
+    if (i < size && j < size) r[(long long)i * ldr + j] = j >= i ? t[i][j] : 0.f;
+    out[i * kTriBlock + j] = x[i][j];
+  }
+  if (j == 0 && failed && info != nullptr) atomicAdd(info + b, 1);
+}
+
+}  // namespace
+
+cudaError_t launch_chol_inv_leaf(const float* G, long long ldg, long long strideG, float* R, long long ldr, long long strideR,
+                                 float* X, long long strideX, int batch, int size, int* info, cudaStream_t stream) {
+  if (batch == 0 || size == 0) return cudaSuccess;
+  if (size > kTriBlock) return cudaErrorInvalidValue;
+  constexpr int kBytes = 2 * kTriBlock * (kTriBlock + 1) * (int)sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(chol_inv_leaf_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  chol_inv_leaf_kernel<<<batch, kTriBlock, kBytes, stream>>>(G, ldg, strideG, R, ldr, strideR, X, strideX, size, info);
+  return cudaGetLastError();
+}
+
 // ------------------------------------------------------------------------------------------ packed upper triangles
 // PSGD stores a triangular factor as the row-major upper triangle ("line").  Row i of the triangle is the contiguous
 // piece dense[i, i:n] and sits at line offset i*n - i*(i-1)/2, so packing and unpacking are row copies: one block per

@@ -18,6 +18,13 @@ constexpr int kTriBlock = 128;
 cudaError_t launch_tri_inv_blocks(const float* Q, long long ld, long long strideQ, int batch, int n, float* X,
                                   cudaStream_t stream);
 
+// Upper Cholesky factor and its inverse of one diagonal leaf (size <= kTriBlock) of a batch of symmetric positive definite
+// matrices: G points at the leaf's first element (row stride ldg, batch stride strideG), likewise R; X: the leaf's
+// kTriBlock x kTriBlock inverse block per matrix (batch stride strideX), completed with an identity for short leaves.
+// info[b] is incremented when a pivot of matrix b was not positive.
+cudaError_t launch_chol_inv_leaf(const float* G, long long ldg, long long strideG, float* R, long long ldr, long long strideR,
+                                 float* X, long long strideX, int batch, int size, int* info, cudaStream_t stream);
+
 // Row-major upper triangle of square matrices, [batch, n, n] <-> [batch, n (n + 1) / 2]; elements of 2 or 4 bytes are
 // moved as bits.  Unpacking writes zeros below the diagonal.  blockIdx.y = batch (<= 65535).
 cudaError_t launch_triu_pack(const void* dense, void* line, int elem_bytes, int batch, int n, cudaStream_t stream);

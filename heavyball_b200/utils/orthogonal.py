@@ -210,24 +210,41 @@ _CHOL_LEAF = 128
 _CHOLQR_MIN = 256  # below this width the panel-wise method is already cheap
 
 
-def _chol_upper_blocked(G: Tensor, R: Tensor, bad: Tensor, lo: int, hi: int):
+def _chol_upper_blocked(G: Tensor, R: Tensor, bad: Tensor, lo: int, hi: int, inv: Tensor = None):
     """Upper Cholesky factor of the (batched) SPD block ``G[lo:hi, lo:hi]`` into ``R[lo:hi, lo:hi]``, recursively:
-    ``R11 = chol(G11)``, ``R12 = R11^-T G12``, ``R22 = chol(G22 - R12^T R12)``.  Only the 128-wide leaves are library
-    factorisations (batched over every matrix at once); the triangular solves and Schur complements are matrix
-    products, which on sm_100a run on the tensor cores.  ``G`` is overwritten; ``bad`` counts failed leaves per matrix."""
+    ``R11 = chol(G11)``, ``R12 = R11^-T G12``, ``R22 = chol(G22 - R12^T R12)``.  Only the 128-wide leaves are
+    factorisations proper (one kernel for the whole batch, which also leaves the leaf's inverse in ``inv`` for every
+    triangular solve that follows; the library's batched factorisation where the extension does not apply); the
+    triangular solves and Schur complements are matrix products, which on sm_100a run on the tensor cores.  ``G`` is
+    overwritten; ``bad`` counts failed leaves per matrix."""
     n = hi - lo
     if n <= _CHOL_LEAF:
+        if inv is not None:
+            from .. import ops
+
+            ops.load().chol_inv_leaf(G, R, inv, lo, n, bad)
+            ops.launch_counter.count += 1
+            return
         r, info = torch.linalg.cholesky_ex(G[:, lo:hi, lo:hi], upper=True)
         R[:, lo:hi, lo:hi] = r
         bad += info.ne(0)
         return
     mid = lo + max(_CHOL_LEAF, (n // 2) // _CHOL_LEAF * _CHOL_LEAF)
-    _chol_upper_blocked(G, R, bad, lo, mid)
+    _chol_upper_blocked(G, R, bad, lo, mid, inv)
     # X^T R11 = G12^T  <=>  X = R11^-T G12 = R12
-    xt = _solve_right_upper(R[:, lo:mid, lo:mid], G[:, lo:mid, mid:hi].mT.contiguous())
+    xt = _solve_right_upper(R[:, lo:mid, lo:mid], G[:, lo:mid, mid:hi].mT.contiguous(), inv, lo // _CHOL_LEAF)
     R[:, lo:mid, mid:hi] = xt.mT
     G[:, mid:hi, mid:hi] -= _mm(xt, xt, False, True)
-    _chol_upper_blocked(G, R, bad, mid, hi)
+    _chol_upper_blocked(G, R, bad, mid, hi, inv)
+
+
+def _leaf_inverse_buffer(gram: Tensor):
+    """Storage for the inverses of the 128-wide diagonal leaves of a batched factor when the extension's leaf kernel
+    applies (fp32 CUDA on sm_100a), else ``None``."""
+    if _skinny_kernels(gram) is None or gram.ndim != 3:
+        return None
+    blocks = (gram.shape[-1] + _CHOL_LEAF - 1) // _CHOL_LEAF
+    return torch.empty(gram.shape[0], blocks, _CHOL_LEAF, _CHOL_LEAF, device=gram.device, dtype=gram.dtype)
 
 
 _CHOLQR_SHIFT = 1e-5  # of the Gram matrix's trace bound; one shifted round lowers the condition number ~300-fold
@@ -260,8 +277,9 @@ def _cholesky_qr2(x: Tensor, shifted_rounds: int = 0):
             # unit columns: the diagonal is 1 and lambda_max <= k
             gram.diagonal(dim1=-2, dim2=-1).add_(_CHOLQR_SHIFT * k)
         r = torch.zeros_like(gram)
-        _chol_upper_blocked(gram, r, info, 0, k)
-        a = _solve_right_upper(r, a)
+        inv = _leaf_inverse_buffer(gram)
+        _chol_upper_blocked(gram, r, info, 0, k, inv)
+        a = _solve_right_upper(r, a, inv, 0)
         if rnd < shifted_rounds:  # columns shrank by different amounts: back to unit columns for the next round
             a = a / a.norm(dim=-2, keepdim=True).clamp_(min=tiny)
     bad += (_mm(a, a, True, False) - eye).abs().amax(dim=(-2, -1)).gt(_CHOLQR_ACCEPT)

@@ -151,3 +151,33 @@ def test_shifted_cholesky_qr_reaches_worse_conditioning(decades, shifted):
     if decades <= 5:  # beyond that the trailing columns of the fp32 input are rounding noise in any method
         ref = torch.linalg.qr(a).Q
         assert ((q.double() * ref).sum(-2).abs() - 1).abs().max().item() < 1e-2
+
+
+@pytest.mark.parametrize("n", [128, 300, 1024])
+def test_blocked_cholesky_with_the_leaf_kernel(n):
+    """128-wide leaves are factored and inverted by one kernel for the whole batch; the inverses serve every solve of
+    the recursion.  A matrix that is not positive definite is counted, the others are unaffected."""
+    from heavyball_b200.utils.orthogonal import _chol_upper_blocked, _leaf_inverse_buffer
+
+    torch.manual_seed(n)
+    B = 3
+    x = torch.randn(B, n, 2 * n, device="cuda", dtype=torch.float64)
+    g64 = x @ x.mT / (2 * n) + 0.1 * torch.eye(n, device="cuda", dtype=torch.float64)
+    g = g64.float()
+    g[1, n // 2, n // 2] = -1.0  # breaks matrix 1 only
+    ref = torch.linalg.cholesky(g64, upper=True)
+    work, r = g.clone(), torch.zeros_like(g)
+    bad = torch.zeros(B, dtype=torch.int32, device="cuda")
+    inv = _leaf_inverse_buffer(work)
+    assert inv is not None
+    _chol_upper_blocked(work, r, bad, 0, n, inv)
+    torch.cuda.synchronize()
+    assert bad.tolist()[0] == 0 and bad.tolist()[2] == 0 and bad.tolist()[1] > 0
+    for b in (0, 2):
+        assert float((r[b].double() - ref[b]).abs().max()) < 2e-4 * float(ref[b].abs().max())
+        assert float(r[b].tril(-1).abs().max()) == 0
+        for blk in range((n + 127) // 128):
+            lo, hi = blk * 128, min(n, blk * 128 + 128)
+            want = torch.linalg.inv(r[b, lo:hi, lo:hi].double())
+            got = inv[b, blk, : hi - lo, : hi - lo].double()
+            assert float((got - want).abs().max()) < 1e-3 * float(want.abs().max())

@@ -291,12 +291,12 @@ def matmul_supported(a: torch.Tensor, b: torch.Tensor) -> bool:
     )  # fmt: skip
 
 
-EPI_STORE, EPI_LERP, EPI_ADAM, EPI_LAPROP = range(4)  # mirror of hb::Tf32EpilogueMode
+EPI_STORE, EPI_LERP, EPI_ADAM, EPI_LAPROP, EPI_ADD = range(5)  # mirror of hb::Tf32EpilogueMode
 SPLIT_NONE, SPLIT_ROWS, SPLIT_COLS = range(3)
 
 
 def tf32_split(x: torch.Tensor, same: bool = True, trans: bool = False):
-    """Split-tf32 operands of a contiguous fp32 ``[batch, R, C]`` tensor, one pass over ``x``.  Returns ``(same, trans)``:
+    """Split-tf32 operands of an fp32 ``[batch, R, C]`` tensor or view (unit inner stride), one pass over ``x``.  Returns ``(same, trans)``:
     ``same`` has the rows of ``x`` as operand rows (``K = C``), ``trans`` its columns (``K = R``); an orientation that
     was not asked for is ``None``.  Either buffer can be the left or the right operand of :func:`tf32_gemm`, so matrices
     that rarely change (eigenbases, preconditioner factors) are split once and kept."""
@@ -312,6 +312,7 @@ def tf32_gemm(a2: torch.Tensor, b2: torch.Tensor, K: int, *, mode: int = EPI_STO
     fp32-level accuracy on the tf32 tensor cores.
 
     ``mode``: ``EPI_STORE`` writes ``alpha * acc``; ``EPI_LERP`` updates ``out <- out + (alpha * acc - out) * w`` in place;
+    ``EPI_ADD`` updates ``out <- out + alpha * acc`` in place (``out`` may be a view with unit inner stride);
     ``EPI_ADAM`` / ``EPI_LAPROP`` advance the fp32 moments ``m``, ``v`` (``[batch, M, N]``, in place, coefficients ``b1``,
     ``b2c`` already debiased) with ``alpha * acc`` as the gradient and pass the preconditioned value on.
     ``out`` (fp32 ``[batch, M, N]``) receives the result; ``split_out`` additionally (or instead) returns it as a split

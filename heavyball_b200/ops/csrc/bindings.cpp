@@ -279,13 +279,14 @@ at::Tensor cross_entropy_(at::Tensor& logits, const at::Tensor& targets, const a
 // (same, trans): same = [batch, R, 2 kp(C)] (operand rows = rows of x), trans = [batch, C, 2 kp(R)] (operand rows =
 // columns of x); an orientation that was not asked for comes back undefined.
 std::vector<at::Tensor> tf32_split(const at::Tensor& x, bool want_same, bool want_trans) {
-  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.dim() == 3 && x.is_contiguous(),
-              "tf32_split: contiguous fp32 [batch, rows, cols] CUDA tensor");
+  // views are welcome: any row and batch stride, unit inner stride
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.dim() == 3 && x.stride(2) == 1 && x.size(0) >= 1 && x.size(1) >= 1 &&
+                  x.size(2) >= 1, "tf32_split: fp32 [batch, rows, cols] CUDA tensor with unit inner stride");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t batch = x.size(0), R = x.size(1), C = x.size(2);
-  at::Tensor same = want_same ? at::empty({batch, R, 2 * hb::tf32_split_kp(C)}, x.options()) : at::Tensor();
-  at::Tensor trans = want_trans ? at::empty({batch, C, 2 * hb::tf32_split_kp(R)}, x.options()) : at::Tensor();
-  check(hb::launch_tf32_split(x.data_ptr<float>(), C, R * C, (int)R, (int)C, (int)batch,
+  at::Tensor same = want_same ? at::empty({batch, R, 2 * hb::tf32_split_kp(C)}, x.options().memory_format(at::MemoryFormat::Contiguous)) : at::Tensor();
+  at::Tensor trans = want_trans ? at::empty({batch, C, 2 * hb::tf32_split_kp(R)}, x.options().memory_format(at::MemoryFormat::Contiguous)) : at::Tensor();
+  check(hb::launch_tf32_split(x.data_ptr<float>(), x.stride(1), x.stride(0), (int)R, (int)C, (int)batch,
                               want_same ? same.data_ptr<float>() : nullptr, want_trans ? trans.data_ptr<float>() : nullptr,
                               at::cuda::getCurrentCUDAStream()), "tf32 split");
   return {same, trans};
@@ -329,7 +330,7 @@ at::Tensor tf32_gemm(const at::Tensor& a2, const at::Tensor& b2, int64_t K, int 
   // X X^T (one buffer as both operands): upper tiles only, mirrored on store.  An in-place lerp target is then
   // symmetric by construction (it only ever receives symmetric increments).
   E.symmetric = (a2.data_ptr() == b2.data_ptr() && M == N && E.C != nullptr && E.S == nullptr &&
-                 (mode == hb::kEpiStore || mode == hb::kEpiLerp)) ? 1 : 0;
+                 (mode == hb::kEpiStore || mode == hb::kEpiLerp || mode == hb::kEpiAdd)) ? 1 : 0;
   check(hb::launch_tf32_gemm(a2.data_ptr<float>(), b2.data_ptr<float>(), (int)M, (int)N, (int)K, (int)batch, E,
                              status.data_ptr<int>(), at::cuda::getCurrentCUDAStream()), "tf32 gemm");
   return s;

@@ -192,67 +192,102 @@ cudaError_t launch_tri_inv_blocks(const float* Q, long long ld, long long stride
 
 
 // ------------------------------------------------------------------------------------------ Cholesky leaf
-// One CTA factors one (up to) 128 x 128 symmetric positive definite block G = R^T R (R upper triangular) and inverts R,
-// both in shared memory.  Thread j owns column j.
-//   factor:  for k = 0 .. n-1:  r_kk = sqrt(g_kk);  r_kj = g_kj / r_kk (j > k);  g_ij -= r_ki r_kj (k < i <= j)
-//   invert:  x_jj = 1 / r_jj,   x_ij = -(sum_{k = i+1 .. j} r_ik x_kj) / r_ii   for i = j-1 .. 0
+// One CTA of 1024 threads factors one (up to) 128 x 128 symmetric positive definite block G = R^T R (R upper triangular)
+// and inverts R, both in shared memory.
+//   factor (right-looking, every trailing element has its own thread slot):
+//     for k = 0 .. n-1:  r_kk = sqrt(g_kk);  r_kj = g_kj / r_kk (j > k);  g_ij -= r_ki r_kj (k < i <= j)
+//   invert: the four 32 x 32 diagonal blocks by back substitution (one warp each, lane = column), then the blocks
+//     above the diagonal by distance d = 1, 2, 3:  X_IJ = -X_II (sum_{K = I+1 .. J} R_IK X_KJ), J = I + d,
+//     as 32 x 32 block products with one output element per thread.
 // A non-positive or non-finite pivot is replaced by 1 and counted in info[b] (the result for that matrix is then
-// meaningless, the others are unaffected).  The batched library factorisation of the same leaf takes ~160 us per call
-// in ten launches, and the blocked solves around it each used to invert the leaves again.
+// meaningless, the others are unaffected).  The refresh of an eigenbasis factors 16 leaves per 2048-wide factor and
+// round, one after the other, so the latency of this kernel is what counts: a thread-per-column version took 270 us
+// (dependent shared-memory loads), the batched library factorisation plus a separate inversion 230 us.
 namespace {
 
-__global__ void __launch_bounds__(kTriBlock) chol_inv_leaf_kernel(const float* __restrict__ G, long long ldg, long long strideG,
-                                                                  float* __restrict__ R, long long ldr, long long strideR,
-                                                                  float* __restrict__ X, long long strideX, int size,
-                                                                  int* __restrict__ info) {
+constexpr int kLeafThreads = 1024;
+constexpr int kLeafLd = kTriBlock + 1;
+
+__global__ void __launch_bounds__(kLeafThreads) chol_inv_leaf_kernel(const float* __restrict__ G, long long ldg, long long strideG,
+                                                                     float* __restrict__ R, long long ldr, long long strideR,
+                                                                     float* __restrict__ X, long long strideX, int size,
+                                                                     int* __restrict__ info) {
   extern __shared__ float leaf_smem[];
-  float(*t)[kTriBlock + 1] = (float(*)[kTriBlock + 1])leaf_smem;
-  float(*x)[kTriBlock + 1] = (float(*)[kTriBlock + 1])(leaf_smem + kTriBlock * (kTriBlock + 1));
+  float(*t)[kLeafLd] = (float(*)[kLeafLd])leaf_smem;
+  float(*x)[kLeafLd] = (float(*)[kLeafLd])(leaf_smem + kTriBlock * kLeafLd);
   __shared__ int failed;
-  const int b = blockIdx.x, j = threadIdx.x;
+  const int b = blockIdx.x, tid = threadIdx.x, ty = tid >> 5, tx = tid & 31;
   const float* g = G + (long long)b * strideG;
-  if (j == 0) failed = 0;
-  for (int i = 0; i < kTriBlock; ++i) {  // upper part of the block; the rest of a short block is an identity
+  if (tid == 0) failed = 0;
+  for (int idx = tid; idx < kTriBlock * kTriBlock; idx += kLeafThreads) {  // upper part; a short block is completed by an identity
+    const int i = idx >> 7, j = idx & (kTriBlock - 1);
     float v = (i == j) ? 1.f : 0.f;
     if (i < size && j < size && j >= i) v = g[(long long)i * ldg + j];
     t[i][j] = v;
     x[i][j] = 0.f;
   }
   __syncthreads();
+
   for (int k = 0; k < size; ++k) {
-    const float d = t[k][k];
+    const float d = t[k][k];  // written for the last time in the previous step's trailing update
     const bool ok = d > 0.f && d < 3.0e38f;
-    const float piv = ok ? sqrtf(d) : 1.f;
-    __syncthreads();  // everyone has read the pivot before it is overwritten
-    if (j == k) {
-      t[k][k] = piv;
-      if (!ok) failed = 1;
-    } else if (j > k) {
-      t[k][j] = t[k][j] / piv;
-    }
+    const float inv_piv = ok ? rsqrtf(d) : 1.f;
+    if (tid > k && tid < size) t[k][tid] *= inv_piv;
     __syncthreads();
-    if (j > k) {
-      const float rkj = t[k][j];
-      for (int i = k + 1; i <= j; ++i) t[i][j] = fmaf(-t[k][i], rkj, t[i][j]);
+    if (tid == 0) {
+      t[k][k] = ok ? d * inv_piv : 1.f;  // sqrt(d); nobody reads the diagonal entry during the trailing update
+      if (!ok) failed = 1;
+    }
+    for (int i = k + 1 + ty; i < size; i += 32) {
+      const float rki = t[k][i];
+      for (int j = i + tx; j < size; j += 32) t[i][j] = fmaf(-rki, t[k][j], t[i][j]);
     }
     __syncthreads();
   }
-  {
-    x[j][j] = 1.0f / t[j][j];
-    for (int i = j - 1; i >= 0; --i) {
+
+  if (tid < kTriBlock) {  // diagonal 32 x 32 blocks: warp = block, lane = column
+    const int base = tid & ~31, jl = tid & 31, col = base + jl;
+    x[col][col] = 1.0f / t[col][col];
+    for (int i = jl - 1; i >= 0; --i) {
       float sum = 0.f;
-      for (int k = i + 1; k <= j; ++k) sum = fmaf(t[i][k], x[k][j], sum);
-      x[i][j] = -sum / t[i][i];
+      for (int k = i + 1; k <= jl; ++k) sum = fmaf(t[base + i][base + k], x[base + k][col], sum);
+      x[base + i][col] = -sum / t[base + i][base + i];
     }
   }
   __syncthreads();
+  for (int dist = 1; dist < kTriBlock / 32; ++dist) {
+    // S_I = sum_K R_IK X_KJ, parked in the (otherwise unused) mirror position below the diagonal
+    for (int I = 0; I + dist < kTriBlock / 32; ++I) {
+      const int J = I + dist;
+      float s0 = 0.f, s1 = 0.f;
+      const float* rrow = &t[32 * I + ty][0];
+      for (int k = 32 * (I + 1); k < 32 * (J + 1); k += 2) {
+        s0 = fmaf(rrow[k], x[k][32 * J + tx], s0);
+        s1 = fmaf(rrow[k + 1], x[k + 1][32 * J + tx], s1);
+      }
+      x[32 * J + ty][32 * I + tx] = s0 + s1;
+    }
+    __syncthreads();
+    for (int I = 0; I + dist < kTriBlock / 32; ++I) {
+      const int J = I + dist;
+      float s0 = 0.f, s1 = 0.f;
+      for (int k = ty; k < 32; k += 2) {  // X_II is upper triangular: columns below the row index are zero
+        s0 = fmaf(x[32 * I + ty][32 * I + k], x[32 * J + k][32 * I + tx], s0);
+        if (k + 1 < 32) s1 = fmaf(x[32 * I + ty][32 * I + k + 1], x[32 * J + k + 1][32 * I + tx], s1);
+      }
+      x[32 * I + ty][32 * J + tx] = -(s0 + s1);
+    }
+    __syncthreads();
+  }
+
   float* r = R + (long long)b * strideR;
   float* out = X + (long long)b * strideX;
-  for (int i = 0; i < kTriBlock; ++i) {
+  for (int idx = tid; idx < kTriBlock * kTriBlock; idx += kLeafThreads) {
+    const int i = idx >> 7, j = idx & (kTriBlock - 1);
     if (i < size && j < size) r[(long long)i * ldr + j] = j >= i ? t[i][j] : 0.f;
-    out[i * kTriBlock + j] = x[i][j];
+    out[idx] = j >= i ? x[i][j] : 0.f;
   }
-  if (j == 0 && failed && info != nullptr) atomicAdd(info + b, 1);
+  if (tid == 0 && failed && info != nullptr) atomicAdd(info + b, 1);
 }
 
 }  // namespace
@@ -268,7 +303,7 @@ cudaError_t launch_chol_inv_leaf(const float* G, long long ldg, long long stride
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  chol_inv_leaf_kernel<<<batch, kTriBlock, kBytes, stream>>>(G, ldg, strideG, R, ldr, strideR, X, strideX, size, info);
+  chol_inv_leaf_kernel<<<batch, kLeafThreads, kBytes, stream>>>(G, ldg, strideG, R, ldr, strideR, X, strideX, size, info);
   return cudaGetLastError();
 }
 

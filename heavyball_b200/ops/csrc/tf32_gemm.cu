@@ -145,15 +145,17 @@ __device__ __forceinline__ void epilogue_direct(uint32_t tmem_warp, int lane, fl
         if (E.C != nullptr) {
           float* cp = E.C + b64 * E.strideC + (int64_t)row * E.ldc + col;
           const bool fast = c_vec && col + 3 < N;
-          if (E.mode == kEpiLerp) {
+          if (E.mode == kEpiLerp || E.mode == kEpiAdd) {
+            // lerp: o + (x - o) w;  add: o + x  (the same expression with the old value left out of the difference)
+            const float keep = E.mode == kEpiLerp ? 1.f : 0.f, w = E.mode == kEpiLerp ? E.w : 1.f;
             if (fast) {
               const float4 o = *(const float4*)cp;
-              x[0] = o.x + (x[0] - o.x) * E.w; x[1] = o.y + (x[1] - o.y) * E.w;
-              x[2] = o.z + (x[2] - o.z) * E.w; x[3] = o.w + (x[3] - o.w) * E.w;
+              x[0] = o.x + (x[0] - keep * o.x) * w; x[1] = o.y + (x[1] - keep * o.y) * w;
+              x[2] = o.z + (x[2] - keep * o.z) * w; x[3] = o.w + (x[3] - keep * o.w) * w;
             } else {
 #pragma unroll
               for (int e = 0; e < 4; ++e)
-                if (col + e < N) { const float o = cp[e]; x[e] = o + (x[e] - o) * E.w; }
+                if (col + e < N) { const float o = cp[e]; x[e] = o + (x[e] - keep * o) * w; }
             }
           }
           if (fast) {
@@ -568,9 +570,9 @@ cudaError_t launch_tf32_gemm(const float* A2, const float* B2, int M, int N, int
   }
   if (M == 0 || N == 0 || batch == 0) return cudaSuccess;
   if ((E.mode == kEpiAdam || E.mode == kEpiLaProp) && (E.m == nullptr || E.v == nullptr)) return cudaErrorInvalidValue;
-  if (E.mode == kEpiLerp && E.C == nullptr) return cudaErrorInvalidValue;
+  if ((E.mode == kEpiLerp || E.mode == kEpiAdd) && E.C == nullptr) return cudaErrorInvalidValue;
   if (E.tri && (M != N || M != K || E.symmetric)) return cudaErrorInvalidValue;
-  if (E.symmetric && (A2 != B2 || M != N || E.C == nullptr || E.S != nullptr || (E.mode != kEpiStore && E.mode != kEpiLerp)))
+  if (E.symmetric && (A2 != B2 || M != N || E.C == nullptr || E.S != nullptr || (E.mode != kEpiStore && E.mode != kEpiLerp && E.mode != kEpiAdd)))
     return cudaErrorInvalidValue;
   const int64_t kp = tf32_split_kp(K), ld = 2 * kp;
   CUtensorMap ma, mb, mc;

@@ -22,6 +22,7 @@ enum Tf32EpilogueMode : int {
   kEpiLerp = 1,     // C <- C + (alpha * acc - C) * w            (statistics update, in place on C)
   kEpiAdam = 2,     // x = alpha*acc; m <- lerp(m, x, 1-b1); v <- lerp(v, x*x, 1-b2); out = m / max(sqrt(v), eps)
   kEpiLaProp = 3,   // x = alpha*acc; v <- lerp(v, x*x, 1-b2); m <- lerp(m, x / max(sqrt(v), eps), 1-b1); out = m
+  kEpiAdd = 4,      // C <- C + alpha * acc                       (Schur complements and solve updates, in place on C)
 };
 
 // What the epilogue does with the finished [M, N] tile values.  Any of C / S may be null.
@@ -41,7 +42,7 @@ struct Tf32Epilogue {
                            // triangular matrix, M == N == K): a tile only walks the K range where both are non-zero,
                            // tiles below the diagonal are stored as zeros without a product
   int symmetric;           // A2 == B2 (so M == N and the product is symmetric): only tiles on or above the diagonal are
-                           // computed and each is also stored transposed.  kEpiStore / kEpiLerp with C set and S null.
+                           // computed and each is also stored transposed.  kEpiStore / kEpiLerp / kEpiAdd with C set and S null.
 };
 
 // out[b] = epilogue(A[b] * B[b]^T) over split operands A2: [batch, M, 2 * kp(K)], B2: [batch, N, 2 * kp(K)].

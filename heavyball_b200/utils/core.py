@@ -496,17 +496,60 @@ def _leaf_inverses(q: Tensor):
     return ops.load().tri_inv_blocks(q)
 
 
-def _solve_right_upper(q: Tensor, b: Tensor, inv: Optional[Tensor] = None, first_block: int = 0) -> Tensor:
+def _tc_sub_product(c: Tensor, a: Tensor, b: Tensor, b_transposed: bool = False) -> bool:
+    """``c -= a @ b`` (``b_transposed``: ``c -= a @ b^T``) in place on the view ``c`` with the subtraction in the
+    product's epilogue and the operands split straight from their views; ``False`` when the tensor-core path does not
+    apply (the caller then uses plain tensor arithmetic)."""
+    if not (c.is_cuda and c.dtype == torch.float32 and c.ndim == 3 and getattr(_settings(), "tensor_core_matmul", True)):
+        return False
+    from .. import ops
+
+    K = a.shape[-1]
+    if not ops.available() or min(c.shape[-2], c.shape[-1], K) < 128:
+        return False
+    if any(t.stride(-1) != 1 or t.dtype != torch.float32 for t in (a, b, c)) or c.data_ptr() % 16 or c.stride(-2) % 4 or c.stride(0) % 4:
+        return False
+    a_s, _ = ops.tf32_split(a, True, False)
+    if b_transposed:
+        b_s = a_s if (b.data_ptr() == a.data_ptr() and b.shape == a.shape and b.stride() == a.stride()) else ops.tf32_split(b, True, False)[0]
+    else:
+        b_s = ops.tf32_split(b, False, True)[1]
+    ops.tf32_gemm(a_s, b_s, K, mode=ops.EPI_ADD, alpha=-1.0, out=c)
+    return True
+
+
+def _solve_right_upper_into(q: Tensor, b: Tensor, x: Tensor, inv: Tensor, first_block: int):
+    """``x <- b q^-1`` for upper-triangular ``q`` through the leaf inverses ``inv``; ``b`` is consumed (its columns to the
+    right receive the updates in place).  All three are views with unit inner stride; nothing is allocated besides the
+    split operands, nothing is concatenated."""
+    d = q.shape[-1]
+    if d <= _TRSM_LEAF:
+        torch.bmm(b, inv[:, first_block, :d, :d], out=x)
+        return
+    h = max(_TRSM_LEAF, (d // 2) // _TRSM_LEAF * _TRSM_LEAF)
+    _solve_right_upper_into(q[..., :h, :h], b[..., :h], x[..., :h], inv, first_block)
+    if not _tc_sub_product(b[..., h:], x[..., :h], q[..., :h, h:]):
+        torch.baddbmm(b[..., h:], x[..., :h], q[..., :h, h:], alpha=-1.0, out=b[..., h:])
+    _solve_right_upper_into(q[..., h:, h:], b[..., h:], x[..., h:], inv, first_block + h // _TRSM_LEAF)
+
+
+def _solve_right_upper(q: Tensor, b: Tensor, inv: Optional[Tensor] = None, first_block: int = 0, consume_b: bool = False) -> Tensor:
     """``X`` with ``X q = b`` for upper-triangular ``q`` (batched).  Large CUDA problems are split recursively,
     ``X_1 = b_1 q_11^-1``, ``X_2 = (b_2 - X_1 q_12) q_22^-1``, so that everything is matrix products: the off-diagonal
-    updates run on the tensor cores, and the 128-wide leaves multiply by block inverses that one small kernel
-    prepares for the whole batch (the library's right-hand triangular solve walks the batch one matrix at a time at
-    a few TFLOP/s and was half of a preconditioner update's GPU time)."""
+    updates run on the tensor cores (subtraction in the epilogue, in place), and the 128-wide leaves multiply by block
+    inverses that one small kernel prepares for the whole batch (the library's right-hand triangular solve walks the
+    batch one matrix at a time at a few TFLOP/s and was half of a preconditioner update's GPU time).  ``consume_b``: the
+    caller no longer needs ``b`` (it becomes the workspace instead of a copy of it)."""
     d = q.shape[-1]
     fast = q.is_cuda and q.dtype == torch.float32
     if fast and inv is None and d > 1:
         inv = _leaf_inverses(q)
         first_block = 0
+    if fast and inv is not None and q.ndim == 3 and b.ndim == 3 and b.dtype == torch.float32:
+        work = b if (consume_b and b.stride(-1) == 1) else b.clone(memory_format=torch.contiguous_format)
+        x = torch.empty(b.shape, device=b.device, dtype=b.dtype)
+        _solve_right_upper_into(q, work, x, inv, first_block)
+        return x
     if d <= _TRSM_LEAF or not fast:
         if inv is not None and fast:
             return b @ inv[:, first_block, :d, :d]

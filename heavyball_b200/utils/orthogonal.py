@@ -23,7 +23,7 @@ import torch
 from torch import Tensor
 
 from .core import copy_stochastic_, list_guard, promote, stochastic_divide_, stochastic_divide_with_eps_, stochastic_round_
-from .core import _mm, _solve_right_upper
+from .core import _mm, _solve_right_upper, _tc_sub_product
 
 
 def _settings():
@@ -232,9 +232,10 @@ def _chol_upper_blocked(G: Tensor, R: Tensor, bad: Tensor, lo: int, hi: int, inv
     mid = lo + max(_CHOL_LEAF, (n // 2) // _CHOL_LEAF * _CHOL_LEAF)
     _chol_upper_blocked(G, R, bad, lo, mid, inv)
     # X^T R11 = G12^T  <=>  X = R11^-T G12 = R12
-    xt = _solve_right_upper(R[:, lo:mid, lo:mid], G[:, lo:mid, mid:hi].mT.contiguous(), inv, lo // _CHOL_LEAF)
+    xt = _solve_right_upper(R[:, lo:mid, lo:mid], G[:, lo:mid, mid:hi].mT.contiguous(), inv, lo // _CHOL_LEAF, consume_b=True)
     R[:, lo:mid, mid:hi] = xt.mT
-    G[:, mid:hi, mid:hi] -= _mm(xt, xt, False, True)
+    if not _tc_sub_product(G[:, mid:hi, mid:hi], xt, xt, b_transposed=True):  # Schur complement, upper tiles mirrored
+        G[:, mid:hi, mid:hi] -= _mm(xt, xt, False, True)
     _chol_upper_blocked(G, R, bad, mid, hi, inv)
 
 
@@ -279,7 +280,7 @@ def _cholesky_qr2(x: Tensor, shifted_rounds: int = 0):
         r = torch.zeros_like(gram)
         inv = _leaf_inverse_buffer(gram)
         _chol_upper_blocked(gram, r, info, 0, k, inv)
-        a = _solve_right_upper(r, a, inv, 0)
+        a = _solve_right_upper(r, a, inv, 0, consume_b=rnd > 0 or a.data_ptr() != x.data_ptr())
         if rnd < shifted_rounds:  # columns shrank by different amounts: back to unit columns for the next round
             a = a / a.norm(dim=-2, keepdim=True).clamp_(min=tiny)
     bad += (_mm(a, a, True, False) - eye).abs().amax(dim=(-2, -1)).gt(_CHOLQR_ACCEPT)

@@ -98,8 +98,34 @@ __device__ __forceinline__ void epilogue_direct(uint32_t tmem_warp, int lane, fl
     __syncwarp();
 
     const int col = col0 + cg;
-#pragma unroll 2
-    for (int it = 0; it < 8; ++it) {
+    // What the epilogue reads from global memory (moments, or the old value of C) is fetched four steps at a time
+    // before the first of them is used: a step-by-step load -> compute -> store chain pays one memory round trip per step
+    // (stores may alias the next step's loads, so the compiler cannot hoist them), which for the small products of a
+    // blocked solve was longer than the product itself.
+    const bool fast_state = moments && state_vec && col + 3 < N;
+    const bool fast_old = (E.mode == kEpiLerp || E.mode == kEpiAdd) && E.C != nullptr && c_vec && col + 3 < N;
+    float4 pa[4], pb[4];
+#pragma unroll 1
+    for (int half = 0; half < 2; ++half) {
+    if (fast_state || fast_old) {
+#pragma unroll
+      for (int i4 = 0; i4 < 4; ++i4) {
+        const int row = row0 + (half * 4 + i4) * 4 + sub;
+        pa[i4] = make_float4(0.f, 0.f, 0.f, 0.f);
+        pb[i4] = pa[i4];
+        if (row < M) {
+          if (fast_state) {
+            pa[i4] = *(const float4*)(E.m + (b64 * M + row) * (int64_t)N + col);
+            pb[i4] = *(const float4*)(E.v + (b64 * M + row) * (int64_t)N + col);
+          } else {
+            pa[i4] = *(const float4*)(E.C + b64 * E.strideC + (int64_t)row * E.ldc + col);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int i4 = 0; i4 < 4; ++i4) {
+      const int it = half * 4 + i4;
       const int lr = it * 4 + sub, row = row0 + lr;
       float* sp = stage + lr * kStageLd + cg;
       const float4 x4 = *(const float4*)sp;
@@ -108,10 +134,10 @@ __device__ __forceinline__ void epilogue_direct(uint32_t tmem_warp, int lane, fl
         if (moments) {
           float* mp = E.m + (b64 * M + row) * (int64_t)N + col;
           float* vp = E.v + (b64 * M + row) * (int64_t)N + col;
-          const bool fast = state_vec && col + 3 < N;
+          const bool fast = fast_state;
           float m4[4], s4[4];
           if (fast) {
-            const float4 a = *(const float4*)mp, c = *(const float4*)vp;
+            const float4 a = pa[i4], c = pb[i4];
             m4[0] = a.x; m4[1] = a.y; m4[2] = a.z; m4[3] = a.w;
             s4[0] = c.x; s4[1] = c.y; s4[2] = c.z; s4[3] = c.w;
           } else {
@@ -149,7 +175,7 @@ __device__ __forceinline__ void epilogue_direct(uint32_t tmem_warp, int lane, fl
             // lerp: o + (x - o) w;  add: o + x  (the same expression with the old value left out of the difference)
             const float keep = E.mode == kEpiLerp ? 1.f : 0.f, w = E.mode == kEpiLerp ? E.w : 1.f;
             if (fast) {
-              const float4 o = *(const float4*)cp;
+              const float4 o = pa[i4];
               x[0] = o.x + (x[0] - keep * o.x) * w; x[1] = o.y + (x[1] - keep * o.y) * w;
               x[2] = o.z + (x[2] - keep * o.z) * w; x[3] = o.w + (x[3] - keep * o.w) * w;
             } else {
@@ -180,6 +206,7 @@ __device__ __forceinline__ void epilogue_direct(uint32_t tmem_warp, int lane, fl
         *(float4*)(srow + E.kpS) = make_float4(lo[0], lo[1], lo[2], lo[3]);
       }
       if (along_rows) *(float4*)sp = make_float4(x[0], x[1], x[2], x[3]);
+    }
     }
 
     if (along_rows) {

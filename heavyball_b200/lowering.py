@@ -76,7 +76,8 @@ _PSGD_STAGES = {
 
 
 class _Program:
-    __slots__ = ("kind", "mars", "palm", "rule", "ortho", "stage", "stage_kw", "u_op", "gclip", "post", "routes", "workspace")
+    __slots__ = ("kind", "mars", "palm", "rule", "ortho", "stage", "stage_kw", "u_op", "gclip", "post", "routes", "workspace",
+                 "pre_project", "after", "stateless")
 
     def __init__(self, kind, mars, palm, rule, ortho=None, stage=None, stage_kw=None, u_op=0, gclip=None, post=None,
                  routes=None):  # fmt: skip
@@ -86,6 +87,9 @@ class _Program:
         self.post = post  # transform that consumes the rule's output inside the same launch (schedule-free)
         self.routes = routes  # kind "route": [(predicate or None for the default, sub-program)]
         self.workspace = {}
+        self.pre_project = False  # OrthoGrad on the gradient before the rule (dot products, then folded into the load)
+        self.after = None  # what happens to the rule's output in a second launch: ("sign", graft) or ("project",)
+        self.stateless = ()  # transforms of the chain that keep no state but still mark themselves as run
 
 
 def _unwrap(fn):
@@ -110,19 +114,20 @@ def _match(fns) -> Optional[_Program]:
         palm = fns.pop(0)
     if not fns:
         return None
-    if len(fns) == 1 and isinstance(fns[0], C.Route) and mars is None and gclip is None:
+    if isinstance(fns[-1], C.Route) and mars is None and gclip is None and not any(isinstance(f, C.Route) for f in fns[:-1]):
+        shared, router = fns[:-1], fns[-1]  # transforms in front of the router run in every branch
         routes = []
-        for pred, sub in [*fns[0].routes, (None, fns[0].default)]:
+        for pred, sub in [*router.routes, (None, router.default)]:
             if sub is None:
                 return None
-            inner = _match(sub)
+            inner = _match([*shared, *sub])
             if inner is None or inner.kind == "route" or inner.palm is not None:
                 return None
             routes.append((pred, inner))
         return _Program("route", None, palm, None, routes=routes)
     prog = _match_tail(fns, mars, palm)
     if prog is not None and gclip is not None:
-        if prog.kind not in ("elementwise", "orthogonal"):
+        if prog.kind not in ("elementwise", "orthogonal") or prog.pre_project or prog.after is not None:
             return None
         prog.gclip = gclip
     return prog
@@ -146,6 +151,33 @@ def _match_tail(fns, mars, palm) -> Optional[_Program]:
         if last_kw.get("cached", False):
             return None
         return _Program("psgd", mars, palm, rule, stage=last, stage_kw=last_kw, u_op=u_op)
+    if len(pairs) >= 2 and pairs[-1][0].fn_name == "apply_update" and not pairs[-1][1]:
+        pairs = pairs[:-1]  # the parameter update every lowered program ends with
+    if u_op == 0 and len(pairs) == 2 and mars is None:
+        (first, first_kw), (second, second_kw) = pairs
+        if (second.fn_name in ("update_by_msam", "update_by_hyperball") and first.fn_name == "scale_by_exp_avg_sq"
+                and not first_kw and not second_kw):  # fmt: skip
+            prog = _Program("elementwise", mars, palm, first, None)
+            prog.after = ("msam" if second.fn_name == "update_by_msam" else "hyperball", second)
+            prog.stateless = ()
+            return prog
+        if second.fn_name == "sign" and not first_kw and first.fn_name in _RULES and not first.fn_name.startswith("update_by"):
+            if set(second_kw) <= {"graft"}:
+                prog = _Program("elementwise", mars, palm, first, None)
+                prog.after = ("sign", bool(second_kw.get("graft", True)))
+                prog.stateless = (second,)
+                return prog
+        if not first_kw and not second_kw:
+            if second.fn_name == "orthogonalize_grad_to_param" and first.fn_name in _RULES and not first.fn_name.startswith("update_by"):
+                prog = _Program("elementwise", mars, palm, first, None)
+                prog.after = ("project",)
+                prog.stateless = (second,)
+                return prog
+            if first.fn_name == "orthogonalize_grad_to_param" and second.fn_name in _RULES:
+                prog = _Program("elementwise", mars, palm, second, None)
+                prog.pre_project = True
+                prog.stateless = (first,)
+                return prog
     if u_op or any(kw for _, kw in pairs):
         return None
     fns = [f for f, _ in pairs]
@@ -187,7 +219,8 @@ def describe(opt) -> str:
         else:
             inner = prog.rule.fn_name
         extra = [name for name, on in (("mars", prog.mars), ("palm", prog.palm), ("grad_clip", prog.gclip),
-                                       ("trust_region", prog.u_op), ("schedule_free", prog.post)) if on]  # fmt: skip
+                                       ("trust_region", prog.u_op), ("schedule_free", prog.post),
+                                       ("orthograd", prog.pre_project), (prog.after[0] if prog.after else "", prog.after)) if on]  # fmt: skip
         return f"{prog.kind}({inner})" + ("".join(f" +{e}" for e in extra))
 
     prog = _program(opt)
@@ -415,6 +448,21 @@ def _run(opt, prog, states, group, grads, params, on_gpu, check_only) -> bool:
         return False  # L2-style decay enters the moments: left to the PyTorch definition
     if prog.gclip is not None and plan is not None:
         return False  # the clip needs the norm of the reduced gradient, which peer kernels never materialise
+    if prog.pre_project or prog.after is not None:
+        # per-tensor dot products / norms of whole tensors: not under a partition plan; the projection reads the
+        # parameter next to the gradient (one dtype for the dot-product kernel); caution would need a third pass
+        if plan is not None or pecc_mode or pdt != torch.float32 or (prog.pre_project and gdt != pdt):
+            return False
+        if prog.after is not None and group["caution"]:
+            return False
+        if prog.after is not None and prog.after[0] in ("msam", "hyperball"):
+            consumer = prog.after[1]
+            if ecc_mode or sdt != torch.float32 or not _state_ready(consumer, states, False):
+                return False
+        if (prog.pre_project or (prog.after is not None and prog.after[0] == "project")) and any(p.numel() < 16 for p in params):
+            # the norm of the projected vector is taken from the dot products (x.x - 2 c p.x + c^2 p.p), which cancels
+            # completely when x is parallel to p - always the case for a one-element tensor
+            return False
     if check_only:
         return True
 
@@ -428,6 +476,10 @@ def _run(opt, prog, states, group, grads, params, on_gpu, check_only) -> bool:
             _mark_initialized(prog.ortho, st)
         if post is not None:
             _mark_initialized(post, st)
+        for tr in prog.stateless:
+            _mark_initialized(tr, st)
+        if prog.after is not None and prog.after[0] in ("msam", "hyperball"):
+            _mark_initialized(prog.after[1], st)
 
     # ---- selection: everything (single process / replicated) or this rank's share (peer data parallelism)
     peer_in, peer_out = {}, {}
@@ -499,6 +551,64 @@ def _run(opt, prog, states, group, grads, params, on_gpu, check_only) -> bool:
         launch(p=params_v, g=grads_v, s0=s0, s1=s1, s2=z, out_mode=ops.OUT_SCHEDULE_FREE, seed=_seed(opt, group, 0),
                **base, **epilogue)  # fmt: skip
         return True
+    if prog.kind == "elementwise" and prog.pre_project:
+        # OrthoGrad: g <- graft(g, g - (w.g / (w.w + eps)) w); the three dot products of every tensor come from one
+        # segmented reduction, the projection itself happens on load inside the rule's launch
+        n = len(params_v)
+        dots = ops.dot(params_v + params_v + grads_v, grads_v + params_v + grads_v).view(3, n).t().contiguous()
+        base.update(gsq=dots, gsq_stride=3, g_clip_mode=ops.CLIP_ORTHO, g_clip_at=group["eps"], g_clip_numel=1.0)
+    if prog.kind == "elementwise" and prog.after is not None and prog.after[0] == "msam":
+        # Momentum-SAM: z holds the unperturbed weights, the parameter sits at the ascent point z - rho m / |m|.
+        # Launch one advances second moment, momentum and z and sums m^2 per tensor; then p <- z, p -= (rho / |m|) m.
+        consumer = prog.after[1]
+        m = [st[consumer._val_names["exp_avg"]] for st in sub_states]
+        z = [st[consumer._val_names["z"]] for st in sub_states]
+        sums = torch.zeros(len(params_v), dtype=torch.float32, device=params[0].device)
+        launch(g=grads_v, s0=m, s1=s1, s2=z, out_mode=ops.OUT_UPDATE, dt_u=ops.NONE, scale=sums, accum_sumsq=1,
+               post_state=ops.POST_MSAM, seed=_seed(opt, group, 0),
+               **{**base, "n_state": 3, "b3": utils.beta_debias(utils.get_beta1(group), group["step"])}, **epilogue)  # fmt: skip
+        coef = sums.sqrt_().clamp_(min=1e-8).reciprocal_().mul_(group["sam_step_size"])
+        torch._foreach_copy_(params_v, z)
+        launch(p=params_v, u=m, scale=coef, use_tensor_scale=1, algo=ops.IDENTITY, u_is_input=1, out_mode=ops.OUT_PARAM,
+               dt_u=ops.dtype_code(m[0]), dt_p=base["dt_p"], dt_g=ops.NONE, dt_s=ops.NONE, lr=1.0, wd=0.0,
+               seed=_seed(opt, group, 1))  # fmt: skip
+        return True
+    if prog.kind == "elementwise" and prog.after is not None and prog.after[0] == "hyperball":
+        # u <- u + p d;  p <- p - lr n0 u / |u|;  p <- p n0 / |p|   (n0: the tensor's norm at initialisation)
+        consumer = prog.after[1]
+        n0 = torch.stack([st[consumer._val_names["init_norm"]].to(torch.float32).reshape(()) for st in sub_states])
+        scratch = _scratch(prog, params_v)
+        sums = torch.zeros(len(params_v), dtype=torch.float32, device=params[0].device)
+        decay = dict(post_state=ops.POST_DECAY_IN, p=params_v, wd=epilogue["wd"], cautious_wd=epilogue["cautious_wd"]) \
+            if epilogue["wd"] != 0 else {}  # fmt: skip
+        launch(g=grads_v, u=scratch, s0=s0, s0e=s0e, s1=s1, s1e=s1e, s2=s2, s2e=s2e, out_mode=ops.OUT_UPDATE, dt_u=ops.F32,
+               scale=sums, accum_sumsq=1, seed=_seed(opt, group, 0), **base, **decay)  # fmt: skip
+        coef = n0 / sums.sqrt_().clamp_(min=1e-12)
+        launch(p=params_v, u=scratch, scale=coef, use_tensor_scale=1, algo=ops.IDENTITY, u_is_input=1, out_mode=ops.OUT_PARAM,
+               dt_u=ops.F32, dt_p=base["dt_p"], dt_g=ops.NONE, dt_s=ops.NONE, lr=group["lr"], wd=0.0,
+               seed=_seed(opt, group, 1))  # fmt: skip
+        # back onto the sphere: p <- p s with s = n0 / |p|, written as p - (1 - s) p so the same kernel does it
+        shrink = 1.0 - n0 / ops.sumsq(params_v).sqrt_().clamp_(min=1e-12)
+        launch(p=params_v, u=params_v, scale=shrink, use_tensor_scale=1, algo=ops.IDENTITY, u_is_input=1,
+               out_mode=ops.OUT_PARAM, dt_u=base["dt_p"], dt_p=base["dt_p"], dt_g=ops.NONE, dt_s=ops.NONE, lr=1.0, wd=0.0,
+               seed=_seed(opt, group, 2))  # fmt: skip
+        return True
+    if prog.kind == "elementwise" and prog.after is not None:
+        n, dev = len(params_v), params[0].device
+        scratch = _scratch(prog, params_v)
+        second = dict(p=params_v, u=scratch, algo=ops.IDENTITY, u_is_input=1, out_mode=ops.OUT_PARAM, dt_u=ops.F32,
+                      dt_p=base["dt_p"], dt_g=ops.NONE, dt_s=ops.NONE, seed=_seed(opt, group, 1), **epilogue)  # fmt: skip
+        if prog.after[0] == "sign":
+            sums = torch.zeros(n, 2, dtype=torch.float32, device=dev)  # per tensor: sum u^2, number of non-zero u
+            launch(g=grads_v, u=scratch, s0=s0, s0e=s0e, s1=s1, s1e=s1e, s2=s2, s2e=s2e, out_mode=ops.OUT_UPDATE, dt_u=ops.F32,
+                   scale=sums, scale_stride=2, accum_sumsq=2, seed=_seed(opt, group, 0), **base)  # fmt: skip
+            launch(scale=sums, scale_stride=2, u_op=ops.UOP_SIGN_GRAFT if prog.after[1] else ops.UOP_SIGN, **second)
+        else:
+            launch(g=grads_v, u=scratch, s0=s0, s0e=s0e, s1=s1, s1e=s1e, s2=s2, s2e=s2e, out_mode=ops.OUT_UPDATE, dt_u=ops.F32,
+                   seed=_seed(opt, group, 0), **base)  # fmt: skip
+            dots = ops.dot(params_v + params_v + scratch, scratch + params_v + scratch).view(3, n).t().contiguous()
+            launch(gsq=dots, gsq_stride=3, g_clip_mode=ops.CLIP_ORTHO, g_clip_at=group["eps"], g_clip_numel=1.0, **second)
+        return True
     if prog.kind == "elementwise":
         if not caution:
             launch(p=params_v, pe=pe, g=grads_v, s0=s0, s0e=s0e, s1=s1, s1e=s1e, s2=s2, s2e=s2e, out_mode=ops.OUT_PARAM,
@@ -507,7 +617,8 @@ def _run(opt, prog, states, group, grads, params, on_gpu, check_only) -> bool:
         scratch = _scratch(prog, params_v)
         masked = torch.zeros(len(params_v), dtype=torch.int32, device=params[0].device)
         launch(g=grads_v, u=scratch, s0=s0, s0e=s0e, s1=s1, s1e=s1e, s2=s2, s2e=s2e, masked=masked, count_caution=1,
-               out_mode=ops.OUT_UPDATE, dt_u=ops.F32, seed=_seed(opt, group, 0), **base, **mars_kw, **peer_in)  # fmt: skip
+               out_mode=ops.OUT_UPDATE, dt_u=ops.F32, seed=_seed(opt, group, 0), **base, **mars_kw, **peer_in,
+               **({"p": params_v} if prog.pre_project else {}))  # fmt: skip
         ops.fused_chain(p=params_v, pe=pe, u=scratch, masked=masked, algo=ops.IDENTITY, u_is_input=1, caution_apply=1,
                         out_mode=ops.OUT_PARAM, dt_u=ops.F32, dt_p=base["dt_p"], dt_g=ops.NONE, dt_s=ops.NONE,
                         seed=_seed(opt, group, 1), **epilogue, **peer_out)  # fmt: skip

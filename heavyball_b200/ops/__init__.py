@@ -42,7 +42,9 @@ F32, BF16, F16, BF16E8, BF16E16, F16E8, F16E16, NONE = range(8)
 # algorithms (mirror of hb::Algo)
 IDENTITY, ADAM, LAPROP, ADOPT, ADEMAMIX, RMSPROP, UNSCALED_ADAM, EXP_AVG, NESTEROV_EMA, HEAVYBALL, NESTEROV_MOM, NADAM = range(12)
 OUT_PARAM, OUT_UPDATE, OUT_SCHEDULE_FREE = 0, 1, 2
-CLIP_NONE, CLIP_L2, CLIP_RMS = 0, 1, 2
+CLIP_NONE, CLIP_L2, CLIP_RMS, CLIP_ORTHO = 0, 1, 2, 3
+UOP_NONE, UOP_TRUST_REGION, UOP_SIGN_GRAFT, UOP_SIGN = 0, 1, 2, 3  # mirror of hb::UpdateOp
+POST_NONE, POST_MSAM, POST_DECAY_IN = 0, 1, 2  # mirror of hb::PostState
 MODE_GRAM, MODE_POLY, MODE_APPLY = 0, 1, 2
 
 CUDA_FLAGS = [

@@ -75,6 +75,8 @@ void fused_chain(const TList& p, const TList& pe, const TList& g, const TList& u
   if (n == 0) return;
   const at::Tensor& ref = !g.empty() ? *g[0] : (!u.empty() ? *u[0] : *p[0]);
   c10::cuda::CUDAGuard guard(ref.device());
+  const int scale_stride = cfg.contains("scale_stride") ? std::max(1, cfg["scale_stride"].cast<int>()) : 1;
+  const int gsq_stride = cfg.contains("gsq_stride") ? std::max(1, cfg["gsq_stride"].cast<int>()) : 1;
   {  // the kernel trusts the table: every buffer must be a contiguous CUDA tensor of the element count and storage
      // kind its slot is declared with, on the device of the launch
     // storage kinds as in common.cuh: 0 fp32, 1 bf16, 2 fp16, 3 bf16+8, 4 bf16+16, 5 fp16+8, 6 fp16+16, 7 none
@@ -101,12 +103,21 @@ void fused_chain(const TList& p, const TList& pe, const TList& g, const TList& u
     }
     for (const at::Tensor* aux : {scale.has_value() ? &*scale : nullptr, masked.has_value() ? &*masked : nullptr}) {
       if (aux == nullptr) continue;
-      TORCH_CHECK(aux->is_cuda() && aux->is_contiguous() && (size_t)aux->numel() >= n && aux->element_size() == 4,
-                  "fused_chain: per-tensor scalars need one 4-byte entry per tensor");
+      const size_t per = aux == (scale.has_value() ? &*scale : nullptr) ? (size_t)scale_stride : 1;
+      TORCH_CHECK(aux->is_cuda() && aux->is_contiguous() && (size_t)aux->numel() >= n * per && aux->element_size() == 4,
+                  "fused_chain: per-tensor scalars need ", per, " 4-byte entries per tensor");
     }
     if (gsq.has_value())
       TORCH_CHECK(gsq->is_cuda() && gsq->is_contiguous() && gsq->scalar_type() == at::kFloat &&
-                      (gsq->numel() == 1 || (size_t)gsq->numel() >= n), "fused_chain: gsq needs one fp32 entry, or one per tensor");
+                      (gsq->numel() == 1 || (size_t)gsq->numel() >= n * (size_t)gsq_stride),
+                  "fused_chain: gsq needs one fp32 entry, or gsq_stride per tensor");
+    const int clip_mode = cfg.contains("g_clip_mode") ? cfg["g_clip_mode"].cast<int>() : 0;
+    TORCH_CHECK(clip_mode != hb::kClipOrtho || (gsq.has_value() && gsq_stride == 3 && !p.empty()),
+                "fused_chain: the OrthoGrad projection needs the parameters and three dot products per tensor");
+    const int uop = cfg.contains("u_op") ? cfg["u_op"].cast<int>() : 0;
+    const int acc = cfg.contains("accum_sumsq") ? cfg["accum_sumsq"].cast<int>() : 0;
+    TORCH_CHECK((uop != hb::kUopSignGraft && acc != 2) || (scale.has_value() && scale_stride == 2),
+                "fused_chain: sign grafting keeps two sums per tensor in `scale`");
   }
   std::vector<hb::TensorMeta> metas(n);
   for (size_t i = 0; i < n; ++i) {
@@ -114,9 +125,9 @@ void fused_chain(const TList& p, const TList& pe, const TList& g, const TList& u
     m.p = ptr_or_null(p, i); m.pe = ptr_or_null(pe, i); m.g = ptr_or_null(g, i); m.u = ptr_or_null(u, i);
     m.s0 = ptr_or_null(s0, i); m.s0e = ptr_or_null(s0e, i); m.s1 = ptr_or_null(s1, i); m.s1e = ptr_or_null(s1e, i);
     m.s2 = ptr_or_null(s2, i); m.s2e = ptr_or_null(s2e, i); m.mars = ptr_or_null(mars, i); m.marse = ptr_or_null(marse, i);
-    m.scale = scale.has_value() ? scale->data_ptr<float>() + i : nullptr;
+    m.scale = scale.has_value() ? scale->data_ptr<float>() + (int64_t)i * scale_stride : nullptr;
     m.masked = masked.has_value() ? masked->data_ptr<int>() + i : nullptr;
-    m.gsq = gsq.has_value() ? gsq->data_ptr<float>() + (gsq->numel() == 1 ? 0 : (int64_t)i) : nullptr;
+    m.gsq = gsq.has_value() ? gsq->data_ptr<float>() + (gsq->numel() == 1 ? 0 : (int64_t)i * gsq_stride) : nullptr;
     const at::Tensor& any = !g.empty() && g[i].has_value() ? *g[i] : (!u.empty() && u[i].has_value() ? *u[i] : *p[i]);
     m.numel = any.numel();
     for (const TList* l : {&p, &pe, &g, &u, &s0, &s0e, &s1, &s1e, &s2, &s2e, &mars, &marse})
@@ -135,7 +146,10 @@ void fused_chain(const TList& p, const TList& pe, const TList& g, const TList& u
   P.dt_p = geti("dt_p"); P.dt_g = geti("dt_g"); P.dt_u = geti("dt_u"); P.dt_s = geti("dt_s");
   P.u_is_input = geti("u_is_input"); P.mars = geti("mars"); P.cautious_wd = geti("cautious_wd");
   P.caution_apply = geti("caution_apply"); P.use_tensor_scale = geti("use_tensor_scale");
-  P.accum_sumsq = geti("accum_sumsq"); P.u_op = geti("u_op");
+  P.accum_sumsq = geti("accum_sumsq"); P.u_op = geti("u_op"); P.post_state = geti("post_state");
+  TORCH_CHECK(P.post_state != hb::kPostMsam || (!s0.empty() && !s2.empty() && P.n_state == 3),
+              "fused_chain: Momentum-SAM keeps its momentum in s0 and the unperturbed weights in s2");
+  TORCH_CHECK(P.post_state != hb::kPostDecayIn || !p.empty(), "fused_chain: decay folded into the update reads the parameters");
   P.g_clip_mode = geti("g_clip_mode"); P.g_clip_at = getf("g_clip_at"); P.g_clip_numel = getf("g_clip_numel");
   P.lr = getf("lr"); P.wd = getf("wd"); P.eps = getf("eps");
   P.b1 = getf("b1"); P.b2 = getf("b2"); P.b3 = getf("b3"); P.alpha = getf("alpha"); P.mars_a = getf("mars_a");

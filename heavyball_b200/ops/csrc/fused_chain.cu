@@ -50,14 +50,24 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
     float n = (float)M.numel;
     cscale *= n / fmaxf(n - (float)(*M.masked), 1.0f);
   }
-  float gclip = 1.0f;
-  if (P.g_clip_mode != kClipNone && M.gsq != nullptr) {
+  float gclip = 1.0f, ortho_c = 0.f;
+  const bool ortho = P.g_clip_mode == kClipOrtho && M.gsq != nullptr;
+  if (ortho) {
+    const float px = M.gsq[0], pp = M.gsq[1], xx = M.gsq[2];
+    ortho_c = px / (pp + P.g_clip_at);
+    if (P.g_clip_numel != 0.f) {
+      const float proj_sq = fmaxf(xx - 2.f * ortho_c * px + ortho_c * ortho_c * pp, 0.f);
+      gclip = sqrtf(fmaxf(xx, 0.f)) / fmaxf(sqrtf(proj_sq), 1e-6f);
+    }
+  } else if (P.g_clip_mode != kClipNone && M.gsq != nullptr) {
     float sq = *M.gsq;
     if (P.g_clip_mode == kClipRms) sq /= (P.g_clip_numel > 0.f ? P.g_clip_numel : (float)M.numel);
     gclip = P.g_clip_at / fmaxf(sqrtf(sq), fmaxf(P.g_clip_at, 1e-8f));
   }
+  float ugraft = 1.0f;
+  if (P.u_op == kUopSignGraft && M.scale != nullptr) ugraft = sqrtf(fmaxf(M.scale[0], 0.f)) / fmaxf(sqrtf(M.scale[1]), 1e-6f);
   int masked_local = 0;
-  float sumsq_local = 0.f;
+  float sumsq_local = 0.f, nonzero_local = 0.f;
 
 #pragma unroll 2
   for (int it = 0; it < kChunk / (kThreads * 4); ++it) {
@@ -107,10 +117,17 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
         u.v[k] = fminf(fmaxf(y * 1.5f, -2.0f), 2.0f);
       }
     }
-    F4 p = P.out_mode == kOutParam ? load4(M.p, M.pe, P.dt_p, i, nv, vec_ok) : F4{};
+    if (P.u_is_input && (P.u_op == kUopSignGraft || P.u_op == kUopSign)) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) u.v[k] = u.v[k] > 0.f ? ugraft : (u.v[k] < 0.f ? -ugraft : 0.f);
+    }
+    F4 p = (P.out_mode == kOutParam || ortho || P.post_state == kPostDecayIn) ? load4(M.p, M.pe, P.dt_p, i, nv, vec_ok) : F4{};
     F4 out;
 
-    if (P.g_clip_mode != kClipNone && !P.u_is_input) {  // the clip acts on the update, caution still sees the raw gradient
+    if (ortho) {  // remove the component along the parameter (and keep the norm): caution still sees the raw gradient
+#pragma unroll
+      for (int k = 0; k < 4; ++k) u.v[k] = (u.v[k] - ortho_c * p.v[k]) * gclip;
+    } else if (P.g_clip_mode != kClipNone && !P.u_is_input) {  // the clip acts on the update, caution still sees the raw gradient
 #pragma unroll
       for (int k = 0; k < 4; ++k) u.v[k] *= gclip;
     }
@@ -188,6 +205,25 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
       out.v[k] = r;
     }
 
+    if (P.post_state == kPostMsam) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float m = lerp_to(s0.v[k], out.v[k], P.b3);
+        float d = P.wd;
+        if (P.cautious_wd && ((__float_as_uint(s2.v[k]) ^ __float_as_uint(m)) >> 31)) d = 0.f;
+        s0.v[k] = m;
+        s2.v[k] = s2.v[k] * (1.0f - d * P.lr) + m * -P.lr;
+        out.v[k] = m;
+      }
+    } else if (P.post_state == kPostDecayIn) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float d = P.wd;
+        if (P.cautious_wd && ((__float_as_uint(p.v[k]) ^ __float_as_uint(out.v[k])) >> 31)) d = 0.f;
+        out.v[k] += p.v[k] * d;
+      }
+    }
+
     // plain bf16 rounding consumes 16 random bits per element: the first two state tensors share one draw
     // (low / high halves); ECC residuals need 32 bits and keep a draw each
     const uint4 r0 = (P.n_state >= 1) ? draw(P.dt_s, rng, ctr, ctr_hi, (uint32_t)t, 0u) : make_uint4(0u, 0u, 0u, 0u);
@@ -229,7 +265,10 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
       if (P.accum_sumsq) {
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          if (k < nv) sumsq_local += out.v[k] * out.v[k];
+          if (k < nv) {
+            sumsq_local += out.v[k] * out.v[k];
+            nonzero_local += out.v[k] != 0.f ? 1.f : 0.f;
+          }
       }
       continue;
     }
@@ -262,6 +301,18 @@ __global__ void __launch_bounds__(kThreads, 4) fused_chain_kernel(const TensorMe
       float tot = 0.f;
       for (int w = 0; w < kThreads / 32; ++w) tot += warp_sq[w];
       atomicAdd(M.scale, tot);
+    }
+    if (P.accum_sumsq == 2) {  // block counts are exact integers (<= 8192); their sum stays exact up to 2^24 elements
+      __syncthreads();
+      float c = nonzero_local;
+      for (int o = 16; o > 0; o >>= 1) c += __shfl_down_sync(0xFFFFFFFFu, c, o);
+      if ((threadIdx.x & 31) == 0) warp_sq[threadIdx.x >> 5] = c;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float tot = 0.f;
+        for (int w = 0; w < kThreads / 32; ++w) tot += warp_sq[w];
+        atomicAdd(M.scale + 1, tot);
+      }
     }
   }
   if (kCountCaution) {

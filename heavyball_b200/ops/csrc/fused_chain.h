@@ -20,9 +20,11 @@ struct TensorMeta {
   void* s2e;
   void* mars;   // previous gradient for MARS
   void* marse;
-  float* scale; // optional per-tensor multiplier applied to the update
+  float* scale; // optional per-tensor multiplier applied to the update; accum_sumsq target ([sum u^2, count u != 0] for
+                // accum_sumsq == 2 and kUopSignGraft)
   int* masked;  // caution: number of masked elements (written by phase one, read by phase two)
-  const float* gsq;  // gradient clipping: sum of squares the clip factor is derived from (this tensor's, or the group's)
+  const float* gsq;  // gradient clipping: sum of squares the clip factor is derived from (this tensor's, or the group's);
+                     // kClipOrtho: this tensor's three dot products [p.x, p.p, x.x]
   int64_t numel;
   int32_t vec_ok;  // all buffers of this tensor are aligned for 4-wide access
   int32_t pad;
@@ -38,9 +40,20 @@ enum Algo : int {
 //   p <- lerp(p, z, b3) + u (lr (alpha (1 - b3)) - lr),  z <- z - lr u     (b3 = c_{k+1}, alpha = beta1)
 enum OutMode : int { kOutParam = 0, kOutUpdate = 1, kOutScheduleFree = 2 };
 // incoming-gradient clip: g <- g * clip_at / max(norm, clip_at, 1e-8), norm = sqrt(gsq) (kClipL2) or sqrt(gsq / n) (kClipRms)
-enum ClipMode : int { kClipNone = 0, kClipL2 = 1, kClipRms = 2 };
+// kClipOrtho (OrthoGrad): x <- a (x - c p) with c = p.x / (p.p + g_clip_at) and, when g_clip_numel != 0, a = |x| / |x - c p|
+// (the projected vector keeps the norm of the original; |x - c p|^2 = x.x - 2 c p.x + c^2 p.p), else a = 1.  It acts on
+// whatever the launch takes in: the gradient, or the update when u_is_input.
+enum ClipMode : int { kClipNone = 0, kClipL2 = 1, kClipRms = 2, kClipOrtho = 3 };
 // kUopTrustRegion: 0.9 tanh(x / 1.5) + 0.1 sign(x) log1p(|x| / 1.5), times 1.5, limited to +-2 (PSGD's default update clip)
-enum UpdateOp : int { kUopNone = 0, kUopTrustRegion = 1 };
+// kUopSignGraft: sign(x) * sqrt(sum x^2) / max(sqrt(count x != 0), 1e-6) with both sums in TensorMeta::scale (written by an
+// earlier launch with accum_sumsq == 2): the sign vector rescaled to the norm of x.  kUopSign: sign(x).
+enum UpdateOp : int { kUopNone = 0, kUopTrustRegion = 1, kUopSignGraft = 2, kUopSign = 3 };
+
+// What happens to the rule's output before anything is stored:
+//   kPostMsam (Momentum-SAM): m = s0 <- lerp(s0, out, 1 - b3);  z = s2 <- z (1 - d lr) - lr m;  out <- m
+//   kPostDecayIn:             out <- out + p d                  (weight decay folded into the update itself)
+// with d = wd, or 0 where cautious_wd is set and the signs of the decayed value and the update differ.
+enum PostState : int { kPostNone = 0, kPostMsam = 1, kPostDecayIn = 2 };
 
 struct ChainParams {
   int n_tensors;
@@ -53,7 +66,9 @@ struct ChainParams {
   int cautious_wd;
   int caution_apply; // phase two: rescale by numel / (numel - masked)
   int use_tensor_scale;
-  int accum_sumsq;   // kOutUpdate: add sum(update^2) of every tensor into its `scale` slot
+  int accum_sumsq;   // kOutUpdate: add sum(update^2) of every tensor into its `scale` slot; 2: also the number of non-zero
+                     // elements into the slot after it
+  int post_state;    // see PostState
   int u_op;          // transformation of an incoming update (u_is_input) before anything else: see UpdateOp
   int g_clip_mode;   // see ClipMode; needs TensorMeta::gsq
   float g_clip_at;

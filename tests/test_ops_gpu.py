@@ -60,6 +60,43 @@ FIRST_ORDER = [
 ]
 
 
+NORMED = [
+    (hb.SignLaProp, {"lr": 1e-2}),
+    (hb.SignLaProp, {"lr": 1e-2, "weight_decay": 0.1, "cautious_weight_decay": True}),
+    (hb.OrthoLaProp, {"lr": 1e-2}),
+    (hb.OrthoLaProp, {"lr": 1e-2, "caution": True, "weight_decay": 0.1}),
+    (hb.LaPropOrtho, {"lr": 1e-2, "weight_decay": 0.1}),
+    (hb.MSAMLaProp, {"lr": 1e-2}),
+    (hb.MSAMLaProp, {"lr": 1e-2, "weight_decay": 0.1, "cautious_weight_decay": True, "sam_step_size": 0.05}),
+    (hb.HyperBallAdamW, {"lr": 1e-2}),
+    (hb.HyperBallAdamW, {"lr": 1e-2, "weight_decay": 0.1}),
+]
+
+
+@pytest.mark.parametrize("cls,kw", NORMED, ids=lambda x: getattr(x, "__name__", str(x))[:40])
+def test_sign_and_orthograd_chains_are_lowered(cls, kw):
+    """Chains whose update depends on a per-tensor norm or projection: the sums come from the rule's own launch or from
+    one segmented reduction, the rescaling happens on load in the launch that writes the parameters."""
+    shapes = [(257,), (64, 33), (3, 5, 7), (8193,), (128, 256), (16,)]
+    ref, _ = _run(cls, kw, shapes, 6, lowered=False)
+    before = ops.launch_counter.count
+    got, opt = _run(cls, kw, shapes, 6, lowered=True)
+    prog = lowering._program(opt)
+    subs = [sub for _, sub in prog.routes] if prog.kind == "route" else [prog]
+    assert any(sub.pre_project or sub.after is not None for sub in subs)
+    assert ops.launch_counter.count - before <= 6 * 6  # the PyTorch definitions never touch the counter; a step is <= 6 launches
+    assert ops.launch_counter.count - before >= 5 * 2  # the first step creates state through the PyTorch definitions
+    for a, b in zip(ref, got):
+        torch.testing.assert_close(b.data, a.data, rtol=1e-4, atol=1e-5)
+
+
+def test_orthograd_with_a_scalar_parameter_takes_the_pytorch_definition():
+    ref, _ = _run(hb.OrthoLaProp, {"lr": 1e-2}, [(1,), (64, 33)], 4, lowered=False)
+    got, _ = _run(hb.OrthoLaProp, {"lr": 1e-2}, [(1,), (64, 33)], 4, lowered=True)
+    for a, b in zip(ref, got):
+        torch.testing.assert_close(b.data, a.data, rtol=1e-6, atol=1e-7)
+
+
 @pytest.mark.parametrize("cls,kw", FIRST_ORDER, ids=lambda x: getattr(x, "__name__", str(x))[:40])
 def test_fused_chain_matches_pytorch_fp32(cls, kw):
     ref, _ = _run(cls, kw, SHAPES, 6, lowered=False)

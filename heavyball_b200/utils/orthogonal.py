@@ -455,10 +455,35 @@ def _scion_matrix_direction(x: Tensor, conv: bool) -> Tensor:
     return flat.reshape_as(x) * scale
 
 
+def _scion_batched_matrices(update: List[Tensor], scale: float) -> List[Tensor]:
+    """Runs the spectral LMO of all 2-D tensors that the Newton-Schulz kernels accept, one batched iteration per shape,
+    and returns the tensors that are left for the per-tensor definitions."""
+    mode = _settings().zeroth_power_mode
+    if str(getattr(mode, "value", mode)) != "newtonschulz" or not update or not update[0].is_cuda:
+        return update
+    from .. import ops
+
+    if not ops.available():
+        return update
+    buckets, rest = {}, []
+    for t in update:
+        if (t.ndim == 2 and t.is_cuda and t.dtype in (torch.float32, torch.bfloat16) and t.is_contiguous()
+                and ops.ns_supported(t.shape[0], t.shape[1])):  # fmt: skip
+            buckets.setdefault((tuple(t.shape), t.dtype), []).append(t)
+        else:
+            rest.append(t)
+    for ((rows, cols), _), members in buckets.items():
+        out = ops.newton_schulz_batched(members, NS5_COEFFS, out_scale=math.sqrt(rows / max(cols, 1)) * scale)
+        for t, d in zip(members, out.unbind(0)):
+            copy_stochastic_(t, d)
+    return rest
+
+
 def scion_auto_lmo_(update: Union[List[Tensor], Tensor], scale):
     """Norm-constrained LMO chosen by rank: spectral (matrices), unfolded spectral (conv kernels),
     RMS (vectors, scalars)."""
     update = list_guard(update)
+    update = _scion_batched_matrices(update, float(scale))  # same-shape matrices in one batched iteration on sm_100a
     for t in update:
         t32 = promote(t)
         if t32.ndim in (3, 4):

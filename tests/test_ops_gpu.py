@@ -395,3 +395,27 @@ def test_orthograd_and_kron_balance_use_the_segmented_reductions():
     psgd.psgd_balance_Q(ref)
     for q, r in zip(qs, ref):
         assert torch.allclose(q.cpu(), r, atol=1e-6, rtol=1e-5)
+
+
+def test_scion_matrices_of_one_shape_share_a_batched_iteration():
+    """The spectral LMO of Scion: same-shape matrices go through one batched Newton-Schulz chain; the result is the
+    per-tensor one up to the rounding noise of the bf16 iteration."""
+    from heavyball_b200.utils import orthogonal
+
+    gen = torch.Generator(device=DEV).manual_seed(3)
+    mats = [torch.randn(192, 320, device=DEV, generator=gen) for _ in range(3)] + [torch.randn(64, 64, device=DEV, generator=gen)]
+    vec = torch.randn(300, device=DEV, generator=gen)
+    want = [orthogonal._scion_matrix_direction(m.clone(), False) * 0.5 for m in mats]
+    want_vec = orthogonal._scion_bias_rms_direction(vec.clone()) * 0.5
+    work = [m.clone() for m in mats] + [vec.clone()]
+    before = ops.launch_counter.count
+    orthogonal.scion_auto_lmo_(work, 0.5)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert ops.launch_counter.count > before
+    for got, ref in zip(work[:-1], want):
+        assert float((got - ref).norm() / ref.norm()) < 0.05
+        s = torch.linalg.svdvals(got.double())
+        unit = 0.5 * (got.shape[0] / got.shape[1]) ** 0.5  # five steps leave the smallest singular values of a square matrix short
+        assert float(s.max()) < 1.3 * unit and 0.7 * unit < float(s.median()) < 1.3 * unit
+    torch.testing.assert_close(work[-1], want_vec)

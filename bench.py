@@ -481,7 +481,11 @@ def run_config(args):
     step_ms = statistics.median(window_ms) / args.steps
 
     # ---- the two halves of a step, device-timed separately (same state, fresh gradients every iteration)
-    fb_ms, opt_ms = [], []
+    fb_ms, opt_ms, work_ms = [], [], []
+    peer_contexts = []
+    if ours and world > 1:
+        peer_contexts = list({id(c): c for c in [getattr(o, "_peer", None) for o in [opt, *getattr(opt, "optimizers", [])]]
+                              if c is not None}.values())  # fmt: skip
     e_a, e_b, e_c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
     for i in range(max(4, min(args.steps, 10))):
         torch.cuda.synchronize()
@@ -496,7 +500,12 @@ def run_config(args):
         opt.zero_grad(set_to_none=True)
         fb_ms.append(e_a.elapsed_time(e_b))
         opt_ms.append(e_b.elapsed_time(e_c))
+        for ctx in peer_contexts:  # time between the two step barriers: the optimizer's work without arrival skew
+            work = ctx.work_ms()
+            if work is not None:
+                work_ms.append(work)
     opt_step_ms = max_over_ranks(statistics.median(opt_ms))
+    opt_work_ms = max_over_ranks(statistics.median(work_ms)) if work_ms else None
     opt_step_max_ms = max_over_ranks(max(opt_ms))  # preconditioner-refresh steps show up here
     fwd_bwd_ms = max_over_ranks(statistics.median(fb_ms))
 
@@ -562,6 +571,9 @@ def run_config(args):
             "window_ms_per_step": [round(w / args.steps, 4) for w in window_ms],
             "ms_x_sm_mhz": (step_ms * sm) if sm else None,
             "optimizer_step_ms": opt_step_ms,
+            # peer data parallelism only: the part of the optimizer step between its two cross-rank barriers (the rest
+            # is waiting for the slowest rank's backward pass)
+            "optimizer_work_ms": opt_work_ms,
             "optimizer_step_max_ms": opt_step_max_ms,
             "fwd_bwd_ms": fwd_bwd_ms,
             "higher_is_better": True,
@@ -666,7 +678,7 @@ def run_child(cmd, timeout):
 def _brief(rec):
     """The fields of a child's line that the parent's line keeps."""
     keep = ("impl", "value", "unit", "n_gpus", "steps", "warmup", "windows", "ms_per_step", "optimizer_step_ms",
-            "optimizer_step_max_ms", "fwd_bwd_ms", "clocks", "e2e", "gpu_launches", "final_loss", "unavailable",
+            "optimizer_step_max_ms", "optimizer_work_ms", "fwd_bwd_ms", "clocks", "e2e", "gpu_launches", "final_loss", "unavailable",
             "seconds", "config", "implementation", "roofline", "note")  # fmt: skip
     return {k: rec[k] for k in keep if k in rec}
 

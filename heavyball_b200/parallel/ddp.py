@@ -256,12 +256,28 @@ class PeerContext:
         self._check_grads_in_slab()
         with _stage("peer.begin"):
             self._barrier(0)
+        self._mark(0)
         for dtype, off, n in self.fallback_ranges:
             dist.all_reduce(self.slabs[dtype]["G"][off : off + n], op=dist.ReduceOp.AVG, group=self.group)
+
+    def _mark(self, which: int):
+        """Two events per step bracket the work between the barriers (the time a rank spends waiting for the slowest
+        peer at the first barrier is arrival skew of the backward passes, not optimizer work)."""
+        events = self.__dict__.setdefault("_work_events", [torch.cuda.Event(enable_timing=True) for _ in range(2)])
+        events[which].record(torch.cuda.current_stream(self.device))
+
+    def work_ms(self) -> Optional[float]:
+        """Device time of the last step between its two barriers (synchronises); ``None`` before the first step."""
+        events = self.__dict__.get("_work_events")
+        if events is None:
+            return None
+        events[1].synchronize()
+        return events[0].elapsed_time(events[1])
 
     def end_step(self):
         """After the last optimizer kernel: wait until every peer has finished reading this rank's
         gradients and writing this rank's parameters, then clear the gradient slab."""
+        self._mark(1)
         with _stage("peer.end"):
             self._barrier(1)
         for slab in self.slabs.values():

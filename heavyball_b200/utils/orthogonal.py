@@ -271,7 +271,7 @@ def _cholesky_qr2(x: Tensor, shifted_rounds: int = 0):
     bad = torch.zeros(a.shape[0], dtype=torch.int32, device=a.device)
     eye = torch.eye(k, device=a.device, dtype=a.dtype)
     rounds = shifted_rounds + 2
-    info = torch.zeros_like(bad)  # failed leaves are not a verdict: what counts is the orthogonality reached at the end
+    info = torch.zeros_like(bad)  # failed leaves do not decide: what counts is the orthogonality reached at the end
     for rnd in range(rounds):
         gram = _mm(a, a, True, False)
         if rnd < shifted_rounds:

@@ -522,6 +522,7 @@ class FunctionTransform:
 
     def assign(self, start, retain):
         """Gives every unnumbered layer the next free index; returns the next free index."""
+        self.__dict__.pop("_mark_indices", None)  # derived from the layer indices by the kernel lowering
         seen_bucket = False
         for layer in self.layers:
             if not retain or layer.index is None:

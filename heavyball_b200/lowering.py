@@ -227,10 +227,23 @@ def describe(opt) -> str:
     return "not lowered" if prog is None else one(prog)
 
 
+_MARKED_LAYERS = (C.ZeroSlots, C.CopySlots, C.InitSlots, C.Tag, C.PerTensor, C.Warmup)
+
+
 def _mark_initialized(tr: C.FunctionTransform, st: dict):
-    for layer in tr.layers:
-        if isinstance(layer, (C.ZeroSlots, C.CopySlots, C.InitSlots, C.Tag, C.PerTensor, C.Warmup)):
-            C._mark(st, layer.index)
+    """Records in the view's state that the transform's layers have run (what the layers do themselves on the PyTorch
+    path).  Called for every state of every step, so the layer walk is done once per transform and a state that
+    already carries the marks costs one set comparison."""
+    indices = tr.__dict__.get("_mark_indices")
+    if indices is None:
+        indices = tr.__dict__["_mark_indices"] = frozenset(
+            layer.index for layer in tr.layers if isinstance(layer, _MARKED_LAYERS)
+        )
+    done = st.get("is_initialized")
+    if isinstance(done, set) and indices <= done:
+        return
+    for index in indices:
+        C._mark(st, index)
 
 
 def _state_ready(tr: C.FunctionTransform, states: List[dict], ecc: bool) -> bool:

@@ -418,11 +418,23 @@ class StatefulOptimizer(torch.optim.Optimizer):
         """Yields ``(parameter view, gradient view)`` pairs of a group.  ``raw`` yields whole parameters with their
         gradients untouched (no views, no promotion); otherwise a curvature step's stored gradient takes precedence
         over ``p.grad`` and its probe / product are re-attached to the views they belong to."""
+        plain = not raw and not group.get("merge_dims", False)
         for p in group["params"]:
             if raw:
                 grad = self._take_grad(p)
                 if grad is not None or not skip_none:
                     yield p, grad
+                continue
+            if plain and not group.get(Scratch.KEY):
+                # the common case, kept short because it runs for every parameter of every step: one view per
+                # parameter (the parameter itself) and nothing stored for the group by a curvature step
+                grad = self._take_grad(p)
+                if grad is None and skip_none:
+                    continue
+                self.views.register(p, (p,))
+                if grad is not None:
+                    grad = (promote(grad) if should_promote else grad).detach()
+                yield p, grad
                 continue
             stored = Scratch.take(group, p, "grad", "vector", "hessian_vector")
             live = self._take_grad(p)

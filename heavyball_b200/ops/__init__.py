@@ -250,22 +250,9 @@ def newton_schulz_batched(mats: Sequence[torch.Tensor], coeffs, out: Optional[to
         ext.ns_prepare(srcs, dtype_code(mats[0]), R, C, norms, eps, XT[0], ldxt, X[0], ldx, seed)
     status = _status(dev)
     launch_counter.count += 1 + 3 * len(coeffs)
-    cur = 0
-    for step, (a, b, c) in enumerate(coeffs):
-        last = step == len(coeffs) - 1
-        x, xt = X[cur], XT[cur]
-        ext.ns_gemm(x, ldx, m * ldx, x, ldx, m * ldx, m, m, n, B, MODE_GRAM, True, S, lds, m * lds, S, lds, m * lds,
-                    None, 0, 0, False, 1.0, None, 0, 0, 0.0, 0.0, 0.0, status)  # fmt: skip
-        ext.ns_gemm(S, lds, m * lds, S, lds, m * lds, m, m, m, B, MODE_POLY, True, Y, lds, m * lds, Y, lds, m * lds,
-                    None, 0, 0, False, 1.0, S, lds, m * lds, a, b, c, status)  # fmt: skip
-        if not last:
-            nx, nxt = X[1 - cur], XT[1 - cur]
-            ext.ns_gemm(Y, lds, m * lds, xt, ldxt, n * ldxt, m, n, m, B, MODE_APPLY, False, nx, ldx, m * ldx, nxt, ldxt,
-                        n * ldxt, None, 0, 0, False, 1.0, None, 0, 0, 0.0, 0.0, 0.0, status)  # fmt: skip
-            cur = 1 - cur
-        else:  # final product goes straight to fp32 in the caller's orientation
-            ext.ns_gemm(Y, lds, m * lds, xt, ldxt, n * ldxt, m, n, m, B, MODE_APPLY, False, None, 0, 0, None, 0, 0,
-                        out, C, R * C, R > C, out_scale, None, 0, 0, 0.0, 0.0, 0.0, status)  # fmt: skip
+    # one call issues the three launches of every step (Gram, polynomial, apply; the last apply writes `out`)
+    ext.ns_chain(X, XT, S, Y, out, m, n, ldx, ldxt, lds, R, C, [[float(v) for v in abc] for abc in coeffs], float(out_scale),
+                 status)  # fmt: skip
     return out
 
 

@@ -253,6 +253,34 @@ void ns_gemm(const at::Tensor& A, int64_t lda, int64_t strideA, const at::Tensor
         "ns_gemm launch");
 }
 
+// The whole Newton-Schulz iteration of one shape bucket in one call: per step Gram, polynomial and apply launches (the
+// last apply writes fp32 into `out`, in the caller's orientation).  x / xt: the two ping-pong pairs of the iterate
+// [batch, m, ldx] and its transpose [batch, n, ldxt] (bf16), pair 0 prepared by ns_prepare; s, y: [batch, m, lds] (bf16).
+void ns_chain(const std::vector<at::Tensor>& x, const std::vector<at::Tensor>& xt, const at::Tensor& s, const at::Tensor& y,
+              at::Tensor& out, int64_t m, int64_t n, int64_t ldx, int64_t ldxt, int64_t lds, int64_t R, int64_t C,
+              const std::vector<std::vector<double>>& coeffs, double out_scale, const at::Tensor& status) {
+  TORCH_CHECK(x.size() == 2 && xt.size() == 2, "ns_chain: two ping-pong buffers per orientation");
+  const int64_t batch = s.size(0);
+  int cur = 0;
+  const OptT none;
+  for (size_t step = 0; step < coeffs.size(); ++step) {
+    TORCH_CHECK(coeffs[step].size() == 3, "ns_chain: (a, b, c) per step");
+    const bool last = step + 1 == coeffs.size();
+    ns_gemm(x[cur], ldx, m * ldx, x[cur], ldx, m * ldx, m, m, n, batch, 0 /* gram */, true, s, lds, m * lds, s, lds, m * lds,
+            none, 0, 0, false, 1.0, none, 0, 0, 0.0, 0.0, 0.0, status);
+    ns_gemm(s, lds, m * lds, s, lds, m * lds, m, m, m, batch, 1 /* poly */, true, y, lds, m * lds, y, lds, m * lds, none, 0, 0,
+            false, 1.0, s, lds, m * lds, coeffs[step][0], coeffs[step][1], coeffs[step][2], status);
+    if (!last) {
+      ns_gemm(y, lds, m * lds, xt[cur], ldxt, n * ldxt, m, n, m, batch, 2 /* apply */, false, x[1 - cur], ldx, m * ldx,
+              xt[1 - cur], ldxt, n * ldxt, none, 0, 0, false, 1.0, none, 0, 0, 0.0, 0.0, 0.0, status);
+      cur = 1 - cur;
+    } else {
+      ns_gemm(y, lds, m * lds, xt[cur], ldxt, n * ldxt, m, n, m, batch, 2 /* apply */, false, none, 0, 0, none, 0, 0, out, C,
+              R * C, R > C, out_scale, none, 0, 0, 0.0, 0.0, 0.0, status);
+    }
+  }
+}
+
 // Store `epoch` into slot[rank] of every peer's flag array (after a system-scope fence).
 void peer_signal(const std::vector<int64_t>& flag_ptrs, int slot, int rank, int epoch) {
   hb::PeerPtrs ptrs{};
@@ -601,6 +629,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("segmented_reduce", &segmented_reduce);
   m.def("ns_prepare", &ns_prepare);
   m.def("ns_gemm", &ns_gemm);
+  m.def("ns_chain", &ns_chain);
   m.def("set_ns_gemm_tile", &hb::set_ns_gemm_tile_override);
   m.def("set_tf32_gemm_tile", &hb::set_tf32_gemm_tile_override);
   m.def("chol_inv_leaf", &chol_inv_leaf);

@@ -27,6 +27,9 @@
 
 #include "common.cuh"
 #include "ns_gemm.h"
+
+#include <mutex>
+#include <unordered_map>
 #include "tc_common.cuh"
 
 namespace hb {
@@ -552,7 +555,42 @@ __global__ void __launch_bounds__(256) ns_prepare_kernel(const void* const* __re
 
 // ------------------------------------------------------------------------------------------ host side
 // bf16 tensor [batch, rows, cols] with leading dimension `ld` elements; box = 64 cols x 128 rows.
+static bool encode_map(CUtensorMap* map, const void* base, int rows, int cols, int64_t ld, int64_t batch_stride, int batch);
+
+// A step launches the same ~60 products over the same workspace addresses (the caching allocator hands the buffers
+// back), and every launch needs up to four descriptors: they are kept by their defining values instead of being
+// encoded again (about 0.6 us each on the host, which is what limits a step once the matrices are split over ranks).
 static bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int64_t ld, int64_t batch_stride, int batch) {
+  struct Key {
+    const void* base; int64_t ld, stride; int rows, cols, batch;
+    bool operator==(const Key& o) const {
+      return base == o.base && ld == o.ld && stride == o.stride && rows == o.rows && cols == o.cols && batch == o.batch;
+    }
+  };
+  struct Hash {
+    size_t operator()(const Key& k) const {
+      size_t h = std::hash<const void*>()(k.base);
+      for (int64_t v : {k.ld, k.stride, (int64_t)k.rows, (int64_t)k.cols, (int64_t)k.batch})
+        h ^= std::hash<int64_t>()(v) + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+      return h;
+    }
+  };
+  static std::unordered_map<Key, CUtensorMap, Hash> cache;
+  static std::mutex guard;
+  const Key key{base, ld, batch_stride, rows, cols, batch};
+  std::lock_guard<std::mutex> lock(guard);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *map = it->second;
+    return true;
+  }
+  if (!encode_map(map, base, rows, cols, ld, batch_stride, batch)) return false;
+  if (cache.size() >= 4096) cache.clear();
+  cache.emplace(key, *map);
+  return true;
+}
+
+static bool encode_map(CUtensorMap* map, const void* base, int rows, int cols, int64_t ld, int64_t batch_stride, int batch) {
   EncodeTiledFn fn = tensor_map_encoder();
   if (fn == nullptr) return false;
   cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};

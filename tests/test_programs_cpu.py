@@ -94,3 +94,38 @@ def test_stage_ranges_are_opened_when_tracing_is_on():
     tracing.seen.clear()
     _run("SOAP", CASES[0][1], 3, lowered=True)
     assert not tracing.seen  # off again: nothing recorded, nothing pushed
+
+
+def test_which_program_runs_each_class():
+    """The chain matcher of the kernel lowering, class by class (no GPU needed to match)."""
+    import torch
+
+    import heavyball_b200 as hb
+    from heavyball_b200 import lowering
+
+    model = torch.nn.Linear(8, 8)
+    want = {
+        "AdamW": "elementwise(update_by_adam)",
+        "LaProp": "elementwise(update_by_laprop)",
+        "ADOPT": "elementwise(update_by_adopt)",
+        "NAdam": "elementwise(update_by_nadam)",
+        "SFAdamW": "elementwise(scale_by_exp_avg_sq) +schedule_free",
+        "Muon": "orthogonal(nesterov_ema)",
+        "MuonAdamW": "route[orthogonal(nesterov_ema) | elementwise(scale_by_adam)]",
+        "SOAP": "soap(adam)",
+        "SOLP": "soap(laprop)",
+        "SignLaProp": "elementwise(scale_by_laprop) +sign",
+        "OrthoLaProp": "elementwise(update_by_laprop) +orthograd",
+        "LaPropOrtho": "elementwise(scale_by_laprop) +project",
+        "MSAMLaProp": "elementwise(scale_by_exp_avg_sq) +msam",
+        "HyperBallAdamW": "route[elementwise(scale_by_exp_avg_sq) +hyperball | elementwise(scale_by_exp_avg_sq)]",
+        "SUDSAdamW": "not lowered",
+        "Scion": "not lowered",
+    }
+    for name, text in want.items():
+        opt = getattr(hb, name)(model.parameters(), lr=1e-3)
+        assert lowering.describe(opt) == text, name
+    assert lowering.describe(hb.PSGDKron(model.parameters(), lr=1e-3)).startswith("psgd(")
+    clipped = hb.AdamW(model.parameters(), lr=1e-3, gradient_clipping="l2_clip_")
+    assert lowering.describe(clipped) == "elementwise(update_by_adam) +grad_clip"
+    assert lowering.describe(hb.SignLaProp(model.parameters(), lr=1e-3, gradient_clipping="l2_clip_")) == "not lowered"

@@ -568,11 +568,11 @@ def psgd_pro_update_precond(G, precond_lr, Q, running_lower_bound, lower_bount_b
             continue
         target = total / (q.shape[0] * q.shape[-1])
         ell = _update_lb(max_eigenvalue_spd(cov, power_iter=power_iter) + target, lb, lower_bount_beta)
-        q32 = q32 - (cov @ q32 - target * q32) / ell[..., None, None] * precond_lr
+        q32 = q32 - (_mm(cov, q32) - target * q32) / ell[..., None, None] * precond_lr
         R = (q32.mT - q32).contiguous()
         R = R / (max_singular_value(R, power_iter=power_iter)[..., None, None] + torch.finfo(R.dtype).smallest_normal)
-        RQ = R @ q32
-        RRQ = R @ RQ
+        RQ = _mm(R, q32)
+        RRQ = _mm(R, RQ)
         c1 = RQ.diagonal(dim1=-2, dim2=-1).sum(dim=-1)
         c2 = RRQ.diagonal(dim1=-2, dim2=-1).sum(dim=-1)
         a = torch.where(c2 < 0, (-c1 / c2).clamp(min=0, max=0.5), 0.5)[..., None, None]

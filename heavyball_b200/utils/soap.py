@@ -353,7 +353,7 @@ def get_orthogonal_matrix_QR(GG, Q, *exp_avg, exp_avg_sq=None, heavy: bool = Fal
         m = promote(m.data)
         if heavy:
             basis = inplace_orthogonal_(_mm(m, promote(q.data)), precise)
-            ray = compiled_einsum("...ij,...ij->...j", basis, m @ basis)
+            ray = compiled_einsum("...ij,...ij->...j", basis, _mm(m, basis))
             order = torch.argsort(ray, descending=True).unsqueeze(-2).expand_as(basis)
             new_qs.append(basis.gather(-1, order))
             continue
@@ -400,7 +400,7 @@ def init_psgd_eigenbasis(Q: List[Tensor]):
         if q.ndim < 3:
             return None
         wide = promote(q)
-        return _stable_symmetric_basis(wide.mT @ wide, out_device=q.device, out_dtype=q.dtype)
+        return _stable_symmetric_basis(_mm(wide, wide, True, False), out_device=q.device, out_dtype=q.dtype)
 
     return [basis(q) for q in Q]
 
@@ -416,8 +416,8 @@ def get_psgd_eigenbasis(Q: List[Tensor], prev: List[Optional[Tensor]]):
         if old is None:
             raise ValueError("get_psgd_eigenbasis requires a previous basis for matrix blocks; use init_psgd_eigenbasis")
         q32, old32 = promote(q), promote(old)
-        raw = _qr_basis(q32.mT @ (q32 @ old32)).to(dtype=q.dtype)
-        proj = q32 @ promote(raw)
+        raw = _qr_basis(_mm(q32, _mm(q32, old32), True, False)).to(dtype=q.dtype)
+        proj = _mm(q32, promote(raw))
         order = torch.argsort(compiled_einsum("...ij,...ij->...j", proj, proj), descending=True)
         raw = raw.gather(-1, order.unsqueeze(-2).expand_as(raw))
         align = compiled_einsum("...ij,...ij->...j", old32, promote(raw))

@@ -263,12 +263,12 @@ class PeerContext:
     def _mark(self, which: int):
         """Two events per step bracket the work between the barriers (the time a rank spends waiting for the slowest
         peer at the first barrier is arrival skew of the backward passes, not optimizer work)."""
-        events = self.__dict__.setdefault("_work_events", [torch.cuda.Event(enable_timing=True) for _ in range(2)])
+        events = self.__dict__.setdefault("_step_events", [torch.cuda.Event(enable_timing=True) for _ in range(2)])
         events[which].record(torch.cuda.current_stream(self.device))
 
     def work_ms(self) -> Optional[float]:
         """Device time of the last step between its two barriers (synchronises); ``None`` before the first step."""
-        events = self.__dict__.get("_work_events")
+        events = self.__dict__.get("_step_events")
         if events is None:
             return None
         events[1].synchronize()

@@ -119,9 +119,11 @@ __global__ void __launch_bounds__(128) tall_t_mul_kernel(const float* __restrict
 
 }  // namespace
 
-int tall_splits(int n) {  // two staged tiles of rows per CTA, up to 16 splits
+int tall_splits(int n) {  // two staged tiles of rows per CTA, up to 16 splits; very long inputs (the flattened parameter
+                          // vector of a low-rank preconditioner: millions of rows) are cut so that every SM gets several CTAs
   const int s = (n + 2 * kTileR - 1) / (2 * kTileR);
-  return s < 1 ? 1 : (s > kMaxSplits ? kMaxSplits : s);
+  const int cap = n > 65536 ? 2048 : kMaxSplits;
+  return s < 1 ? 1 : (s > cap ? cap : s);
 }
 
 cudaError_t launch_tall_t_mul(const float* X, long long ldx, long long strideX, const float* W, long long ldw,

@@ -653,6 +653,20 @@ def _d_step(d, d_orig, invQtv, vector, inv_precond_vector, hessian_vector, preco
         copy_stochastic_(d, d32 - nabla * scale)
 
 
+def _skinny_gram(A: Tensor, B: Tensor) -> Tensor:
+    """``A^T B`` for tall matrices ``[n, r]`` with a small ``r``: on sm_100a one pass of the long-dimension product
+    kernel (partial sums per slice of rows, added up afterwards); the library runs this shape as a SIMT GEMM with the
+    whole reduction inside one tile."""
+    if (A.is_cuda and A.dtype == torch.float32 and B.dtype == torch.float32 and A.ndim == 2 and A.shape == B.shape
+            and A.shape[1] <= 32 and A.is_contiguous() and B.is_contiguous()):  # fmt: skip
+        from .. import ops
+
+        if ops.available():
+            ops.launch_counter.count += 1
+            return ops.load().tall_t_mul(A.unsqueeze(0), A.shape[1], B.unsqueeze(0)).sum(0)[0]
+    return compiled_einsum("br,bn->rn", A, B)
+
+
 def update_lra_precond_(U, V, d, vector, hessian_vector, eps, step, delayed, precond_u):
     """One fitting step of the low-rank preconditioner (alternating between ``U`` and ``V``)."""
     U_orig, V_orig, d_orig = U, V, d
@@ -663,7 +677,7 @@ def update_lra_precond_(U, V, d, vector, hessian_vector, eps, step, delayed, pre
     Qh = low_rank_mm(U, V, d * hessian_vector)
     Ph = low_rank_mm(V, U, Qh)
     rank = U.size(1)
-    VtU = compiled_einsum("br,bn->rn", V, U)
+    VtU = _skinny_gram(V, U)
     IpVtU = torch.eye(rank, dtype=VtU.dtype, device=VtU.device) + VtU
     invQtv = vector / d
 

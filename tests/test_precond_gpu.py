@@ -181,3 +181,18 @@ def test_blocked_cholesky_with_the_leaf_kernel(n):
             want = torch.linalg.inv(r[b, lo:hi, lo:hi].double())
             got = inv[b, blk, : hi - lo, : hi - lo].double()
             assert float((got - want).abs().max()) < 1e-3 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("n,r", [(5000, 7), (300_000, 23), (1_000_003, 32)])
+def test_skinny_gram_of_very_tall_matrices(n, r):
+    """``A^T B`` over millions of rows (the low-rank preconditioner's flattened parameter vector) on the long-dimension
+    product kernel, cut into enough slices to fill the machine."""
+    from heavyball_b200.utils.psgd import _skinny_gram
+
+    g = torch.Generator(device="cuda").manual_seed(n)
+    a = torch.randn(n, r, device="cuda", generator=g)
+    b = torch.randn(n, r, device="cuda", generator=g)
+    got = _skinny_gram(a, b)
+    want = a.double().T @ b.double()
+    assert got.shape == (r, r)
+    assert float((got.double() - want).abs().max()) < 1e-5 * float((a.double().abs().T @ b.double().abs()).max())

@@ -456,7 +456,11 @@ def run_config(args):
     sampler.begin()
     if args.cuda_profiler:
         torch.cuda.profiler.start()
-    window_ms, last = [], None
+    peer_contexts = []
+    if ours and world > 1:
+        peer_contexts = list({id(c): c for c in [getattr(o, "_peer", None) for o in [opt, *getattr(opt, "optimizers", [])]]
+                              if c is not None}.values())  # fmt: skip
+    window_ms, last, work_ms = [], None, []
     for w in range(max(1, args.windows)):
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         marks = []
@@ -470,6 +474,9 @@ def run_config(args):
         stop.record()
         barrier()
         window_ms.append(max_over_ranks(start.elapsed_time(stop)))
+        # the last step of the window, as it ran in the pipelined loop (launches queued while the GPU was still in the
+        # backward pass): device time between the optimizer's two cross-rank barriers
+        work_ms += [t for t in (ctx.work_ms() for ctx in peer_contexts) if t is not None]
         if marks:
             per_step = [a.elapsed_time(b) for a, b in zip([start] + marks[:-1], marks)]
             print(f"rank {rank} window {w} step ms: " + " ".join(f"{t:.1f}" for t in per_step), file=sys.stderr)
@@ -481,11 +488,7 @@ def run_config(args):
     step_ms = statistics.median(window_ms) / args.steps
 
     # ---- the two halves of a step, device-timed separately (same state, fresh gradients every iteration)
-    fb_ms, opt_ms, work_ms = [], [], []
-    peer_contexts = []
-    if ours and world > 1:
-        peer_contexts = list({id(c): c for c in [getattr(o, "_peer", None) for o in [opt, *getattr(opt, "optimizers", [])]]
-                              if c is not None}.values())  # fmt: skip
+    fb_ms, opt_ms, isolated_work_ms = [], [], []
     e_a, e_b, e_c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
     for i in range(max(4, min(args.steps, 10))):
         torch.cuda.synchronize()
@@ -500,12 +503,10 @@ def run_config(args):
         opt.zero_grad(set_to_none=True)
         fb_ms.append(e_a.elapsed_time(e_b))
         opt_ms.append(e_b.elapsed_time(e_c))
-        for ctx in peer_contexts:  # time between the two step barriers: the optimizer's work without arrival skew
-            work = ctx.work_ms()
-            if work is not None:
-                work_ms.append(work)
+        isolated_work_ms += [t for t in (ctx.work_ms() for ctx in peer_contexts) if t is not None]
     opt_step_ms = max_over_ranks(statistics.median(opt_ms))
     opt_work_ms = max_over_ranks(statistics.median(work_ms)) if work_ms else None
+    opt_work_isolated_ms = max_over_ranks(statistics.median(isolated_work_ms)) if isolated_work_ms else None
     opt_step_max_ms = max_over_ranks(max(opt_ms))  # preconditioner-refresh steps show up here
     fwd_bwd_ms = max_over_ranks(statistics.median(fb_ms))
 
@@ -572,8 +573,10 @@ def run_config(args):
             "ms_x_sm_mhz": (step_ms * sm) if sm else None,
             "optimizer_step_ms": opt_step_ms,
             # peer data parallelism only: the part of the optimizer step between its two cross-rank barriers (the rest
-            # is waiting for the slowest rank's backward pass)
+            # is waiting for the slowest rank's backward pass), sampled in the pipelined loop of phase 1, and the same
+            # when the host starts issuing the step only after the GPU has drained (as in the optimizer_step_ms loop)
             "optimizer_work_ms": opt_work_ms,
+            "optimizer_work_isolated_ms": opt_work_isolated_ms,
             "optimizer_step_max_ms": opt_step_max_ms,
             "fwd_bwd_ms": fwd_bwd_ms,
             "higher_is_better": True,
@@ -678,7 +681,7 @@ def run_child(cmd, timeout):
 def _brief(rec):
     """The fields of a child's line that the parent's line keeps."""
     keep = ("impl", "value", "unit", "n_gpus", "steps", "warmup", "windows", "ms_per_step", "optimizer_step_ms",
-            "optimizer_step_max_ms", "optimizer_work_ms", "fwd_bwd_ms", "clocks", "e2e", "gpu_launches", "final_loss", "unavailable",
+            "optimizer_step_max_ms", "optimizer_work_ms", "optimizer_work_isolated_ms", "fwd_bwd_ms", "clocks", "e2e", "gpu_launches", "final_loss", "unavailable",
             "seconds", "config", "implementation", "roofline", "note")  # fmt: skip
     return {k: rec[k] for k in keep if k in rec}
 

@@ -117,11 +117,27 @@ class ViewIndex:
     def __init__(self):
         self.forward: Dict[Tensor, List[Tensor]] = {}
         self.backward: Dict[tuple, Tuple[Tensor, int]] = {}
+        self._plain: Dict[int, int] = {}  # id(param) -> storage address it was registered with as its own only view
 
     def register(self, param: Tensor, views) -> None:
+        self._plain.pop(id(param), None)
         self.forward[param] = views
         for index, view in enumerate(views):
             self.backward[_tensor_key(view)] = (param, index)
+
+    def register_plain(self, param: Tensor) -> None:
+        """``register(param, (param,))`` for the per-step path of unmerged groups: nothing to do while the parameter
+        still lives at the address it was registered with (``forward`` keeps the parameter alive, so its ``id`` cannot
+        have been handed to another tensor)."""
+        address = param.data_ptr()
+        if self._plain.get(id(param)) == address:
+            return
+        self.register(param, (param,))
+        self._plain[id(param)] = address
+
+    def is_plain(self, tensor: Tensor) -> bool:
+        views = self.forward.get(tensor)
+        return views is not None and len(views) == 1 and views[0] is tensor
 
     def ensure(self, groups) -> None:
         for group in groups:
@@ -368,6 +384,8 @@ class StatefulOptimizer(torch.optim.Optimizer):
 
     def state_(self, arg: Tensor, fail: bool = True):
         """State dictionary of a view (found by its storage address)."""
+        if self.views.is_plain(arg):  # a parameter that is its own only view: no address arithmetic needed
+            return self.state.setdefault(arg, {}).setdefault(0, {})
         where = self.views.locate(arg)
         if where is None:
             self.views.ensure(self.param_groups)
@@ -431,7 +449,7 @@ class StatefulOptimizer(torch.optim.Optimizer):
                 grad = self._take_grad(p)
                 if grad is None and skip_none:
                     continue
-                self.views.register(p, (p,))
+                self.views.register_plain(p)
                 if grad is not None:
                     grad = (promote(grad) if should_promote else grad).detach()
                 yield p, grad

@@ -170,3 +170,35 @@ def test_segmented_reduction_call_sites_fall_back_on_cpu():
     psgd.psgd_balance_Q(q)
     assert torch.allclose(q[0].abs().amax((1, 2)), q[1].abs().amax(1), rtol=1e-5)  # common max-abs per slot
     assert torch.allclose(torch.einsum("bij,bk->bijk", q[0], q[1]), before[0], rtol=1e-4, atol=1e-6)  # product unchanged
+
+
+@pytest.mark.parametrize("name", ["AdamW", "LaProp", "Muon", "SOAP", "PSGDKron", "SFAdamW"])
+def test_stepping_from_backward_hooks_follows_the_explicit_loop(name):
+    """``hook_optimizer_into_model`` steps every parameter as soon as its gradient is complete; the loss curve is the
+    one of an explicit ``step()`` / ``zero_grad()`` loop (per-parameter optimizers see the same gradients)."""
+    import heavyball_b200 as hb
+    from heavyball_b200 import utils
+
+    cls = getattr(hb, name)
+    curves = []
+    for hooked in (False, True):
+        torch.manual_seed(0x2131290)
+        model = torch.nn.Sequential(torch.nn.Linear(16, 16), torch.nn.Tanh(), torch.nn.Linear(16, 16))
+        kwargs = dict(lr=1e-3, weight_decay=1e-4, warmup_steps=4)
+        if hooked:
+            utils.hook_optimizer_into_model(model, cls, **kwargs)
+        else:
+            opt = cls(model.parameters(), **kwargs)
+        data = torch.Generator().manual_seed(7)
+        losses = []
+        for _ in range(12):
+            loss = model(torch.randn(64, 16, generator=data)).square().mean()
+            loss.backward()
+            if not hooked:
+                opt.step()
+                opt.zero_grad()
+            losses.append(float(loss.detach()))
+        curves.append(losses)
+    for a, b in zip(*curves):
+        assert abs(a - b) <= 0.05 * abs(a) + 1e-6
+    assert curves[1][-1] < curves[1][0]

@@ -239,3 +239,41 @@ def test_panel_cholesky_qr_matches_householder_up_to_column_signs():
             ref = torch.linalg.qr(power.double()).Q
             assert ((q.double() * ref).sum(-2).abs() - 1).abs().max() < 1e-4
     assert _panel_cholesky_qr(torch.zeros(2, 64, 64)) is None
+
+
+# ---------------------------------------------------------------------------------------- overflow-safe roots (PSGD initial scale)
+
+
+def _log_mean_pow(x64, power):
+    """log(mean(|x|^power)) in fp64 through the log-sum-exp form (the direct power overflows for the cases below)."""
+    logs = x64.abs().clamp(min=1e-300).log() * power
+    return torch.logsumexp(logs, 0) - math.log(x64.numel())
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float16, 2e-2), (torch.float32, 1e-5), (torch.float64, 1e-10)])
+def test_stable_exp_matches_exp_on_both_sides_of_zero(dtype, tol):
+    x = torch.linspace(-10, 10, 41, dtype=torch.float64)
+    got = utils.stable_exp(x.to(dtype)).double()
+    want = x.to(dtype).double().exp()
+    assert torch.allclose(got, want, rtol=tol, atol=0)
+
+
+@pytest.mark.parametrize("scale", [1e-3, 1.0, 1e3])
+@pytest.mark.parametrize("power", [1, 3, 7, 15])
+@pytest.mark.parametrize("numel", [1, 4, 512])
+def test_roots_of_power_means_do_not_overflow(numel, power, scale):
+    """``mean_root`` = mean(|x|^p)^(-1/2p), ``divided_root`` = the ratio of two such roots (inverted): evaluated through
+    logarithms, so 1e3^15 (far beyond fp32) is no problem."""
+    gen = torch.Generator().manual_seed(numel * 31 + power)
+    x = (torch.rand(numel, generator=gen) + 0.1) * scale
+    y = (torch.rand(numel, generator=gen) + 0.1) * scale * 3
+    x64, y64 = x.double(), y.double()
+    lse = utils._lse_mean(x, power, 1e-30)
+    assert torch.isfinite(lse).all()
+    assert abs(float(lse) - float(_log_mean_pow(x64, power)) / power / 2) < 1e-4 * max(1.0, abs(float(lse)))
+    root = utils.mean_root(x, power)
+    want_root = math.exp(-float(_log_mean_pow(x64, power)) / power / 2)
+    assert math.isfinite(float(root)) and abs(float(root) - want_root) < 1e-4 * want_root
+    ratio = utils.divided_root(x, y, power, power)
+    want_ratio = math.exp(float(_log_mean_pow(x64, power)) / power / 2 - float(_log_mean_pow(y64, power)) / power / 2)
+    assert math.isfinite(float(ratio)) and abs(float(ratio) - want_ratio) < 1e-4 * want_ratio

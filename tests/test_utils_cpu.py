@@ -277,3 +277,58 @@ def test_roots_of_power_means_do_not_overflow(numel, power, scale):
     ratio = utils.divided_root(x, y, power, power)
     want_ratio = math.exp(float(_log_mean_pow(x64, power)) / power / 2 - float(_log_mean_pow(y64, power)) / power / 2)
     assert math.isfinite(float(ratio)) and abs(float(ratio) - want_ratio) < 1e-4 * want_ratio
+
+
+# ---------------------------------------------------------------------------------------- spectral estimators
+
+
+def _with_spectrum(rows, cols, decades, dtype=torch.float32, seed=0, rank=None):
+    """``U diag(s) V^T`` with singular values spread log-uniformly over ``decades`` decades below 1 (``rank``: only that
+    many are non-zero)."""
+    gen = torch.Generator().manual_seed(seed)
+    r = min(rows, cols)
+    u = torch.linalg.qr(torch.randn(rows, r, generator=gen, dtype=torch.float64)).Q
+    v = torch.linalg.qr(torch.randn(cols, r, generator=gen, dtype=torch.float64)).Q
+    s = torch.logspace(0, -decades, r, dtype=torch.float64)
+    if rank is not None:
+        s[rank:] = 0
+    return ((u * s) @ v.T).to(dtype)
+
+
+@pytest.mark.parametrize("shape,decades,dtype,iters,rtol", [
+    ((128, 128), 10, torch.float64, 20, 0.01),
+    ((32, 32), 4, torch.float64, 8, 0.03),
+    ((128, 96), 1, torch.float32, 20, 0.03),
+    ((32, 48), 4, torch.float32, 8, 0.03),
+    ((4, 4), 8, torch.float32, 8, 0.03),
+    ((32, 32), 1, torch.bfloat16, 8, 0.1),
+])  # fmt: skip
+def test_largest_singular_value_by_power_iteration(shape, decades, dtype, iters, rtol):
+    a = _with_spectrum(*shape, decades, dtype)
+    want = float(torch.linalg.svdvals(a.double()).max())
+    got = float(utils.max_singular_value(a, power_iter=iters))
+    assert abs(got - want) <= rtol * want + 1e-6
+
+
+@pytest.mark.parametrize("n", [32, 128, 512])
+def test_largest_singular_value_of_rank_deficient_and_ill_conditioned_matrices(n):
+    low_rank = _with_spectrum(n, n, 1, rank=max(1, n // 8))
+    want = float(torch.linalg.svdvals(low_rank.double()).max())
+    got = float(utils.max_singular_value(low_rank, power_iter=16))
+    assert 0.92 * want <= got <= 1.01 * want  # a lower bound that closes slowly when the leading values are clustered
+    idx = torch.arange(1, n + 1, dtype=torch.float64)
+    hilbert = (1.0 / (idx[:, None] + idx[None, :] - 1)).float()  # condition number beyond any float format
+    want = float(torch.linalg.svdvals(hilbert.double()).max())
+    assert abs(float(utils.max_singular_value(hilbert, power_iter=16)) - want) <= 0.03 * want
+    assert float(utils.max_singular_value(torch.zeros(n, n))) == 0.0
+
+
+@pytest.mark.parametrize("n,decades,dtype,rtol", [(32, 0, torch.float64, 0.01), (32, 1, torch.float64, 0.1), (4, 4, torch.float64, 0.1),
+                                                  (32, 0, torch.float32, 0.01), (64, 1, torch.float32, 0.5)])  # fmt: skip
+def test_smallest_eigenvalue_of_a_symmetric_psd_matrix(n, decades, dtype, rtol):
+    gen = torch.Generator().manual_seed(n)
+    u = torch.linalg.qr(torch.randn(n, n, generator=gen, dtype=torch.float64)).Q
+    a = ((u * torch.logspace(0, -decades, n, dtype=torch.float64)) @ u.T).to(dtype)
+    want = float(torch.linalg.eigvalsh(a.double()).min())
+    got = float(utils.min_singular_value(a, power_iter=20))
+    assert abs(got - want) <= rtol * want + 1e-5

@@ -419,3 +419,64 @@ def test_scion_matrices_of_one_shape_share_a_batched_iteration():
         unit = 0.5 * (got.shape[0] / got.shape[1]) ** 0.5  # five steps leave the smallest singular values of a square matrix short
         assert float(s.max()) < 1.3 * unit and 0.7 * unit < float(s.median()) < 1.3 * unit
     torch.testing.assert_close(work[-1], want_vec)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shift", [0, 1])
+def test_canary_words_around_every_buffer_survive_the_fused_chain(dtype, shift):
+    """Every tensor of a launch is carved out of one arena with sentinel words before and after it (sizes 1 .. 8193,
+    16-byte aligned and - with ``shift`` - deliberately misaligned starts, which take the scalar path): after Adam
+    steps with caution (two launches, scratch and mask counters included) no sentinel has changed and the parameters
+    match the PyTorch arithmetic."""
+    sizes = [1, 7, 63, 64, 65, 4099, 8191, 8192, 8193]
+    gap, sentinel = 32, -12288.0  # exactly representable in bf16
+    gen = torch.Generator(device=DEV).manual_seed(11 + shift)
+
+    def arena(fill):
+        total = sum(n + gap for n in sizes) + gap + 8
+        buf = torch.full((total,), sentinel, device=DEV, dtype=torch.float32 if fill == "f32" else dtype)
+        views, mask, off = [], torch.ones(total, dtype=torch.bool, device=DEV), gap + shift
+        for n in sizes:
+            off = (off + 3) // 4 * 4 + shift
+            views.append(buf[off : off + n])
+            mask[off : off + n] = False
+            off += n + gap
+        return buf, views, mask
+
+    bufs = {name: arena("f32" if name in ("u",) else "x") for name in ("p", "g", "m", "v", "u")}
+    p, g, m, v, u = (bufs[k][1] for k in ("p", "g", "m", "v", "u"))
+    for t in p:
+        t.copy_(torch.randn(t.shape, device=DEV, generator=gen))
+    for t in m + v + u:
+        t.zero_()
+    ref_p = [t.float().clone() for t in p]
+    ref_m, ref_v = [torch.zeros_like(t) for t in ref_p], [torch.zeros_like(t) for t in ref_p]
+    lr, b1, b2, eps = 1e-2, 0.9, 0.99, 1e-8
+    for step in range(1, 4):
+        for t in g:
+            t.copy_(torch.randn(t.shape, device=DEV, generator=gen) * 0.1)
+        d1, d2 = 1 - (1 - b1) / (1 - b1**step), 1 - (1 - b2) / (1 - b2**step)
+        masked = torch.zeros(len(sizes), dtype=torch.int32, device=DEV)
+        common = dict(algo=ops.ADAM, n_state=2, b1=d1, b2=d2, eps=eps, dt_g=ops.dtype_code(g[0]), dt_s=ops.dtype_code(m[0]),
+                      dt_p=ops.dtype_code(p[0]))  # fmt: skip
+        ops.fused_chain(g=g, u=u, s0=m, s1=v, masked=masked, count_caution=1, out_mode=ops.OUT_UPDATE, dt_u=ops.F32, seed=step,
+                        **common)  # fmt: skip
+        ops.fused_chain(p=p, u=u, masked=masked, algo=ops.IDENTITY, u_is_input=1, caution_apply=1, out_mode=ops.OUT_PARAM,
+                        dt_u=ops.F32, dt_p=common["dt_p"], dt_g=ops.NONE, dt_s=ops.NONE, lr=lr, wd=0.0, seed=step + 100)  # fmt: skip
+        if dtype == torch.float32:
+            for i in range(len(sizes)):
+                g32 = g[i].float()
+                ref_m[i] = ref_m[i] * (1 - (1 - d1)) + g32 * (1 - d1)
+                ref_v[i] = ref_v[i] * (1 - (1 - d2)) + g32 * g32 * (1 - d2)
+                upd = ref_m[i] / ref_v[i].sqrt().clamp(min=eps)
+                keep = ~(g32.signbit() ^ upd.signbit())
+                upd = upd * keep * (upd.numel() / max(1, int(keep.sum())))
+                ref_p[i] = ref_p[i] - lr * upd
+    torch.cuda.synchronize()
+    for name, (buf, _, mask) in bufs.items():
+        assert bool((buf[mask].float() == sentinel).all()), name
+    if dtype == torch.float32:
+        for got, want in zip(p, ref_p):
+            torch.testing.assert_close(got, want, rtol=2e-5, atol=2e-6)
+    else:
+        assert all(torch.isfinite(t.float()).all() for t in p)

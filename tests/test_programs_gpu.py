@@ -277,3 +277,49 @@ def test_captured_fit_matches_eager():
         for w, g in zip(want, got):  # the fit's random probe comes from the generator in both modes: same trajectory
             assert torch.isfinite(g).all()
             assert float((g - w).abs().max()) <= 0.05 * float(w.abs().max())
+
+
+@pytest.mark.parametrize("B,M,N,K", [(2, 200, 136, 160), (1, 264, 264, 128)])
+def test_sentinels_around_gemm_outputs_survive_every_epilogue(B, M, N, K, tile):
+    """Outputs (plain, lerp, add, mirrored, moments) are views with padding rows and columns full of a sentinel value:
+    no epilogue writes outside ``[M, N]``; split outputs are checked through their zero padding."""
+    sentinel = -7.0
+    a, b = _rand(B, M, K, seed=31), _rand(B, N, K, seed=32)
+    a_s, _ = ops.tf32_split(a, True, False)
+    b_s, _ = ops.tf32_split(b, True, False)
+
+    def padded(rows, cols):
+        buf = torch.full((B, rows + 3, cols + 12), sentinel, device="cuda")
+        return buf, buf[:, 1 : rows + 1, 4 : cols + 4]
+
+    def intact(buf, rows, cols):
+        probe = buf.clone()
+        probe[:, 1 : rows + 1, 4 : cols + 4] = sentinel
+        return bool((probe == sentinel).all())
+
+    want = a.double() @ b.double().transpose(1, 2)
+    tol = _tol(a.double(), b.double())
+    for mode, kwargs in (("store", {}), ("lerp", dict(mode=ops.EPI_LERP, w=0.5)), ("add", dict(mode=ops.EPI_ADD, alpha=-1.0))):
+        buf, view = padded(M, N)
+        view.zero_()
+        ops.tf32_gemm(a_s, b_s, K, out=view, **kwargs)
+        torch.cuda.synchronize()
+        assert intact(buf, M, N), mode
+        scale = {"store": 1.0, "lerp": 0.5, "add": -1.0}[mode]
+        assert float((view.double() - scale * want).abs().max()) < tol, mode
+    if M == N:  # one buffer as both operands: upper tiles plus mirrored stores
+        buf, view = padded(M, M)
+        view.zero_()
+        ops.tf32_gemm(a_s, a_s, K, mode=ops.EPI_ADD, alpha=1.0, out=view)
+        torch.cuda.synchronize()
+        assert intact(buf, M, M)
+        assert float((view.double() - a.double() @ a.double().transpose(1, 2)).abs().max()) < _tol(a.double(), a.double())
+    m, v = torch.zeros(B, M, N, device="cuda"), torch.zeros(B, M, N, device="cuda")
+    guard_m = torch.full((B * M * N + 64,), sentinel, device="cuda")
+    m = guard_m[32 : 32 + B * M * N].view(B, M, N).zero_()
+    s = ops.tf32_gemm(a_s, b_s, K, mode=ops.EPI_ADAM, b1=0.9, b2c=0.99, eps=1e-8, m=m, v=v, split_out=ops.SPLIT_COLS)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert bool((guard_m[:32] == sentinel).all()) and bool((guard_m[32 + B * M * N :] == sentinel).all())
+    kp = s.shape[-1] // 2
+    assert s.shape == (B, N, 2 * kp) and (kp == M or float(s[..., M:kp].abs().max()) == 0)
